@@ -1,0 +1,195 @@
+/*
+ * tokenselect_b200 -- C ABI of the decode-time token selection + sparse paged attention path.
+ *
+ * One library, plain C signatures, device pointers and sizes only.  The host side (Python,
+ * ctypes) mirrors the reference's patched attention forward on top of these calls.
+ *
+ * Conventions
+ *   - every call returns an int status (TS_OK == 0); nothing throws;
+ *   - calls that take a stream enqueue work on it and return without synchronising the host;
+ *   - all tensor pointers are borrowed device pointers that must stay valid until the stream has
+ *     passed the call's work; the library owns only its workspace and the per-request selection
+ *     cache, both allocated once by ts_create();
+ *   - one handle per process and GPU; calls on one handle are not thread-safe (the serving
+ *     stack drives a GPU from a single worker thread);
+ *   - errors found on the device (a pool row outside the pool, a workspace that is too small, a
+ *     bounded wait that ran out) are recorded in a sticky device word: later kernels of the
+ *     handle return early until ts_last_error() has read and cleared it.
+ *
+ * File:line citations name the reference code each entry point replaces
+ * (patcher/token_retrieval.py of pzs19/TokenSelect).
+ */
+#ifndef TOKENSELECT_B200_H
+#define TOKENSELECT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TS_ABI_VERSION 1
+
+/* status codes */
+#define TS_OK 0
+#define TS_ERR_INVALID_ARG 1
+#define TS_ERR_UNSUPPORTED 2      /* shape or dtype the kernels are not built for */
+#define TS_ERR_CUDA 3             /* a CUDA runtime call failed (see ts_last_cuda_error) */
+#define TS_ERR_CAPACITY 4         /* batch / context larger than the workspace was created for */
+#define TS_ERR_DEVICE_TIMEOUT 5   /* a bounded device-side wait ran out */
+#define TS_ERR_BAD_SLOT 6         /* a pool row index outside [0, pool_rows) */
+#define TS_ERR_BAD_LENGTH 7       /* a sequence length outside [1, max_ctx] or a bad request slot */
+#define TS_ERR_INTERNAL 8         /* an internal consistency check failed */
+
+/* element type of q, k, v, the pools and the output */
+#define TS_DTYPE_BF16 0
+#define TS_DTYPE_F32 1            /* check mode: every kernel computes from fp32 inputs */
+
+/* query-head -> KV-head pairing used while scoring (token_retrieval.py:202) */
+#define TS_GQA_MOD 0              /* h % hkv: what the reference does */
+#define TS_GQA_DIV 1              /* h / (hq/hkv): the conventional map */
+
+/* per-request decision of one layer step, as written to dbg_flags */
+#define TS_FLAG_DENSE 0           /* n_init+top_k+n_local >= N: attend to all tokens (:376-378) */
+#define TS_FLAG_RECOMPUTE 1       /* scores recomputed                               (:395-417) */
+#define TS_FLAG_REUSE 2           /* cached index set reused                         (:418-420) */
+
+/* ts_config.flags */
+#define TS_CFG_PLAIN_SCORE 1u     /* score with the plain-load kernel also for bf16 (diagnostic) */
+
+/*
+ * Knobs.  Replaces the module globals written by patch() (token_retrieval.py:885-918), the
+ * constructor arguments of ReqToTokenRetriever / TokenRetriever (:117-146, :264-327) and the
+ * attention arguments at :815-823.  Head counts are those of this tensor-parallel rank.
+ */
+typedef struct ts_config {
+    uint32_t struct_size;          /* sizeof(ts_config), checked */
+    int32_t device;                /* CUDA device ordinal */
+    int32_t n_layers;
+    int32_t hq;                    /* query heads on this rank            (:461, :580-582) */
+    int32_t hkv;                   /* KV heads on this rank               (:462, :583)     */
+    int32_t head_dim;
+    int32_t dtype;                 /* TS_DTYPE_* */
+    int32_t n_init;                /* :912 */
+    int32_t n_local;               /* :913 */
+    int32_t top_k;                 /* :911 */
+    int32_t kernel_size;           /* vote max-pool width, <= 0 off       (:366-369, :914) */
+    int32_t query_cache;           /* selection cache on/off              (:918) */
+    float similarity_threshold;    /* cosine threshold, fp32              (:313-315) */
+    int32_t gqa_map;               /* TS_GQA_* */
+    double rope_base;              /* :907 */
+    double rope_scale;             /* :908 */
+    float sm_scale;                /* attention logit scale               (:818) */
+    float logit_cap;               /* soft cap, used when > 0             (:819) */
+    int32_t max_reqs;              /* rows of req_to_token == request slots with cache state */
+    int32_t max_batch;             /* requests per call */
+    int32_t max_ctx;               /* longest sequence                    (:909 max_n_tokens) */
+    int64_t max_total_tokens;      /* sum of sequence lengths over one batch */
+    int32_t tp_rank;
+    int32_t tp_size;
+    uint32_t flags;                /* TS_CFG_* */
+    uint32_t reserved;
+    /* Optional host tables built the way RotaryEmbedding builds them (:73-96).  NULL: computed
+     * by the library from rope_base / rope_scale.
+     *   score_cos_sin: [head_dim/2][2] cos,sin at position n_local*rope_scale (:380-388)
+     *   attn_cos_sin : [n_init+top_k+n_local+1][head_dim/2][2] for positions 0.. with
+     *                  frequencies divided by rope_scale (:820-822) */
+    const float* score_cos_sin;
+    const float* attn_cos_sin;
+} ts_config;
+
+/*
+ * One decode step of one layer for a ragged batch.  Replaces the arguments that
+ * patched_radix_attention_forward (:827-842) takes from `self`, `q, k, v` and `input_metadata`.
+ */
+typedef struct ts_decode_args {
+    uint32_t struct_size;          /* sizeof(ts_decode_args), checked */
+    int32_t layer;
+    int32_t batch;
+    int32_t reserved;
+    const void* q;                 /* [batch, hq*head_dim], un-rotated                      (:816) */
+    const void* k_new;             /* [batch, hkv*head_dim] or NULL: rows appended first    (:849) */
+    const void* v_new;             /* [batch, hkv*head_dim] or NULL                         (:850) */
+    const int32_t* out_cache_loc;  /* [batch] pool rows of the new token                    (:849-852) */
+    void* k_pool;                  /* [pool_rows, hkv, head_dim] key buffer of this layer   (:847) */
+    void* v_pool;                  /* [pool_rows, hkv, head_dim] value buffer               (:848) */
+    int64_t pool_rows;
+    const int32_t* req_to_token;   /* [max_reqs, stride]: logical position -> pool row      (:599-601) */
+    int64_t req_to_token_stride;   /* elements between rows */
+    const int32_t* req_pool_indices; /* [batch] row of req_to_token per request             (:522) */
+    const int32_t* seq_lens;       /* [batch] tokens per request, counting the new one      (:523) */
+    void* out;                     /* [batch, hq*head_dim]                                  (:825) */
+    /* tensor-parallel exchange buffers (tp_size > 1): the caller all-reduces them between the
+     * three ts_tp_* calls                                                                  (:363-364) */
+    float* tp_votes;               /* >= ts_vote_buffer_elems() floats */
+    float* tp_cos;                 /* 4 floats per request: q.c, |q|^2, |c|^2, unused */
+    /* optional device outputs for inspection, NULL to skip */
+    int32_t* dbg_sel_slots;        /* [batch, n_sel] pool rows attended, list order */
+    int32_t* dbg_sel_pos;          /* [batch, n_sel] logical positions */
+    int32_t* dbg_sel_count;        /* [batch] */
+    int32_t* dbg_flags;            /* [batch] TS_FLAG_* */
+    void* stream;                  /* cudaStream_t */
+} ts_decode_args;
+
+typedef struct ts_handle ts_handle;
+
+int ts_abi_version(void);
+const char* ts_status_string(int status);
+
+/* Device bytes ts_create() will allocate for `cfg` (workspace + selection cache). */
+int ts_query_workspace(const ts_config* cfg, size_t* bytes);
+
+/* Elements of the fp32 vote vector for this configuration (size of the tp_votes buffer and of
+ * the tensor-parallel all-reduce message). */
+int ts_vote_buffer_elems(const ts_config* cfg, int64_t* elems);
+
+/* Allocate workspace and per-request state: replaces ReqToTokenRetriever.__init__ and
+ * TokenRetriever.__init__ (:117-146, :264-327). */
+int ts_create(const ts_config* cfg, ts_handle** out);
+int ts_destroy(ts_handle* h);
+
+/* A request joined or left request slot `req_slot`: forget its cached query, cached index set
+ * and counters.  Replaces get_token_retriever()'s fresh TokenRetriever (:147-163, :322-327). */
+int ts_reset_request(ts_handle* h, int32_t req_slot, void* stream);
+
+/* Whole layer step on one GPU: append K/V, select, attend.  Replaces
+ * patched_radix_attention_decode_forward_flashinfer (:777-825) with store_kv_cache (:844-854)
+ * and retrieval_indices (:375-449). */
+int ts_decode_layer(ts_handle* h, const ts_decode_args* args);
+
+/* The same step split at the tensor-parallel exchange points (:363-364):
+ *   ts_tp_prepare       K/V append, scoring-query rotation, cosine terms -> args->tp_cos
+ *   [caller: all_reduce(tp_cos, SUM) when the selection cache is on]
+ *   ts_tp_score_vote    decision, scoring, per-head softmax + head sum  -> args->tp_votes
+ *   [caller: all_reduce(tp_votes, SUM)]
+ *   ts_tp_select_attend top-k on the reduced votes, union, attention    -> args->out        */
+int ts_tp_prepare(ts_handle* h, const ts_decode_args* args);
+int ts_tp_score_vote(ts_handle* h, const ts_decode_args* args);
+int ts_tp_select_attend(ts_handle* h, const ts_decode_args* args);
+
+/* Selection-cache counters of a request slot (retrieval_count / skip_count, :150-161, :420-421).
+ * Synchronises the stream given. */
+int ts_get_counters(ts_handle* h, int32_t req_slot, uint64_t* retrievals, uint64_t* reuses, void* stream);
+
+/* Read and clear the sticky device error word.  Synchronises the device.  *code is a TS_ERR_*
+ * value or TS_OK; *detail is the offending value (row, length, ...) where one exists. */
+int ts_last_error(ts_handle* h, int32_t* code, int32_t* detail);
+const char* ts_last_cuda_error(ts_handle* h);
+
+/* Copy an internal buffer of the last call to host memory (synchronises; for tests).
+ *   which: 0 rotated scoring queries [batch, hq*head_dim] (dtype)
+ *          1 logits  [vote elems, hq] fp32, column c = kv_head*(hq/hkv) + j where j counts the
+ *            query heads paired with kv_head in ascending head order
+ *          2 votes   [vote elems] fp32 (after max-pool when enabled)
+ * In 1 and 2 the requests that recomputed their scores follow each other in batch order, each
+ * region starting on a multiple of 128 candidates. */
+int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes);
+
+/* Number of kernels launched by this handle so far. */
+int ts_launch_count(ts_handle* h, uint64_t* launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TOKENSELECT_B200_H */

@@ -1,0 +1,126 @@
+"""CPU-only checks: the C-ABI library builds, loads and exports every declared symbol; host-side
+configuration, rotation tables and knob plumbing.  No kernel is launched here."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tokenselect_oracle as orc
+from tokenselect_b200 import _lib, build, patcher
+from tokenselect_b200.engine import TokenSelectConfig, TokenSelectEngine, rotary_tables
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="session", autouse=True)
+def built_library():
+    build.build_library()
+    return _lib.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tokenselect_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ts_[a-z_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_library):
+    names = _declared_symbols()
+    assert len(names) >= 15
+    assert set(names) == set(_lib.EXPORTS)
+    for n in names:
+        assert hasattr(built_library, n), n
+    assert built_library.ts_abi_version() == _lib.TS_ABI_VERSION
+    assert built_library.ts_status_string(0) == b"ok"
+    assert b"slot" in built_library.ts_status_string(6) or b"row" in built_library.ts_status_string(6)
+
+
+def _cfg(**kw):
+    c = _lib.TsConfig()
+    c.struct_size = C.sizeof(_lib.TsConfig)
+    c.n_layers, c.hq, c.hkv, c.head_dim, c.dtype = 32, 32, 8, 128, 0
+    c.n_init, c.n_local, c.top_k, c.kernel_size = 128, 512, 2048, -1
+    c.rope_base, c.rope_scale, c.sm_scale = 5e5, 1.0, 128 ** -0.5
+    c.max_reqs, c.max_batch, c.max_ctx, c.max_total_tokens = 4, 1, 1 << 17, 1 << 17
+    c.tp_rank, c.tp_size = 0, 1
+    for k, v in kw.items():
+        setattr(c, k, v)
+    return c
+
+
+def test_workspace_query_and_validation(built_library):
+    ws = C.c_size_t()
+    assert built_library.ts_query_workspace(C.byref(_cfg()), C.byref(ws)) == 0
+    # logits (fp32, 32 heads) dominate: ~128 B per candidate
+    assert 16 << 20 < ws.value < 256 << 20
+    ve = C.c_int64()
+    assert built_library.ts_vote_buffer_elems(C.byref(_cfg()), C.byref(ve)) == 0
+    assert ve.value >= (1 << 17)
+    for bad, status in ((dict(struct_size=8), 1), (dict(hq=30), 1), (dict(head_dim=96), 2), (dict(dtype=5), 2),
+                        (dict(hq=32, hkv=2), 2), (dict(max_batch=100000), 1), (dict(tp_rank=2), 1),
+                        (dict(n_local=0), 1), (dict(rope_base=0.0), 1)):
+        assert built_library.ts_query_workspace(C.byref(_cfg(**bad)), C.byref(ws)) == status, bad
+    h = C.c_void_p()
+    assert built_library.ts_create(C.byref(_cfg(hq=30)), C.byref(h)) == 1
+    assert built_library.ts_reset_request(None, 0, None) == 1
+    assert built_library.ts_decode_layer(None, None) == 1
+
+
+def test_struct_layout_matches_header():
+    """Compile a one-line C program against the header and compare sizeof with the ctypes mirror."""
+    import subprocess
+    import tempfile
+    src = ('#include "tokenselect_b200.h"\n#include <stdio.h>\n#include <stddef.h>\n'
+           'int main(){printf("%zu %zu %zu %zu\\n", sizeof(ts_config), sizeof(ts_decode_args),'
+           ' offsetof(ts_config, rope_base), offsetof(ts_decode_args, stream));return 0;}\n')
+    with tempfile.TemporaryDirectory() as d:
+        open(os.path.join(d, "s.c"), "w").write(src)
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), os.path.join(d, "s.c"), "-o",
+                               os.path.join(d, "s")])
+        a, b, c, e = map(int, subprocess.check_output([os.path.join(d, "s")]).split())
+    assert a == C.sizeof(_lib.TsConfig) and b == C.sizeof(_lib.TsDecodeArgs)
+    assert c == _lib.TsConfig.rope_base.offset and e == _lib.TsDecodeArgs.stream.offset
+
+
+def test_rotation_tables_match_oracle_bitwise():
+    cfg = TokenSelectConfig(rope_base=5e5, n_init=16, n_local=64, top_k=256, head_dim=128)
+    score, attn = rotary_tables(cfg)
+    inv = orc.rope_inv_freq(128, 5e5)
+    cos, sin = orc.rope_cos_sin(torch.tensor([64.0]), inv)
+    assert torch.equal(score[:, 0], cos[0, :64]) and torch.equal(score[:, 1], sin[0, :64])
+    cos, sin = orc.rope_cos_sin(torch.arange(cfg.n_sel + 1, dtype=torch.float32), inv)
+    assert torch.equal(attn[..., 0], cos[:, :64]) and torch.equal(attn[..., 1], sin[:, :64])
+    assert attn.shape == (cfg.n_sel + 1, 64, 2)
+
+
+def test_config_from_reference_style_yaml(tmp_path):
+    p = tmp_path / "llama.yaml"
+    p.write_text("model:\n  type: token-retrieval\n  path: some/model\n  rope_base: 500000\n  rope_scale: 1\n"
+                 "  n_init: 128\n  n_local: 512\n  top_k: 2048\n  max_n_tokens: 1048576\nmax_len: 1048576\n"
+                 "chunk_size: 8192\ndtype: bfloat16\n")
+    cfg = TokenSelectConfig.from_yaml(str(p), query_cache=True)
+    assert (cfg.rope_base, cfg.n_init, cfg.n_local, cfg.top_k, cfg.max_n_tokens) == (500000, 128, 512, 2048, 1048576)
+    assert cfg.query_cache and cfg.n_sel == 2688 and cfg.kernel_size == -1
+
+
+def test_patch_sets_reference_knobs():
+    patcher.patch(rope_base=5e5, rope_scale=1, max_n_tokens=4096, top_k=64, n_init=4, n_local=32, kernel_size=5)
+    assert (patcher.ROPE_BASE, patcher.TOP_K, patcher.N_INIT, patcher.N_Local, patcher.KERNEL_SIZE) == \
+        (5e5, 64, 4, 32, 5)
+    assert patcher.QUERY_ROTATE is True and patcher.QUERY_CACHE is False and patcher.PREFILL_CHUNK_SIZE == 512
+    with pytest.raises(NotImplementedError):
+        patcher.patch(rope_model="ROPE_OTHER")
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU failure mode")
+def test_engine_refuses_to_run_without_a_gpu():
+    with pytest.raises(RuntimeError, match="CUDA"):
+        TokenSelectEngine(TokenSelectConfig())
+
+
+def test_vote_prefix_bound():
+    assert TokenSelectEngine.vote_elems_for([131072], 128, 512) == (131072 - 640 + 127) // 128 * 128
+    assert TokenSelectEngine.vote_elems_for([100, 700, 641], 128, 512) == 128 + 128

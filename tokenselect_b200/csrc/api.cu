@@ -1,0 +1,382 @@
+// C ABI of tokenselect_b200: handle, workspace, call sequencing.  See include/tokenselect_b200.h.
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+using namespace ts;
+
+struct ts_handle {
+    ts_config cfg;
+    int num_sms;
+    int n_sel;
+    size_t elem;                  // bytes per element of the model dtype
+    long long cand_capacity;
+    int score_grid;
+    int attn_chunk_tokens, attn_chunks;
+    // one device allocation, carved up
+    unsigned char* arena;
+    size_t arena_bytes;
+    LayerParams base;             // workspace pointers and configuration, call fields empty
+    unsigned long long launches;
+    int last_batch;
+    char cuda_msg[256];
+};
+
+namespace {
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int validate(const ts_config* c) {
+    if (!c || c->struct_size != sizeof(ts_config)) return TS_ERR_INVALID_ARG;
+    if (c->n_layers < 1 || c->hq < 1 || c->hkv < 1 || c->hq % c->hkv != 0) return TS_ERR_INVALID_ARG;
+    if (c->hq > kMaxHq) return TS_ERR_UNSUPPORTED;
+    if (c->head_dim != 64 && c->head_dim != 128) return TS_ERR_UNSUPPORTED;
+    if (c->dtype != TS_DTYPE_BF16 && c->dtype != TS_DTYPE_F32) return TS_ERR_UNSUPPORTED;
+    if (c->hq / c->hkv > 8) return TS_ERR_UNSUPPORTED;
+    if (c->n_init < 0 || c->n_local < 1 || c->top_k < 1) return TS_ERR_INVALID_ARG;
+    if (c->max_reqs < 1 || c->max_batch < 1 || c->max_batch > kMaxBatch) return TS_ERR_INVALID_ARG;
+    if (c->max_ctx < 1 || c->max_total_tokens < 1) return TS_ERR_INVALID_ARG;
+    if (c->gqa_map != TS_GQA_MOD && c->gqa_map != TS_GQA_DIV) return TS_ERR_INVALID_ARG;
+    if (c->tp_size < 1 || c->tp_rank < 0 || c->tp_rank >= c->tp_size) return TS_ERR_INVALID_ARG;
+    if (!(c->rope_base > 0.0) || !(c->rope_scale > 0.0)) return TS_ERR_INVALID_ARG;
+    return TS_OK;
+}
+
+long long cand_capacity_of(const ts_config* c) {
+    // every request's candidate region is rounded up to kCandAlign
+    return (long long)align_up((size_t)c->max_total_tokens, kCandAlign) + (long long)kCandAlign * c->max_batch;
+}
+
+struct Carve {
+    size_t off = 0;
+    size_t take(size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; }
+};
+
+// Computes the arena layout; with h == nullptr only the total is produced.
+size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
+    const size_t elem = c->dtype == TS_DTYPE_BF16 ? 2 : 4;
+    const int n_sel = c->n_init + c->top_k + c->n_local;
+    const long long cap = cand_capacity_of(c);
+    const int grid = score_grid_size(num_sms);
+    const size_t hd = (size_t)c->hq * c->head_dim;
+    // split the list so that one request's chunks cover the SMs about once
+    int ch = (n_sel + num_sms - 1) / num_sms;
+    ch = ch < 16 ? 16 : (ch + 7) / 8 * 8;
+    const int chunks = (n_sel + ch - 1) / ch;
+    Carve cv;
+    size_t o_err = cv.take(16);
+    size_t o_qrot = cv.take((size_t)c->max_batch * hd * elem);
+    size_t o_flags = cv.take((size_t)c->max_batch * 4);
+    size_t o_cos = cv.take((size_t)c->max_batch * 16);
+    size_t o_logits = cv.take((size_t)cap * c->hq * 4);
+    size_t o_part = cv.take((size_t)c->max_batch * grid * c->hq * 8);
+    size_t o_votes = cv.take((size_t)cap * 4);
+    size_t o_vpool = cv.take(c->kernel_size > 0 ? (size_t)cap * 4 : 16);
+    size_t o_hist = cv.take((size_t)c->max_batch * kHistBins * 4);
+    size_t o_bitmap = cv.take((size_t)cap / 8 + 64);
+    size_t o_cand = cv.take((size_t)cap * 8);
+    size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
+    size_t o_pos = cv.take((size_t)c->max_batch * n_sel * 4);
+    size_t o_count = cv.take((size_t)c->max_batch * 4);
+    size_t o_ao = cv.take((size_t)c->max_batch * chunks * hd * 4);
+    size_t o_aml = cv.take((size_t)c->max_batch * chunks * c->hq * 8);
+    size_t o_scs = cv.take((size_t)(c->head_dim / 2) * 8);
+    size_t o_acs = cv.take((size_t)(n_sel + 1) * (c->head_dim / 2) * 8);
+    size_t o_fp = cv.take((size_t)c->max_reqs * c->n_layers * hd * elem);
+    size_t o_pc = cv.take((size_t)c->max_reqs * c->n_layers * c->top_k * 4);
+    size_t o_valid = cv.take((size_t)c->max_reqs * c->n_layers * 4);
+    size_t o_cnt = cv.take((size_t)c->max_reqs * 16);
+    if (h) {
+        unsigned char* a = h->arena;
+        LayerParams& p = h->base;
+        memset(&p, 0, sizeof(p));
+        p.hq = c->hq; p.hkv = c->hkv; p.d = c->head_dim; p.group = c->hq / c->hkv;
+        p.n_init = c->n_init; p.n_local = c->n_local; p.top_k = c->top_k; p.n_sel = n_sel;
+        p.gqa_map = c->gqa_map; p.query_cache = c->query_cache ? 1 : 0; p.kernel_size = c->kernel_size;
+        p.theta = c->similarity_threshold; p.sm_scale = c->sm_scale; p.logit_cap = c->logit_cap;
+        p.n_layers = c->n_layers; p.max_reqs = c->max_reqs; p.max_ctx = c->max_ctx; p.tp_size = c->tp_size;
+        p.err = reinterpret_cast<int*>(a + o_err);
+        p.q_rot = a + o_qrot;
+        p.flags = reinterpret_cast<int*>(a + o_flags);
+        p.cos_terms = reinterpret_cast<float*>(a + o_cos);
+        p.logits = reinterpret_cast<float*>(a + o_logits);
+        p.partials = reinterpret_cast<float2*>(a + o_part);
+        p.score_grid = grid;
+        p.votes = reinterpret_cast<float*>(a + o_votes);
+        p.votes_pool = reinterpret_cast<float*>(a + o_vpool);
+        p.votes_sel = c->kernel_size > 0 ? p.votes_pool : p.votes;
+        p.hist = reinterpret_cast<unsigned*>(a + o_hist);
+        p.bitmap = reinterpret_cast<unsigned*>(a + o_bitmap);
+        p.cand = reinterpret_cast<uint2*>(a + o_cand);
+        p.sel_slots = reinterpret_cast<int*>(a + o_slots);
+        p.sel_pos = reinterpret_cast<int*>(a + o_pos);
+        p.sel_count = reinterpret_cast<int*>(a + o_count);
+        p.attn_o = reinterpret_cast<float*>(a + o_ao);
+        p.attn_ml = reinterpret_cast<float2*>(a + o_aml);
+        p.attn_chunks = chunks; p.attn_chunk_tokens = ch;
+        p.score_cs = reinterpret_cast<const float2*>(a + o_scs);
+        p.attn_cs = reinterpret_cast<const float2*>(a + o_acs);
+        p.cand_capacity = cap;
+        p.fp_cache = a + o_fp;
+        p.pos_cache = reinterpret_cast<int*>(a + o_pc);
+        p.valid = reinterpret_cast<int*>(a + o_valid);
+        p.counters = reinterpret_cast<unsigned long long*>(a + o_cnt);
+        h->elem = elem; h->n_sel = n_sel; h->cand_capacity = cap; h->score_grid = grid;
+        h->attn_chunk_tokens = ch; h->attn_chunks = chunks;
+    }
+    return cv.off;
+}
+
+int cuda_fail(ts_handle* h, cudaError_t e, const char* what) {
+    if (h) snprintf(h->cuda_msg, sizeof(h->cuda_msg), "%s: %s", what, cudaGetErrorString(e));
+    return TS_ERR_CUDA;
+}
+
+int num_sms_of(int device, int* out) {
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return TS_ERR_CUDA;
+    *out = prop.multiProcessorCount;
+    return TS_OK;
+}
+
+int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l) {
+    if (!h || !a || a->struct_size != sizeof(ts_decode_args)) return TS_ERR_INVALID_ARG;
+    if (a->layer < 0 || a->layer >= h->cfg.n_layers) return TS_ERR_INVALID_ARG;
+    if (a->batch < 1) return TS_ERR_INVALID_ARG;
+    if (a->batch > h->cfg.max_batch) return TS_ERR_CAPACITY;
+    if (!a->q || !a->k_pool || !a->v_pool || !a->req_to_token || !a->req_pool_indices || !a->seq_lens || !a->out)
+        return TS_ERR_INVALID_ARG;
+    if ((a->k_new != nullptr) != (a->v_new != nullptr)) return TS_ERR_INVALID_ARG;
+    if (a->k_new && !a->out_cache_loc) return TS_ERR_INVALID_ARG;
+    if (a->pool_rows < 1 || a->req_to_token_stride < 1) return TS_ERR_INVALID_ARG;
+    p = h->base;
+    p.layer = a->layer; p.batch = a->batch;
+    p.q = a->q; p.k_new = a->k_new; p.v_new = a->v_new; p.out_cache_loc = a->out_cache_loc;
+    p.k_pool = a->k_pool; p.v_pool = a->v_pool; p.pool_rows = a->pool_rows;
+    p.rtt = a->req_to_token; p.rtt_stride = a->req_to_token_stride;
+    p.req_pool_indices = a->req_pool_indices; p.seq_lens = a->seq_lens; p.out = a->out;
+    if (h->cfg.tp_size > 1) {
+        if (!a->tp_votes || !a->tp_cos) return TS_ERR_INVALID_ARG;
+        p.votes = a->tp_votes;
+        p.cos_terms = a->tp_cos;
+        if (h->cfg.kernel_size <= 0) p.votes_sel = p.votes;
+    }
+    l.stream = reinterpret_cast<cudaStream_t>(a->stream);
+    l.num_sms = h->num_sms;
+    l.dtype = h->cfg.dtype;
+    l.flags = h->cfg.flags;
+    l.launch_count = &h->launches;
+    h->last_batch = a->batch;
+    return TS_OK;
+}
+
+int copy_debug(ts_handle* h, const ts_decode_args* a, const LayerParams& p, cudaStream_t s) {
+    cudaError_t e = cudaSuccess;
+    const size_t nb = (size_t)a->batch;
+    if (a->dbg_sel_slots && e == cudaSuccess)
+        e = cudaMemcpyAsync(a->dbg_sel_slots, p.sel_slots, nb * h->n_sel * 4, cudaMemcpyDeviceToDevice, s);
+    if (a->dbg_sel_pos && e == cudaSuccess)
+        e = cudaMemcpyAsync(a->dbg_sel_pos, p.sel_pos, nb * h->n_sel * 4, cudaMemcpyDeviceToDevice, s);
+    if (a->dbg_sel_count && e == cudaSuccess)
+        e = cudaMemcpyAsync(a->dbg_sel_count, p.sel_count, nb * 4, cudaMemcpyDeviceToDevice, s);
+    if (a->dbg_flags && e == cudaSuccess)
+        e = cudaMemcpyAsync(a->dbg_flags, p.flags, nb * 4, cudaMemcpyDeviceToDevice, s);
+    return e == cudaSuccess ? TS_OK : cuda_fail(h, e, "debug copy");
+}
+
+#define TS_TRY(expr, what)                                     \
+    do {                                                       \
+        cudaError_t e__ = (expr);                              \
+        if (e__ != cudaSuccess) return cuda_fail(h, e__, what); \
+    } while (0)
+
+}  // namespace
+
+extern "C" {
+
+int ts_abi_version(void) { return TS_ABI_VERSION; }
+
+const char* ts_status_string(int s) {
+    switch (s) {
+        case TS_OK: return "ok";
+        case TS_ERR_INVALID_ARG: return "invalid argument";
+        case TS_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+        case TS_ERR_CUDA: return "CUDA runtime error";
+        case TS_ERR_CAPACITY: return "batch or context exceeds the workspace";
+        case TS_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        case TS_ERR_BAD_SLOT: return "pool row index outside the pool";
+        case TS_ERR_BAD_LENGTH: return "sequence length or request slot out of range";
+        case TS_ERR_INTERNAL: return "internal consistency check failed";
+    }
+    return "unknown status";
+}
+
+int ts_query_workspace(const ts_config* cfg, size_t* bytes) {
+    int s = validate(cfg);
+    if (s != TS_OK) return s;
+    if (!bytes) return TS_ERR_INVALID_ARG;
+    int sms = 148;
+    int dev_count = 0;
+    if (cudaGetDeviceCount(&dev_count) == cudaSuccess && cfg->device < dev_count) num_sms_of(cfg->device, &sms);
+    *bytes = layout(cfg, sms, nullptr);
+    return TS_OK;
+}
+
+int ts_vote_buffer_elems(const ts_config* cfg, int64_t* elems) {
+    int s = validate(cfg);
+    if (s != TS_OK) return s;
+    if (!elems) return TS_ERR_INVALID_ARG;
+    *elems = cand_capacity_of(cfg);
+    return TS_OK;
+}
+
+int ts_create(const ts_config* cfg, ts_handle** out) {
+    int s = validate(cfg);
+    if (s != TS_OK) return s;
+    if (!out) return TS_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (cudaSetDevice(cfg->device) != cudaSuccess) return TS_ERR_CUDA;
+    ts_handle* h = new (std::nothrow) ts_handle();
+    if (!h) return TS_ERR_CUDA;
+    memset(h, 0, sizeof(*h));
+    h->cfg = *cfg;
+    h->cfg.score_cos_sin = nullptr;
+    h->cfg.attn_cos_sin = nullptr;
+    if (num_sms_of(cfg->device, &h->num_sms) != TS_OK) { delete h; return TS_ERR_CUDA; }
+    h->arena_bytes = layout(cfg, h->num_sms, nullptr);
+    if (cudaMalloc(&h->arena, h->arena_bytes) != cudaSuccess) { delete h; return TS_ERR_CUDA; }
+    layout(cfg, h->num_sms, h);
+    const LayerParams& p = h->base;
+    const int half = cfg->head_dim / 2;
+    cudaError_t e = cudaMemset(h->arena, 0, h->arena_bytes);
+    // rotation tables: taken from the caller when given, otherwise computed on the device
+    if (e == cudaSuccess && (!cfg->score_cos_sin || !cfg->attn_cos_sin))
+        e = launch_rope_tables(const_cast<float2*>(p.score_cs), const_cast<float2*>(p.attn_cs), cfg->head_dim,
+                               h->n_sel + 1, cfg->rope_base, cfg->rope_scale, cfg->n_local, 0);
+    if (e == cudaSuccess && cfg->score_cos_sin)
+        e = cudaMemcpy(const_cast<float2*>(p.score_cs), cfg->score_cos_sin, (size_t)half * 8, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && cfg->attn_cos_sin)
+        e = cudaMemcpy(const_cast<float2*>(p.attn_cs), cfg->attn_cos_sin, (size_t)(h->n_sel + 1) * half * 8,
+                       cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { cudaFree(h->arena); delete h; return TS_ERR_CUDA; }
+    *out = h;
+    return TS_OK;
+}
+
+int ts_destroy(ts_handle* h) {
+    if (!h) return TS_ERR_INVALID_ARG;
+    cudaSetDevice(h->cfg.device);
+    cudaDeviceSynchronize();
+    cudaFree(h->arena);
+    delete h;
+    return TS_OK;
+}
+
+int ts_reset_request(ts_handle* h, int32_t req_slot, void* stream) {
+    if (!h || req_slot < 0 || req_slot >= h->cfg.max_reqs) return TS_ERR_INVALID_ARG;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    TS_TRY(cudaMemsetAsync(h->base.valid + (size_t)req_slot * h->cfg.n_layers, 0, (size_t)h->cfg.n_layers * 4, s),
+           "reset valid");
+    TS_TRY(cudaMemsetAsync(h->base.counters + 2 * (size_t)req_slot, 0, 16, s), "reset counters");
+    return TS_OK;
+}
+
+int ts_tp_prepare(ts_handle* h, const ts_decode_args* a) {
+    LayerParams p; Launch l;
+    int s = fill(h, a, p, l);
+    if (s != TS_OK) return s;
+    TS_TRY(launch_prep(p, l, false), "prep");
+    return TS_OK;
+}
+
+int ts_tp_score_vote(ts_handle* h, const ts_decode_args* a) {
+    LayerParams p; Launch l;
+    int s = fill(h, a, p, l);
+    if (s != TS_OK) return s;
+    if (p.query_cache) TS_TRY(launch_decide(p, l), "decide");
+    TS_TRY(launch_score(p, l), "score");
+    TS_TRY(launch_vote(p, l, false), "vote");
+    return TS_OK;
+}
+
+int ts_tp_select_attend(ts_handle* h, const ts_decode_args* a) {
+    LayerParams p; Launch l;
+    int s = fill(h, a, p, l);
+    if (s != TS_OK) return s;
+    TS_TRY(launch_pool_hist(p, l), "pool_hist");
+    TS_TRY(launch_select(p, l), "select");
+    TS_TRY(launch_attend(p, l), "attend");
+    return copy_debug(h, a, p, l.stream);
+}
+
+int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
+    if (h && h->cfg.tp_size > 1) {
+        // single call without the exchange: each rank would select from its own votes only
+        return TS_ERR_INVALID_ARG;
+    }
+    LayerParams p; Launch l;
+    int s = fill(h, a, p, l);
+    if (s != TS_OK) return s;
+    const bool pooled = p.kernel_size > 0;
+    TS_TRY(launch_prep(p, l, true), "prep");
+    TS_TRY(launch_score(p, l), "score");
+    TS_TRY(launch_vote(p, l, !pooled), "vote");
+    if (pooled) TS_TRY(launch_pool_hist(p, l), "pool_hist");
+    TS_TRY(launch_select(p, l), "select");
+    TS_TRY(launch_attend(p, l), "attend");
+    return copy_debug(h, a, p, l.stream);
+}
+
+int ts_get_counters(ts_handle* h, int32_t req_slot, uint64_t* retrievals, uint64_t* reuses, void* stream) {
+    if (!h || req_slot < 0 || req_slot >= h->cfg.max_reqs) return TS_ERR_INVALID_ARG;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    unsigned long long v[2];
+    TS_TRY(cudaMemcpyAsync(v, h->base.counters + 2 * (size_t)req_slot, 16, cudaMemcpyDeviceToHost, s), "counters");
+    TS_TRY(cudaStreamSynchronize(s), "counters sync");
+    if (retrievals) *retrievals = v[0];
+    if (reuses) *reuses = v[1];
+    return TS_OK;
+}
+
+int ts_last_error(ts_handle* h, int32_t* code, int32_t* detail) {
+    if (!h) return TS_ERR_INVALID_ARG;
+    int v[2] = {0, 0};
+    TS_TRY(cudaDeviceSynchronize(), "sync");
+    TS_TRY(cudaMemcpy(v, h->base.err, 8, cudaMemcpyDeviceToHost), "read error word");
+    if (v[0] != 0) TS_TRY(cudaMemset(h->base.err, 0, 8), "clear error word");
+    if (code) *code = v[0];
+    if (detail) *detail = v[1];
+    return TS_OK;
+}
+
+const char* ts_last_cuda_error(ts_handle* h) { return h ? h->cuda_msg : ""; }
+
+int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes) {
+    if (!h || !host_dst) return TS_ERR_INVALID_ARG;
+    const LayerParams& p = h->base;
+    const void* src = nullptr;
+    size_t avail = 0;
+    const size_t hd = (size_t)h->cfg.hq * h->cfg.head_dim;
+    switch (which) {
+        case 0: src = p.q_rot; avail = (size_t)h->cfg.max_batch * hd * h->elem; break;
+        case 1: src = p.logits; avail = (size_t)h->cand_capacity * h->cfg.hq * 4; break;
+        case 2: src = p.votes_sel; avail = (size_t)h->cand_capacity * 4; break;
+        default: return TS_ERR_INVALID_ARG;
+    }
+    if (bytes > avail) return TS_ERR_INVALID_ARG;
+    TS_TRY(cudaDeviceSynchronize(), "sync");
+    TS_TRY(cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost), "debug read");
+    return TS_OK;
+}
+
+int ts_launch_count(ts_handle* h, uint64_t* launches) {
+    if (!h || !launches) return TS_ERR_INVALID_ARG;
+    *launches = h->launches;
+    return TS_OK;
+}
+
+}  // extern "C"

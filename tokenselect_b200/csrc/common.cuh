@@ -1,0 +1,170 @@
+// Shared declarations of the tokenselect_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tokenselect_b200.h"
+
+namespace ts {
+
+constexpr int kMaxBatch = 256;        // requests per call (plan arrays live in shared memory)
+constexpr int kMaxHq = 64;            // query heads per rank
+constexpr int kCandAlign = 128;       // each request's candidate region starts on this multiple
+constexpr int kHistBins = 2048;       // first radix level: vote bits [30:20]
+constexpr int kScoreThreads = 288;    // 1 copy-issuing warp + 8 mma warps
+constexpr int kScoreStages = 5;
+constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stage
+constexpr int kAttnThreads = 256;
+constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
+
+// Everything a kernel of one layer step needs.  Passed by value.
+struct LayerParams {
+    // configuration
+    int hq, hkv, d, group;
+    int n_init, n_local, top_k, n_sel;
+    int gqa_map, query_cache, kernel_size;
+    float theta, sm_scale, logit_cap;
+    int n_layers, max_reqs, max_ctx;
+    int tp_size;
+    // call
+    int layer, batch;
+    const void* q;
+    const void* k_new;
+    const void* v_new;
+    const int* out_cache_loc;
+    void* k_pool;
+    void* v_pool;
+    long long pool_rows;
+    const int* rtt;
+    long long rtt_stride;
+    const int* req_pool_indices;
+    const int* seq_lens;
+    void* out;
+    // workspace
+    void* q_rot;               // [max_batch, hq*d] dtype: rotated scoring queries
+    int* flags;                // [max_batch] TS_FLAG_*
+    float* cos_terms;          // [max_batch, 4] (q.c, |q|^2, |c|^2, -)
+    float* logits;             // [cand_capacity, hq]
+    float2* partials;          // [max_batch, score_grid, hq] per-CTA (max, sum exp)
+    int score_grid;
+    float* votes;              // [cand_capacity] head-summed softmax
+    float* votes_sel;          // votes the selection reads (== votes, or the pooled copy)
+    float* votes_pool;         // [cand_capacity] max-pooled votes
+    unsigned* hist;            // [max_batch, kHistBins]
+    unsigned* bitmap;          // [cand_capacity/32] selected-candidate bits
+    uint2* cand;               // [cand_capacity] (candidate index, vote bits) of the threshold bin
+    int* sel_slots;            // [max_batch, n_sel]
+    int* sel_pos;              // [max_batch, n_sel]
+    int* sel_count;            // [max_batch]
+    float* attn_o;             // [max_batch, attn_chunks, hq, d]
+    float2* attn_ml;           // [max_batch, attn_chunks, hq]
+    int attn_chunks;
+    int attn_chunk_tokens;
+    const float2* score_cs;    // [d/2] (cos, sin) of the scoring position
+    const float2* attn_cs;     // [n_sel+1, d/2]
+    long long cand_capacity;
+    // per-request selection cache
+    void* fp_cache;            // [max_reqs, n_layers, hq*d] dtype
+    int* pos_cache;            // [max_reqs, n_layers, top_k]
+    int* valid;                // [max_reqs, n_layers]
+    unsigned long long* counters;  // [max_reqs, 2] retrievals, reuses
+    int* err;                  // [2] sticky (code, detail)
+};
+
+// Per-request plan, rebuilt in shared memory by every kernel from seq_lens and flags.
+struct Plan {
+    int n[kMaxBatch];          // sequence length
+    int flag[kMaxBatch];
+    int nc[kMaxBatch];         // candidates scored this step (0 unless RECOMPUTE)
+    int off[kMaxBatch + 1];    // start of the request's candidate region (multiple of kCandAlign)
+    int ok;                    // 0: the sticky error word is set, or the workspace is too small
+};
+
+__device__ __forceinline__ void set_error(int* err, int code, int detail) {
+    if (atomicCAS(err, 0, code) == 0) err[1] = detail;
+}
+
+// Number of candidates the selection reads after the optional max-pool: an even window shortens
+// the vote vector by one (padding (K-1)/2 on both sides, stride 1).
+__host__ __device__ __forceinline__ int pooled_len(int nc, int kernel_size) {
+    if (kernel_size <= 0) return nc;
+    int pad = (kernel_size - 1) / 2;
+    return nc + 2 * pad - kernel_size + 1;
+}
+
+// All threads of the block call this; returns after a __syncthreads().  False means: do nothing.
+__device__ __forceinline__ bool build_plan(const LayerParams& p, Plan& s) {
+    for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
+        int n = p.seq_lens[b];
+        int f = p.flags[b];
+        s.n[b] = n;
+        s.flag[b] = f;
+        s.nc[b] = (f == TS_FLAG_RECOMPUTE) ? (n - p.n_init - p.n_local) : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int carry = 0;
+        for (int base = 0; base < p.batch; base += 32) {
+            int b = base + threadIdx.x;
+            int v = (b < p.batch) ? ((s.nc[b] + kCandAlign - 1) / kCandAlign) * kCandAlign : 0;
+            int inc = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                int t = __shfl_up_sync(0xffffffffu, inc, o);
+                if ((int)threadIdx.x >= o) inc += t;
+            }
+            if (b < p.batch) s.off[b] = carry + inc - v;
+            carry += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (threadIdx.x == 0) {
+            s.off[p.batch] = carry;
+            s.ok = (*(volatile int*)p.err == 0) ? 1 : 0;
+            if ((long long)carry > p.cand_capacity) {
+                set_error(p.err, TS_ERR_CAPACITY, carry);
+                s.ok = 0;
+            }
+        }
+    }
+    __syncthreads();
+    return s.ok != 0;
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// (max, sum) pairs of an online softmax.
+__device__ __forceinline__ void ml_merge(float& m, float& l, float mo, float lo) {
+    float mn = fmaxf(m, mo);
+    if (mn == -INFINITY) { m = mn; l = 0.f; return; }
+    l = l * exp2f((m - mn) * 1.4426950408889634f) + lo * exp2f((mo - mn) * 1.4426950408889634f);
+    m = mn;
+}
+
+// host-side launchers, one per translation unit ------------------------------------------------
+struct Launch {
+    cudaStream_t stream;
+    int num_sms;
+    int dtype;
+    unsigned flags;
+    unsigned long long* launch_count;
+};
+
+cudaError_t launch_rope_tables(float2* score_cs, float2* attn_cs, int d, int n_rows, double base,
+                               double rope_scale, int n_local, cudaStream_t stream);
+cudaError_t launch_prep(const LayerParams& p, const Launch& l, bool fused_decide);
+cudaError_t launch_decide(const LayerParams& p, const Launch& l);
+cudaError_t launch_score(const LayerParams& p, const Launch& l);
+cudaError_t launch_vote(const LayerParams& p, const Launch& l, bool with_hist);
+cudaError_t launch_pool_hist(const LayerParams& p, const Launch& l);
+cudaError_t launch_select(const LayerParams& p, const Launch& l);
+cudaError_t launch_attend(const LayerParams& p, const Launch& l);
+int score_grid_size(int num_sms);
+size_t score_smem_bytes(int hkv);
+
+}  // namespace ts

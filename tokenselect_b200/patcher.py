@@ -1,0 +1,177 @@
+"""Drop-in surface of the reference's patcher for the decode path.
+
+The reference monkey-patches a serving stack that is not a dependency here.  This module keeps the
+names, argument meaning and error behaviour of the pieces the decode path touches
+(patcher/token_retrieval.py):
+
+* ``patch(...)``                      -- the knob entry point (:885-921); stores module-level knobs.
+* ``ForwardMode``, ``InputMetadata``  -- the metadata fields the patched forward reads (:519-532).
+* ``ReqToTokenPool``, ``TokenToKVPool`` -- the paged layout: page size 1, ``req_to_token[req, pos]``
+  is a pool row, K and V buffers of ``[rows, kv_heads, head_dim]`` per layer (:170, :599-601, :847-848).
+* ``ReqToTokenRetriever``             -- per-request state keyed by request id (:117-163).
+* ``RadixAttention.forward(q, k, v, input_metadata)`` -- the patched forward (:827-842): stores the
+  new K/V, selects, attends, returns ``[batch, heads*head_dim]``.
+
+A serving stack integrates by constructing one ``ReqToTokenRetriever`` per model runner (as
+PatchedModelRunner does at :458-469) and assigning ``RadixAttention.forward`` /
+``patched_radix_attention_forward`` onto its attention class (as :868-875 does).
+"""
+from __future__ import annotations
+
+import dataclasses
+import enum
+from typing import List, Optional, Sequence
+
+import torch
+
+from .engine import TokenSelectConfig, TokenSelectEngine
+
+# knobs written by patch(), same names as the reference's module globals (:29-39)
+ROPE_BASE = -1
+ROPE_SCALE = -1
+ROPE_MODE = ""
+MAX_N_TOKENS = -1
+TOP_K = -1
+N_INIT = -1
+N_Local = -1
+PREFILL_CHUNK_SIZE = -1
+QUERY_ROTATE = False
+QUERY_CACHE = False
+KERNEL_SIZE = -1
+SIMILARITY_THRESHOLD = 0.9
+GQA_MAP = "mod"
+
+
+def patch(rope_base=1e6, rope_scale=1, rope_model="ROPE_LLAMA", max_n_tokens=1024, top_k=16, n_init=1,
+          n_local=16, kernel_size=-1, *, query_cache=False, similarity_threshold=0.9, gqa_map="mod"):
+    """Same positional knobs and defaults as the reference's ``patch`` (:885-894).  The keyword-only
+    extras expose what the reference hard-codes: ``QUERY_CACHE`` (:918), the 0.9 threshold (:313-315)
+    and the scoring head map (:202)."""
+    global ROPE_BASE, ROPE_SCALE, ROPE_MODE, MAX_N_TOKENS, TOP_K, N_INIT, N_Local, KERNEL_SIZE
+    global QUERY_ROTATE, QUERY_CACHE, PREFILL_CHUNK_SIZE, SIMILARITY_THRESHOLD, GQA_MAP
+    if rope_model != "ROPE_LLAMA":
+        raise NotImplementedError("only the ROPE_LLAMA positional mode is implemented")
+    ROPE_BASE, ROPE_SCALE, ROPE_MODE = rope_base, rope_scale, rope_model
+    MAX_N_TOKENS, TOP_K, N_INIT, N_Local, KERNEL_SIZE = max_n_tokens, top_k, n_init, n_local, kernel_size
+    QUERY_ROTATE, PREFILL_CHUNK_SIZE = True, 512
+    QUERY_CACHE, SIMILARITY_THRESHOLD, GQA_MAP = bool(query_cache), float(similarity_threshold), gqa_map
+
+
+class ForwardMode(enum.IntEnum):
+    PREFILL = enum.auto()
+    EXTEND = enum.auto()
+    DECODE = enum.auto()
+
+
+class ReqToTokenPool:
+    """``req_to_token [size, max_context_len] int32``: logical position -> pool row (:599-601)."""
+
+    def __init__(self, size: int, max_context_len: int, device="cuda"):
+        self.size = size
+        self.max_context_len = max_context_len
+        self.req_to_token = torch.zeros((size, max_context_len), dtype=torch.int32, device=device)
+
+
+class TokenToKVPool:
+    """Per-layer K and V buffers ``[size, kv_heads, head_dim]`` (:170, :847-848)."""
+
+    def __init__(self, size: int, dtype: torch.dtype, head_num: int, head_dim: int, layer_num: int,
+                 device="cuda"):
+        self.size = size
+        self.k_buffer = [torch.zeros((size, head_num, head_dim), dtype=dtype, device=device) for _ in range(layer_num)]
+        self.v_buffer = [torch.zeros((size, head_num, head_dim), dtype=dtype, device=device) for _ in range(layer_num)]
+
+    def get_key_buffer(self, layer_id: int) -> torch.Tensor:
+        return self.k_buffer[layer_id]
+
+    def get_value_buffer(self, layer_id: int) -> torch.Tensor:
+        return self.v_buffer[layer_id]
+
+    def get_kv_buffer(self, layer_id: int):
+        return self.k_buffer[layer_id], self.v_buffer[layer_id]
+
+
+class ReqToTokenRetriever:
+    """Per-request selection state, keyed by request id (:117-163).  The reference supports one
+    running request (:130); here every request slot of the batch has its own state."""
+
+    def __init__(self, num_layers, head_dim, num_heads, num_kv_heads, max_num_tokens, dtype,
+                 max_reqs: int = 8, max_batch: int = 8, max_total_tokens: Optional[int] = None,
+                 sm_scale: Optional[float] = None, logit_cap: float = 0.0, tp_rank: int = 0,
+                 tp_size: int = 1, process_group=None, device=None):
+        if TOP_K < 0:
+            raise RuntimeError("call patch(...) before building the model runner")
+        cfg = TokenSelectConfig(
+            rope_base=ROPE_BASE, rope_scale=ROPE_SCALE, rope_model=ROPE_MODE, max_n_tokens=max_num_tokens,
+            top_k=TOP_K, n_init=N_INIT, n_local=N_Local, kernel_size=KERNEL_SIZE, query_cache=QUERY_CACHE,
+            similarity_threshold=SIMILARITY_THRESHOLD, gqa_map=GQA_MAP, n_layers=num_layers,
+            num_q_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, dtype=dtype,
+            sm_scale=sm_scale, logit_cap=logit_cap, max_reqs=max_reqs, max_batch=max_batch,
+            max_total_tokens=max_total_tokens, tp_rank=tp_rank, tp_size=tp_size)
+        self.engine = TokenSelectEngine(cfg, device=device, process_group=process_group)
+
+    def get_token_retriever(self, req_ids: Sequence[object], req_pool_indices: Sequence[int]) -> TokenSelectEngine:
+        """New request id in a slot -> fresh state for that slot (:147-163)."""
+        self.engine.bind_requests(req_ids, req_pool_indices)
+        return self.engine
+
+
+@dataclasses.dataclass
+class InputMetadata:
+    """The fields of the serving stack's batch metadata that the patched forward reads (:519-532)."""
+    forward_mode: ForwardMode
+    batch_size: int
+    req_pool_indices: torch.Tensor        # [batch] int32
+    seq_lens: torch.Tensor                # [batch] int32, counting the token being decoded
+    req_to_token_pool: ReqToTokenPool
+    token_to_kv_pool: TokenToKVPool
+    out_cache_loc: torch.Tensor           # [batch] int32
+    token_retriever: TokenSelectEngine = None
+    seq_lens_cpu: Optional[List[int]] = None   # optional host copy; bounds the tensor-parallel message
+
+
+def patched_radix_attention_forward(self, q, k, v, input_metadata: InputMetadata):
+    """Replacement for ``RadixAttention.forward`` (:827-842).  ``q [batch, heads*head_dim]``,
+    ``k, v [batch, kv_heads*head_dim]`` un-rotated (the patched model skips its own rotary layer,
+    :856-866, :878-881)."""
+    if k is not None:
+        assert v is not None
+        k = k.view(-1, self.tp_k_head_num * self.qk_head_dim)
+        v = v.view(-1, self.tp_v_head_num * self.v_head_dim)
+    if input_metadata.forward_mode == ForwardMode.DECODE:
+        eng = input_metadata.token_retriever
+        k_pool, v_pool = input_metadata.token_to_kv_pool.get_kv_buffer(self.layer_id)
+        ve = None
+        if input_metadata.seq_lens_cpu is not None:
+            ve = eng.vote_elems_for(input_metadata.seq_lens_cpu, eng.cfg.n_init, eng.cfg.n_local)
+        o = eng.decode_layer(
+            self.layer_id, q.contiguous().view(-1, self.tp_q_head_num * self.head_dim),
+            None if k is None else k.contiguous(), None if v is None else v.contiguous(),
+            input_metadata.out_cache_loc, k_pool, v_pool, input_metadata.req_to_token_pool.req_to_token,
+            input_metadata.req_pool_indices, input_metadata.seq_lens, vote_elems=ve)
+        return o.view(-1, self.tp_q_head_num * self.head_dim)
+    raise NotImplementedError(
+        "only ForwardMode.DECODE runs through tokenselect_b200; prefill stays with the serving stack")
+
+
+class RadixAttention:
+    """Attribute surface of the serving stack's attention layer that the patched forward reads
+    (:708, :754-756, :795, :816-819, :832-833)."""
+
+    def __init__(self, num_heads: int, head_dim: int, scaling: float, num_kv_heads: int, layer_id: int,
+                 logit_cap: float = -1):
+        self.tp_q_head_num = num_heads
+        self.tp_k_head_num = num_kv_heads
+        self.tp_v_head_num = num_kv_heads
+        self.head_dim = head_dim
+        self.qk_head_dim = head_dim
+        self.v_head_dim = head_dim
+        self.scaling = scaling
+        self.layer_id = layer_id
+        self.logit_cap = logit_cap if logit_cap is not None and logit_cap > 0 else 0
+        self.sliding_window_size = -1
+
+    forward = patched_radix_attention_forward
+
+    def __call__(self, q, k, v, input_metadata):
+        return self.forward(q, k, v, input_metadata)
