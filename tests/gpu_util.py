@@ -35,8 +35,8 @@ def run_gpu(eng: TokenSelectEngine, layer, q, k_pool, v_pool, rtt, req_idx, seq_
     kp, vp = k_pool.to(dev), v_pool.to(dev)
     out = eng.decode_layer(
         layer, q.to(dev), None if k_new is None else k_new.to(dev), None if v_new is None else v_new.to(dev),
-        None if loc is None else loc.to(dev=dev, dtype=torch.int32), kp, vp, rtt.to(dev),
-        req_idx.to(dev=dev, dtype=torch.int32), seq_lens.to(dev=dev, dtype=torch.int32), debug=dbg)
+        None if loc is None else loc.to(device=dev, dtype=torch.int32), kp, vp, rtt.to(dev),
+        req_idx.to(device=dev, dtype=torch.int32), seq_lens.to(device=dev, dtype=torch.int32), debug=dbg)
     torch.cuda.synchronize()
     eng.raise_on_device_error()
     res = {k: v.cpu() for k, v in dbg.items()}

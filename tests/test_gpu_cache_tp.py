@@ -88,7 +88,7 @@ def test_tensor_parallel_split_on_one_gpu(tp, hq, hkv):
                            query_cache=True) for r in range(tp)]
     dev = engs[0].device
     rtt_d = rtt.to(dev)
-    ridx_d, lens_d = ridx.to(dev=dev, dtype=torch.int32), lens.to(dev=dev, dtype=torch.int32)
+    ridx_d, lens_d = ridx.to(device=dev, dtype=torch.int32), lens.to(device=dev, dtype=torch.int32)
     outs, dbgs, args, keep = [], [], [], []
     for r, e in enumerate(engs):
         qr = q.view(1, hq, d)[:, r * hq_r:(r + 1) * hq_r].reshape(1, -1).contiguous().to(dev)

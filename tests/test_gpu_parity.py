@@ -207,7 +207,7 @@ def test_bad_pool_row_is_reported_not_dereferenced():
     eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, BF16, max_ctx=n + 8)
     dev = eng.device
     eng.decode_layer(0, q.to(dev), None, None, None, kp.to(dev), vp.to(dev), rtt.to(dev),
-                     ridx.to(dev=dev, dtype=torch.int32), lens.to(dev=dev, dtype=torch.int32))
+                     ridx.to(device=dev, dtype=torch.int32), lens.to(device=dev, dtype=torch.int32))
     torch.cuda.synchronize()
     code, detail = eng.last_error()
     assert code == 6 and detail == kp.shape[0] + 123
@@ -223,7 +223,7 @@ def test_workspace_capacity_is_checked_on_the_device():
     eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, BF16, max_ctx=n + 8, max_batch=1, max_total=1024)
     dev = eng.device
     eng.decode_layer(0, q.to(dev), None, None, None, kp.to(dev), vp.to(dev), rtt.to(dev),
-                     ridx.to(dev=dev, dtype=torch.int32), lens.to(dev=dev, dtype=torch.int32))
+                     ridx.to(device=dev, dtype=torch.int32), lens.to(device=dev, dtype=torch.int32))
     torch.cuda.synchronize()
     code, _ = eng.last_error()
     assert code == 4
