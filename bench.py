@@ -1,0 +1,382 @@
+#!/usr/bin/env python
+"""Decode throughput of the token-selection + sparse-attention path at 128K context.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N=1): Llama-3-8B attention shape (32 query / 8 KV heads, head_dim 128, 32 layers), one
+request with 131072 context tokens in a page-size-1 KV pool addressed through a permuted
+``req_to_token`` row, n_init=128, n_local=512, top_k=2048, bf16 K/V ~ N(0,1) with 1 % planted
+outlier tokens and 4 outlier channels x8 (synthetic, generated on the device from a seed).
+One step = one decoded token = the hot path (K/V append, selection, sparse attention) over all 32
+layers through the C ABI.  The model's dense projections lie outside the patched attention forward
+and are not part of the step.
+
+With N > 1 (launched by torch.distributed.run) the same request is sharded by KV head over N ranks
+(tensor parallel): every rank scores its heads, the fp32 vote vector is all-reduced with NCCL, every
+rank runs the same top-k.  Total work is fixed ("strong" scaling).
+
+Prints one JSON line on rank 0 (see the keys below).  ``--impl reference`` times the reference's
+selection + attention arithmetic restated in torch on the host CPU cores (the CPU oracle), one layer
+per step, and reports the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode tok/s at 128K ctx (1-8 GPU); select+attn us/layer vs HBM roofline"
+HQ, HKV, D, LAYERS = 32, 8, 128, 32
+N_INIT, N_LOCAL, TOP_K, ROPE_BASE = 128, 512, 2048, 5e5
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=131072)
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--query-cache", action="store_true", help="selection cache on (threshold 0.9)")
+    ap.add_argument("--contiguous-slots", action="store_true", help="pool rows in position order")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seed", type=int, default=2024)
+    return ap.parse_args()
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons for this rank's GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        try:
+            p = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                  "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                 stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        try:
+            while not self._stop.is_set():
+                line = p.stdout.readline()
+                if not line:
+                    break
+                self.rows.append([x.strip() for x in line.split(",")])
+        finally:
+            p.terminate()
+
+    def start(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+        sm, smax, reasons = [], 0.0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                smax = max(smax, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        busy = [x for x in sm if x >= 0.5 * smax] or sm
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": smax or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------------------------
+def algorithmic_bytes(n_tokens: int, hq: int, hkv: int, d: int) -> dict:
+    """Compulsory bytes of one layer step for one request (bf16): key rows of the candidates, their
+    slot indices, the query and the index list for selection; K and V rows of the selected tokens,
+    their slots, query and output for attention."""
+    nc = n_tokens - N_INIT - N_LOCAL
+    n_sel = N_INIT + TOP_K + N_LOCAL
+    score = nc * hkv * d * 2 + nc * 4 + hq * d * 2
+    sel = score + n_sel * 4
+    attn = 2 * n_sel * hkv * d * 2 + n_sel * 4 + 2 * hq * d * 2
+    return {"score_kernel": score, "select": sel, "attend": attn, "layer": sel + attn}
+
+
+def make_layer_data(gen, dev, rows, ctx, hkv, planted_rows, u):
+    """One layer's K/V pools: N(0,1), 4 outlier channels x8, planted rows aligned with ``u``."""
+    k = torch.randn(rows, hkv, D, generator=gen, device=dev, dtype=torch.float32)
+    v = torch.randn(rows, hkv, D, generator=gen, device=dev, dtype=torch.float32)
+    ch = torch.randperm(D, generator=gen, device=dev)[:4]
+    k[:, :, ch] *= 8
+    v[:, :, ch] *= 8
+    k[planted_rows] += 3.0 * u
+    return k.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def cpu_layer_times(ctx, layers_to_time, seed, threads=None):
+    """Seconds per layer step of the CPU oracle (selection + attention) on this box's host cores,
+    on the same workload shape (all heads, one request of ``ctx`` tokens)."""
+    from oracle import tokenselect_oracle as orc
+    torch.set_num_threads(threads or os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    rows = ctx + 64
+    k = torch.randn(rows, HKV, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(rows, HKV, D, generator=g).to(torch.bfloat16)
+    rtt = torch.zeros(2, ctx + 8, dtype=torch.int32)
+    rtt[1, :ctx] = torch.randperm(rows, generator=g)[:ctx].to(torch.int32)
+    cfg = orc.OracleConfig(1, HQ, HKV, D, N_INIT, N_LOCAL, TOP_K, ROPE_BASE)
+    o = orc.DecodeOracle(cfg)
+    times = []
+    for i in range(layers_to_time + 1):
+        q = torch.randn(1, HQ * D, generator=g).to(torch.bfloat16)
+        t0 = time.perf_counter()
+        o.decode_layer(0, q, None, None, None, k, v, rtt, torch.tensor([1]), torch.tensor([ctx]))
+        dt = time.perf_counter() - t0
+        if i > 0:
+            times.append(dt)
+    return times, torch.get_num_threads()
+
+
+def run_reference(args, rank):
+    """Reference arm: the reference's selection + attention arithmetic on the host CPU (CPU oracle,
+    all host threads).  One step = one layer step; tok/s = 1 / (layers * mean layer seconds)."""
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 24))
+    times, threads = cpu_layer_times(args.ctx, steps, args.seed)
+    mean = sum(times) / len(times)
+    tok_s = 1.0 / (args.layers * mean)
+    sample = f"{len(times)} layer steps of {args.layers} at ctx {args.ctx} (1 warm-up), torch fp32 on bf16 data"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": len(times), "warmup": 1, "ms_per_step": 1e3 * mean * args.layers, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"llama3-8b-shape decode hot path, bs=1, ctx={args.ctx}, {args.layers} layers, "
+                               f"top_k={TOP_K}, n_init={N_INIT}, n_local={N_LOCAL}"},
+        "us_per_layer": 1e6 * mean,
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    tp = world
+    if HKV % tp != 0:
+        raise SystemExit("the KV heads must divide over the ranks")
+
+    import torch.distributed as dist
+    from tokenselect_b200 import TokenSelectConfig, TokenSelectEngine
+    from tokenselect_b200 import build as _build
+    _build.build_library()
+
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if tp > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hq, hkv = HQ // tp, HKV // tp
+    ctx, layers, total_steps = args.ctx, args.layers, args.warmup + args.steps
+    n_sel = N_INIT + TOP_K + N_LOCAL
+    rows = ctx + 2 * total_steps + 64
+    # identical layout on every rank: same seed for the slot map and the planted positions
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    perm = (torch.arange(rows, device=dev) if args.contiguous_slots
+            else torch.randperm(rows, generator=g, device=dev)).to(torch.int32)
+    max_ctx = ctx + 2 * total_steps + 8
+    rtt = torch.zeros(2, max_ctx, dtype=torch.int32, device=dev)
+    rtt[1] = perm[:max_ctx]
+    planted = torch.randperm(ctx - N_INIT - N_LOCAL, generator=g, device=dev)[: ctx // 100] + N_INIT
+    planted_rows = perm[planted].long()
+    gr = torch.Generator(device=dev).manual_seed(args.seed + 17 * (rank + 1))
+    k_pools, v_pools, dirs = [], [], []
+    for _ in range(layers):
+        u = torch.randn(hkv, D, generator=gr, device=dev)
+        u = u / u.norm(dim=-1, keepdim=True)
+        k, v = make_layer_data(gr, dev, rows, ctx, hkv, planted_rows, u)
+        k_pools.append(k)
+        v_pools.append(v)
+        dirs.append(u)
+    # per (step, layer) inputs: queries lean towards the planted direction of their KV head
+    qs = torch.randn(total_steps, layers, hq, D, generator=gr, device=dev)
+    for li in range(layers):
+        kv_of_h = torch.arange(hq, device=dev) % hkv
+        qs[:, li] += 2.0 * (D ** 0.5) * dirs[li][kv_of_h] / 4
+    qs = qs.to(torch.bfloat16).reshape(total_steps, layers, 1, hq * D).contiguous()
+    ks = torch.randn(total_steps, layers, 1, hkv * D, generator=gr, device=dev).to(torch.bfloat16)
+    vs = torch.randn(total_steps, layers, 1, hkv * D, generator=gr, device=dev).to(torch.bfloat16)
+    ridx = torch.tensor([1], dtype=torch.int32, device=dev)
+    lens_all = torch.arange(ctx + 1, ctx + 1 + total_steps, dtype=torch.int32, device=dev).view(-1, 1)
+    locs_all = perm[ctx: ctx + total_steps].view(-1, 1).contiguous()
+    outs = torch.empty(layers, 1, hq * D, dtype=torch.bfloat16, device=dev)
+
+    cfg = TokenSelectConfig(rope_base=ROPE_BASE, max_n_tokens=max_ctx, top_k=TOP_K, n_init=N_INIT, n_local=N_LOCAL,
+                            n_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=D, max_reqs=2, max_batch=1,
+                            max_total_tokens=max_ctx, query_cache=args.query_cache, tp_rank=rank, tp_size=tp)
+    eng = TokenSelectEngine(cfg, device=dev)
+    eng.reset_request(1)
+    ve = eng.vote_elems_for([max_ctx], N_INIT, N_LOCAL)
+
+    def step(i):
+        for li in range(layers):
+            eng.decode_layer(li, qs[i, li], ks[i, li], vs[i, li], locs_all[i], k_pools[li], v_pools[li], rtt, ridx,
+                             lens_all[i], out=outs[li], vote_elems=ve)
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    eng.raise_on_device_error()
+
+    # ---- timed region 1: inputs resident in HBM -------------------------------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = eng.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.warmup, total_steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    launches = eng.launch_count - launches0
+    eng.raise_on_device_error()
+    if tp > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- timed region 2: through the same call with HOST buffers ---------------------------------
+    hq_pin = qs[args.warmup:].cpu().pin_memory()
+    hk_pin = ks[args.warmup:].cpu().pin_memory()
+    hv_pin = vs[args.warmup:].cpu().pin_memory()
+    out_pin = torch.empty(layers, 1, hq * D, dtype=torch.bfloat16).pin_memory()
+    dq, dk, dv = torch.empty_like(qs[0]), torch.empty_like(ks[0]), torch.empty_like(vs[0])
+    # rewind the request: the same tokens are appended again at the same rows
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for j, i in enumerate(range(args.warmup, total_steps)):
+        for li in range(layers):
+            dq[li].copy_(hq_pin[j, li], non_blocking=True)
+            dk[li].copy_(hk_pin[j, li], non_blocking=True)
+            dv[li].copy_(hv_pin[j, li], non_blocking=True)
+            eng.decode_layer(li, dq[li], dk[li], dv[li], locs_all[i], k_pools[li], v_pools[li], rtt, ridx,
+                             lens_all[i], out=outs[li], vote_elems=ve)
+            out_pin[li].copy_(outs[li], non_blocking=True)
+        torch.cuda.current_stream().synchronize()      # the token's result is on the host
+    e3.record()
+    barrier()
+    ms_e2e = e2.elapsed_time(e3)
+    if tp > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    h2d = layers * (hq * D + 2 * hkv * D) * 2
+    d2h = layers * hq * D * 2
+
+    # ---- per-kernel device time (event pair around every kernel; separate pass) ------------------
+    eng.timing_begin(16 * layers * args.steps + 64)
+    for i in range(args.warmup, total_steps):
+        step(i)
+    stages = eng.timing_end()
+    eng.raise_on_device_error()
+
+    if rank == 0:
+        ab = algorithmic_bytes(ctx + args.warmup + args.steps // 2, hq, hkv, D)
+        peak, peak_kind = hbm_peak()
+        # dominant kernel: the fused selection kernel (under tensor parallelism: its two parts)
+        score_ms, score_n = stages["select"]
+        score_ms += stages["select_tp_b"][0]
+        score_us = 1e3 * score_ms / max(score_n, 1)
+        achieved = ab["select"] / (score_us * 1e-6) / 1e9 if score_n else None
+        us_layer = 1e3 * ms / (args.steps * layers)
+        per_stage_us = {k: round(1e3 * v[0] / max(v[1], 1), 3) for k, v in stages.items() if v[1]}
+        line = {
+            "metric": METRIC, "value": args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": tp,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"llama3-8b-shape decode hot path (KV append + token selection + sparse paged "
+                                   f"attention), bs=1, ctx={ctx}, {layers} layers, top_k={TOP_K}, n_init={N_INIT}, "
+                                   f"n_local={N_LOCAL}, page size 1, "
+                                   f"{'contiguous' if args.contiguous_slots else 'permuted'} pool rows, "
+                                   f"query_cache={'on' if args.query_cache else 'off'}",
+                       "parallelism": f"tp{tp} by KV head" if tp > 1 else "single GPU",
+                       "l2": "inputs larger than L2: each layer streams its own 268 MB of keys"},
+            "us_per_layer": us_layer,
+            "layer_roofline": {"bytes": ab["layer"], "achieved_gbs": ab["layer"] / (us_layer * 1e-6) / 1e9,
+                               "frac_of_measured_copy": ab["layer"] / (us_layer * 1e-6) / 1e9 / peak,
+                               "frac_of_8tbs": ab["layer"] / (us_layer * 1e-6) / 1e9 / 8000.0},
+            "kernel_us": per_stage_us,
+            "roofline": {"bound": "hbm", "kernel": "fused_select_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
+                         "peak_source": peak_kind, "bytes_per_launch": ab["select"],
+                         "us_per_launch": score_us, "traffic": None},
+            "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if tp == 1 and not args.no_cpu_baseline:
+            times, threads = cpu_layer_times(ctx, 3, args.seed)
+            mean = sum(times) / len(times)
+            line["cpu_baseline"] = {"value": 1.0 / (layers * mean), "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": f"3 layer steps of {layers} at ctx {ctx} (1 warm-up); "
+                                              f"{mean * 1e3:.1f} ms per layer step"}
+        print(json.dumps(line), flush=True)
+    if tp > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -189,6 +189,19 @@ int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes);
 /* Number of kernels launched by this handle so far. */
 int ts_launch_count(ts_handle* h, uint64_t* launches);
 
+/* Per-kernel device timing with CUDA events recorded on the launching stream around every kernel.
+ * ts_timing_begin() allocates the event pool (up to `max_launches` kernels) and switches recording
+ * on; ts_timing_end() synchronises, switches it off and returns, per stage, the summed device
+ * milliseconds and the number of launches.  Stages: 0 prepare (tensor-parallel form only), 1 the
+ * selection kernel (prepare, score, vote, top-k, emit; or its first part under tensor parallelism),
+ * 2 its second part under tensor parallelism, 3 attend-split, 4 attend-merge, 5-7 unused.  The
+ * reference's counterpart is the
+ * cuda_timer context manager (token_retrieval.py:41-53).  Recording adds an event pair per kernel,
+ * so throughput numbers are taken with it off. */
+#define TS_NUM_STAGES 8
+int ts_timing_begin(ts_handle* h, int32_t max_launches);
+int ts_timing_end(ts_handle* h, double* ms_by_stage, uint64_t* launches_by_stage);
+
 #ifdef __cplusplus
 }
 #endif

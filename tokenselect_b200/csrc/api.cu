@@ -14,13 +14,14 @@ struct ts_handle {
     int n_sel;
     size_t elem;                  // bytes per element of the model dtype
     long long cand_capacity;
-    int score_grid;
+    int grid;
     int attn_chunk_tokens, attn_chunks;
     // one device allocation, carved up
     unsigned char* arena;
     size_t arena_bytes;
     LayerParams base;             // workspace pointers and configuration, call fields empty
     unsigned long long launches;
+    StageTimer timer;
     int last_batch;
     char cuda_msg[256];
 };
@@ -60,7 +61,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     const size_t elem = c->dtype == TS_DTYPE_BF16 ? 2 : 4;
     const int n_sel = c->n_init + c->top_k + c->n_local;
     const long long cap = cand_capacity_of(c);
-    const int grid = score_grid_size(num_sms);
+    const int grid = fused_grid_size(num_sms);
     const size_t hd = (size_t)c->hq * c->head_dim;
     // split the list so that one request's chunks cover the SMs about once
     int ch = (n_sel + num_sms - 1) / num_sms;
@@ -76,7 +77,9 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_votes = cv.take((size_t)cap * 4);
     size_t o_vpool = cv.take(c->kernel_size > 0 ? (size_t)cap * 4 : 16);
     size_t o_hist = cv.take((size_t)c->max_batch * kHistBins * 4);
-    size_t o_bitmap = cv.take((size_t)cap / 8 + 64);
+    size_t o_ccount = cv.take((size_t)c->max_batch * 4);
+    size_t o_sure = cv.take((size_t)c->max_batch * grid * 4);
+    size_t o_bar = cv.take(16);
     size_t o_cand = cv.take((size_t)cap * 8);
     size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
     size_t o_pos = cv.take((size_t)c->max_batch * n_sel * 4);
@@ -104,12 +107,15 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.cos_terms = reinterpret_cast<float*>(a + o_cos);
         p.logits = reinterpret_cast<float*>(a + o_logits);
         p.partials = reinterpret_cast<float2*>(a + o_part);
-        p.score_grid = grid;
+        p.grid = grid;
+        p.tile_tokens = fused_tile_tokens(c->dtype, c->flags, c->hkv, c->head_dim, c->hq / c->hkv);
         p.votes = reinterpret_cast<float*>(a + o_votes);
         p.votes_pool = reinterpret_cast<float*>(a + o_vpool);
         p.votes_sel = c->kernel_size > 0 ? p.votes_pool : p.votes;
         p.hist = reinterpret_cast<unsigned*>(a + o_hist);
-        p.bitmap = reinterpret_cast<unsigned*>(a + o_bitmap);
+        p.cand_count = reinterpret_cast<unsigned*>(a + o_ccount);
+        p.sure_count = reinterpret_cast<unsigned*>(a + o_sure);
+        p.grid_bar = reinterpret_cast<unsigned*>(a + o_bar);
         p.cand = reinterpret_cast<uint2*>(a + o_cand);
         p.sel_slots = reinterpret_cast<int*>(a + o_slots);
         p.sel_pos = reinterpret_cast<int*>(a + o_pos);
@@ -124,7 +130,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.pos_cache = reinterpret_cast<int*>(a + o_pc);
         p.valid = reinterpret_cast<int*>(a + o_valid);
         p.counters = reinterpret_cast<unsigned long long*>(a + o_cnt);
-        h->elem = elem; h->n_sel = n_sel; h->cand_capacity = cap; h->score_grid = grid;
+        h->elem = elem; h->n_sel = n_sel; h->cand_capacity = cap; h->grid = grid;
         h->attn_chunk_tokens = ch; h->attn_chunks = chunks;
     }
     return cv.off;
@@ -169,6 +175,7 @@ int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l) {
     l.dtype = h->cfg.dtype;
     l.flags = h->cfg.flags;
     l.launch_count = &h->launches;
+    l.timer = &h->timer;
     h->last_batch = a->batch;
     return TS_OK;
 }
@@ -267,10 +274,18 @@ int ts_create(const ts_config* cfg, ts_handle** out) {
     return TS_OK;
 }
 
+static void free_timer(ts_handle* h) {
+    for (int i = 0; i < 2 * h->timer.capacity; ++i) cudaEventDestroy(h->timer.events[i]);
+    delete[] h->timer.events;
+    delete[] h->timer.stages;
+    memset(&h->timer, 0, sizeof(h->timer));
+}
+
 int ts_destroy(ts_handle* h) {
     if (!h) return TS_ERR_INVALID_ARG;
     cudaSetDevice(h->cfg.device);
     cudaDeviceSynchronize();
+    free_timer(h);
     cudaFree(h->arena);
     delete h;
     return TS_OK;
@@ -289,7 +304,7 @@ int ts_tp_prepare(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l);
     if (s != TS_OK) return s;
-    TS_TRY(launch_prep(p, l, false), "prep");
+    TS_TRY(launch_prep(p, l), "prepare");
     return TS_OK;
 }
 
@@ -297,9 +312,7 @@ int ts_tp_score_vote(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l);
     if (s != TS_OK) return s;
-    if (p.query_cache) TS_TRY(launch_decide(p, l), "decide");
-    TS_TRY(launch_score(p, l), "score");
-    TS_TRY(launch_vote(p, l, false), "vote");
+    TS_TRY(launch_fused(p, l, kModeTpA), "score+vote");
     return TS_OK;
 }
 
@@ -307,8 +320,7 @@ int ts_tp_select_attend(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l);
     if (s != TS_OK) return s;
-    TS_TRY(launch_pool_hist(p, l), "pool_hist");
-    TS_TRY(launch_select(p, l), "select");
+    TS_TRY(launch_fused(p, l, kModeTpB), "select");
     TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);
 }
@@ -321,12 +333,7 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l);
     if (s != TS_OK) return s;
-    const bool pooled = p.kernel_size > 0;
-    TS_TRY(launch_prep(p, l, true), "prep");
-    TS_TRY(launch_score(p, l), "score");
-    TS_TRY(launch_vote(p, l, !pooled), "vote");
-    if (pooled) TS_TRY(launch_pool_hist(p, l), "pool_hist");
-    TS_TRY(launch_select(p, l), "select");
+    TS_TRY(launch_fused(p, l, kModeAll), "select");
     TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);
 }
@@ -347,7 +354,11 @@ int ts_last_error(ts_handle* h, int32_t* code, int32_t* detail) {
     int v[2] = {0, 0};
     TS_TRY(cudaDeviceSynchronize(), "sync");
     TS_TRY(cudaMemcpy(v, h->base.err, 8, cudaMemcpyDeviceToHost), "read error word");
-    if (v[0] != 0) TS_TRY(cudaMemset(h->base.err, 0, 8), "clear error word");
+    if (v[0] != 0) {
+        TS_TRY(cudaMemset(h->base.err, 0, 8), "clear error word");
+        // a grid barrier that gave up may have left its word mid-count
+        TS_TRY(cudaMemset(h->base.grid_bar, 0, 4), "reset barrier word");
+    }
     if (code) *code = v[0];
     if (detail) *detail = v[1];
     return TS_OK;
@@ -370,6 +381,36 @@ int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes) {
     if (bytes > avail) return TS_ERR_INVALID_ARG;
     TS_TRY(cudaDeviceSynchronize(), "sync");
     TS_TRY(cudaMemcpy(host_dst, src, bytes, cudaMemcpyDeviceToHost), "debug read");
+    return TS_OK;
+}
+
+int ts_timing_begin(ts_handle* h, int32_t max_launches) {
+    if (!h || max_launches < 1) return TS_ERR_INVALID_ARG;
+    if (h->timer.capacity < max_launches) {
+        free_timer(h);
+        h->timer.events = new (std::nothrow) cudaEvent_t[2 * (size_t)max_launches];
+        h->timer.stages = new (std::nothrow) int[max_launches];
+        if (!h->timer.events || !h->timer.stages) return TS_ERR_CUDA;
+        for (int i = 0; i < 2 * max_launches; ++i) TS_TRY(cudaEventCreate(&h->timer.events[i]), "event create");
+        h->timer.capacity = max_launches;
+    }
+    h->timer.used = 0;
+    h->timer.on = 1;
+    return TS_OK;
+}
+
+int ts_timing_end(ts_handle* h, double* ms_by_stage, uint64_t* launches_by_stage) {
+    if (!h || !ms_by_stage || !launches_by_stage) return TS_ERR_INVALID_ARG;
+    h->timer.on = 0;
+    TS_TRY(cudaDeviceSynchronize(), "sync");
+    for (int s = 0; s < TS_NUM_STAGES; ++s) { ms_by_stage[s] = 0.0; launches_by_stage[s] = 0; }
+    for (int i = 0; i < h->timer.used; ++i) {
+        float ms = 0.f;
+        TS_TRY(cudaEventElapsedTime(&ms, h->timer.events[2 * i], h->timer.events[2 * i + 1]), "elapsed");
+        const int s = h->timer.stages[i];
+        if (s >= 0 && s < TS_NUM_STAGES) { ms_by_stage[s] += ms; ++launches_by_stage[s]; }
+    }
+    h->timer.used = 0;
     return TS_OK;
 }
 

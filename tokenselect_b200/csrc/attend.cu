@@ -221,13 +221,15 @@ __global__ void attend_merge_kernel(const LayerParams p) {
 template <typename T, int P>
 static cudaError_t launch_attend_t(const LayerParams& p, const Launch& l) {
     dim3 grid(p.attn_chunks, p.batch);
+    stage_begin(l, kStageAttendSplit);
     if (p.group <= 4) attend_split_kernel<T, P, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
     else attend_split_kernel<T, P, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
-    ++*l.launch_count;
+    stage_end(l);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
+    stage_begin(l, kStageAttendMerge);
     attend_merge_kernel<T><<<dim3(p.hq, p.batch), p.d, 0, l.stream>>>(p);
-    ++*l.launch_count;
+    stage_end(l);
     return cudaGetLastError();
 }
 

@@ -13,9 +13,10 @@ constexpr int kMaxBatch = 256;        // requests per call (plan arrays live in 
 constexpr int kMaxHq = 64;            // query heads per rank
 constexpr int kCandAlign = 128;       // each request's candidate region starts on this multiple
 constexpr int kHistBins = 2048;       // first radix level: vote bits [30:20]
-constexpr int kScoreThreads = 288;    // 1 copy-issuing warp + 8 mma warps
+constexpr int kFusedThreads = 288;    // 1 copy-issuing warp + 8 mma warps
 constexpr int kScoreStages = 5;
 constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stage
+constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
 constexpr int kAttnThreads = 256;
 constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
 
@@ -47,14 +48,17 @@ struct LayerParams {
     int* flags;                // [max_batch] TS_FLAG_*
     float* cos_terms;          // [max_batch, 4] (q.c, |q|^2, |c|^2, -)
     float* logits;             // [cand_capacity, hq]
-    float2* partials;          // [max_batch, score_grid, hq] per-CTA (max, sum exp)
-    int score_grid;
+    float2* partials;          // [max_batch, grid, hq] per-CTA (max, sum exp)
+    int grid;                  // CTAs of the selection kernel (one per SM)
+    int tile_tokens;           // candidates per work tile; fixes which CTA owns which candidates
     float* votes;              // [cand_capacity] head-summed softmax
     float* votes_sel;          // votes the selection reads (== votes, or the pooled copy)
     float* votes_pool;         // [cand_capacity] max-pooled votes
     unsigned* hist;            // [max_batch, kHistBins]
-    unsigned* bitmap;          // [cand_capacity/32] selected-candidate bits
     uint2* cand;               // [cand_capacity] (candidate index, vote bits) of the threshold bin
+    unsigned* cand_count;      // [max_batch] entries of `cand` per request
+    unsigned* sure_count;      // [max_batch, grid] winners above the threshold bin, per CTA
+    unsigned* grid_bar;        // [1] self-resetting grid barrier word
     int* sel_slots;            // [max_batch, n_sel]
     int* sel_pos;              // [max_batch, n_sel]
     int* sel_count;            // [max_batch]
@@ -95,10 +99,20 @@ __host__ __device__ __forceinline__ int pooled_len(int nc, int kernel_size) {
 }
 
 // All threads of the block call this; returns after a __syncthreads().  False means: do nothing.
+// kGuardOnly: derive the flags from the length guard alone (selection cache off) instead of reading
+// the flags a previous phase wrote.
+template <bool kGuardOnly = false>
 __device__ __forceinline__ bool build_plan(const LayerParams& p, Plan& s) {
     for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
         int n = p.seq_lens[b];
-        int f = p.flags[b];
+        int f;
+        if (kGuardOnly) {
+            const int req = p.req_pool_indices[b];
+            const bool bad = n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs;
+            f = (bad || p.n_sel >= n) ? TS_FLAG_DENSE : TS_FLAG_RECOMPUTE;
+        } else {
+            f = __ldcg(p.flags + b);
+        }
         s.n[b] = n;
         s.flag[b] = f;
         s.nc[b] = (f == TS_FLAG_RECOMPUTE) ? (n - p.n_init - p.n_local) : 0;
@@ -147,24 +161,55 @@ __device__ __forceinline__ void ml_merge(float& m, float& l, float mo, float lo)
 }
 
 // host-side launchers, one per translation unit ------------------------------------------------
+// Optional per-kernel event timing (ts_timing_begin / ts_timing_end).
+struct StageTimer {
+    cudaEvent_t* events;       // [2 * capacity] start/stop pairs
+    int* stages;               // [capacity] stage id of each recorded launch
+    int capacity, used, on;
+};
+
 struct Launch {
     cudaStream_t stream;
     int num_sms;
     int dtype;
     unsigned flags;
     unsigned long long* launch_count;
+    StageTimer* timer;
 };
+
+enum Stage { kStagePrep = 0, kStageSelect = 1, kStageSelectTpB = 2, kStageAttendSplit = 3, kStageAttendMerge = 4 };
+
+// Bracket every kernel launch with these two: counts the launch and, when timing is on, records an
+// event pair on the launching stream.
+inline void stage_begin(const Launch& l, int stage) {
+    ++*l.launch_count;
+    StageTimer* t = l.timer;
+    if (t && t->on && t->used < t->capacity) {
+        t->stages[t->used] = stage;
+        cudaEventRecord(t->events[2 * t->used], l.stream);
+    }
+}
+inline void stage_end(const Launch& l) {
+    StageTimer* t = l.timer;
+    if (t && t->on && t->used < t->capacity) {
+        cudaEventRecord(t->events[2 * t->used + 1], l.stream);
+        ++t->used;
+    }
+}
 
 cudaError_t launch_rope_tables(float2* score_cs, float2* attn_cs, int d, int n_rows, double base,
                                double rope_scale, int n_local, cudaStream_t stream);
-cudaError_t launch_prep(const LayerParams& p, const Launch& l, bool fused_decide);
-cudaError_t launch_decide(const LayerParams& p, const Launch& l);
-cudaError_t launch_score(const LayerParams& p, const Launch& l);
-cudaError_t launch_vote(const LayerParams& p, const Launch& l, bool with_hist);
-cudaError_t launch_pool_hist(const LayerParams& p, const Launch& l);
-cudaError_t launch_select(const LayerParams& p, const Launch& l);
+// Phases the selection kernel runs in one launch.
+enum FusedMode {
+    kModeAll = 0,   // prepare, score, vote, top-k, emit (single GPU)
+    kModeTpA = 1,   // decide, score, vote -> raw votes (before the tensor-parallel sum)
+    kModeTpB = 2,   // histogram of the summed votes, top-k, emit
+};
+
+cudaError_t launch_prep(const LayerParams& p, const Launch& l);
+cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode);
 cudaError_t launch_attend(const LayerParams& p, const Launch& l);
-int score_grid_size(int num_sms);
-size_t score_smem_bytes(int hkv);
+int fused_grid_size(int num_sms);
+int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group);
 
 }  // namespace ts

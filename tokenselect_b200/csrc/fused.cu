@@ -1,0 +1,898 @@
+// Token selection of one layer step as ONE persistent kernel (one CTA per SM, cooperative launch):
+//
+//   phase 0  per-request preparation (K/V append, query rotation, selection-cache decision)
+//   phase 1  GQA query.key scoring of the candidate range [n_init, N - n_local) of every request that
+//            recomputes, logits to global memory, per-CTA softmax statistics
+//   phase 2  soft vote: vote[t] = sum_heads softmax_t(logit[h, :])[t], first-level histogram
+//   phase 3  threshold bin of the exact top-k; winners above it counted, members of it listed
+//   phase 4  remaining radix levels on the listed candidates, ordered emission of
+//            init || top-k || local as logical positions and pool rows
+//
+// with a grid-wide barrier between phases.  Every CTA owns one contiguous range of the candidates for
+// all phases, so after scoring a CTA only touches its own logits and votes plus a few small arrays
+// shared through L2.
+//
+// Replaces, from patcher/token_retrieval.py: paged_matmul_kernel / paged_matmul (:166-261) as called
+// from get_topk_tokens (:350-359); softmax + head sum (:361); max_pool1d (:366-369); topk + sort
+// (:371-372); the "+ n_init" shift (:433); init || top-k || local (:436-446); the slot gather (:448);
+// the cached-index reuse (:419) and cache write (:415); get_all_tokens (:329-330) for the dense
+// fallback; and (phase 0) what prep.cuh lists.  The tensor-parallel exchange (:363-364) splits the
+// kernel after phase 2: mode A ends with the raw votes, mode B starts from the summed votes.
+//
+// Scoring, bf16: warp 0 stages the owned part of the request's req_to_token row in shared memory a
+// block at a time and issues one bulk asynchronous copy (TMA engine, mbarrier completion, L2
+// evict-first) per key row of hkv*256 B into a 5-stage shared-memory ring; warps 1..8 each own one
+// (16-token, kv-head) unit of a stage, read it with ldmatrix and multiply it with the head group's
+// queries on mma.sync m16n8k16 (tokens = M, query heads of the group = N <= 8, fp32 accumulate; bf16
+// products are exact in fp32).  Rows are padded by 16 B in shared memory so the eight row addresses of
+// an ldmatrix phase fall into distinct banks.  fp32 check mode (and bf16 on request) scores with plain
+// loads, one warp per candidate.
+//
+// Top-k: radix select on the raw fp32 bit pattern (votes are >= 0, so unsigned order == value
+// order); level 1 is a 2048-bin histogram of bits [30:20]; the candidates inside the threshold bin are
+// resolved by further levels on (low 20 vote bits, inverted index), which makes every key distinct and
+// breaks exact ties in favour of the lowest position.
+//
+// Logits are stored token-major, [candidate][hq], with column c = kv_head*group + j.
+#include <cooperative_groups.h>
+
+#include "prep.cuh"
+
+namespace ts {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kWarps = kFusedThreads / 32;
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kWaitCycles, records TS_ERR_DEVICE_TIMEOUT and lets the caller carry
+// on (control flow stays uniform so no barrier is left short of a participant).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead, int where) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (dead) return;
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 1023u) == 0u) {
+            if (clock64() - t0 > kWaitCycles) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); dead = true; return; }
+            if (*(volatile int*)err != 0) { dead = true; return; }
+        }
+    }
+}
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// One row, global -> shared, completion counted in bytes on an mbarrier; streamed through L2.
+__device__ __forceinline__ void bulk_row_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar), "l"(pol)
+        : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// ------------------------------------------------------------------------------------------
+// shared state
+// ------------------------------------------------------------------------------------------
+struct Seg { int b, t0, t1; };        // candidates [t0, t1) of request b owned by this CTA
+
+struct FusedShared {
+    Plan plan;
+    int tile_off[kMaxBatch + 1];
+    Seg seg[kMaxBatch];
+    int nseg;
+    PrepShared prep;
+    float2 stats[8][8];               // [mma warp][column]
+    float s_m[kMaxHq], s_inv[kMaxHq];
+    unsigned hist[kHistBins];
+    unsigned warp_sum[32];
+    unsigned long long warp_sum64[32];
+    int res_bin;
+    unsigned res_above, res_cnt;
+    unsigned tmp_u[4];
+    unsigned long long full[kScoreStages];
+    unsigned long long empty[kScoreStages];
+    int idx[2][kIdxBlock];
+};
+
+template <int HKV>
+struct ScoreGeom {
+    static constexpr int kTok = kScoreStageUnits / HKV;     // tokens per stage
+    static constexpr int kRowBytes = HKV * 256;             // one key row (all kv heads) in the pool
+    static constexpr int kRowStride = kRowBytes + 16;       // padded row in shared memory
+    static constexpr int kStageBytes = kTok * kRowStride;
+    static constexpr int kRowsPerLane = (kTok + 31) / 32;
+};
+
+// Self-resetting grid barrier (bounded).  Every CTA of the grid must call it the same number of
+// times.  The word returns to its start value once all have arrived: CTA 0 adds 0x80000000-(G-1), the
+// others add 1, and everyone waits for the top bit to flip.
+__device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned expected = gridDim.x;
+        const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (expected - 1u)) : 1u;
+        __threadfence();
+        const unsigned old = atomicAdd(p.grid_bar, add);
+        if (!dead) {
+            const long long t0 = clock64();
+            unsigned spins = 0;
+            while ((((old ^ *(volatile unsigned*)p.grid_bar) & 0x80000000u) == 0u)) {
+                if ((++spins & 255u) == 0u && clock64() - t0 > kWaitCycles) {
+                    set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 10);
+                    dead = true;
+                    break;
+                }
+            }
+        }
+        __threadfence();
+    }
+    __syncthreads();
+}
+
+template <typename U>
+__device__ __forceinline__ U block_inclusive_scan(U v, U* warp_sum) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    U inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        U t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_sum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        U w = lane < kWarps ? warp_sum[lane] : (U)0;
+        U winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            U t = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += t;
+        }
+        warp_sum[lane] = winc - w;    // exclusive prefix of the warp totals
+    }
+    __syncthreads();
+    U r = inc + warp_sum[warp];
+    __syncthreads();
+    return r;
+}
+
+// Given a 2048-bin histogram in shared memory, find the bin holding the k-th largest key (bins
+// counted from the top), the number of keys in higher bins and the bin's own count.
+__device__ __forceinline__ void find_threshold(FusedShared& sh, unsigned k) {
+    const int tid = threadIdx.x;
+    constexpr int kPer = 8;            // 256 threads x 8 bins
+    unsigned c[kPer];
+    unsigned sum = 0;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+        c[j] = tid < kHistBins / kPer ? sh.hist[kHistBins - 1 - (tid * kPer + j)] : 0u;
+        sum += c[j];
+    }
+    const unsigned incl = block_inclusive_scan(sum, sh.warp_sum);
+    unsigned ex = incl - sum;
+    if (ex < k && k <= incl) {
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            if (ex < k && k <= ex + c[j]) {
+                sh.res_bin = kHistBins - 1 - (tid * kPer + j);
+                sh.res_above = ex;
+                sh.res_cnt = c[j];
+            }
+            ex += c[j];
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ unsigned vote_bin(float v) { return (__float_as_uint(v) >> 20) & (kHistBins - 1); }
+
+__device__ __forceinline__ unsigned long long cand_key(uint2 c) {
+    return ((unsigned long long)(c.y & 0xFFFFFu) << 32) | (unsigned long long)(0xFFFFFFFFu - c.x);
+}
+
+__device__ __forceinline__ int checked_slot(const LayerParams& p, const int* row, int pos) {
+    int s = __ldg(row + pos);
+    if ((unsigned long long)(long long)s >= (unsigned long long)p.pool_rows) {
+        set_error(p.err, TS_ERR_BAD_SLOT, s);
+        s = 0;
+    }
+    return s;
+}
+
+// Element e of the rotated, dtype-rounded scoring query of head h (same arithmetic as prep.cuh).
+template <typename T>
+__device__ __forceinline__ T rotated_q(const LayerParams& p, const T* q, int h, int e) {
+    const int half = p.d / 2;
+    const int i = e < half ? e : e - half;
+    const float x1 = to_f32<T>(q[h * p.d + i]);
+    const float x2 = to_f32<T>(q[h * p.d + i + half]);
+    const float2 cs = p.score_cs[i];
+    const float r = e < half ? __fadd_rn(__fmul_rn(x1, cs.x), __fmul_rn(-x2, cs.y))
+                             : __fadd_rn(__fmul_rn(x2, cs.x), __fmul_rn(x1, cs.y));
+    return from_f32<T>(r);
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 1, bf16: TMA ring + mma
+// ------------------------------------------------------------------------------------------
+template <int HKV>
+__device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShared& sh, unsigned char* ring, bool& dead) {
+    using G = ScoreGeom<HKV>;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const uint32_t ring_base = smem_u32(ring);
+    const int cta = blockIdx.x;
+    const int hq = p.hq, group = p.group;
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
+        const uint64_t pol = l2_evict_first_policy();
+        int stage = 0;
+        uint32_t phase = 0;
+        uint32_t issued_mask = 0, last_parity_mask = 0;
+        int buf = 0;
+        for (int s = 0; s < sh.nseg; ++s) {
+            const Seg sg = sh.seg[s];
+            const int* row = p.rtt + (long long)p.req_pool_indices[sg.b] * p.rtt_stride + p.n_init;
+            // index blocks: the next block's loads are in flight while this block's rows are issued
+            int pre[kIdxBlock / 32];
+            auto load_block = [&](int t_begin) {
+#pragma unroll
+                for (int j = 0; j < kIdxBlock / 32; ++j) {
+                    const int t = t_begin + lane + 32 * j;
+                    pre[j] = (t < sg.t1) ? __ldg(row + t) : 0;
+                }
+            };
+            auto store_block = [&](int which) {
+#pragma unroll
+                for (int j = 0; j < kIdxBlock / 32; ++j) {
+                    int v = pre[j];
+                    if ((unsigned long long)(long long)v >= (unsigned long long)p.pool_rows) {
+                        set_error(p.err, TS_ERR_BAD_SLOT, v);
+                        v = 0;
+                    }
+                    sh.idx[which][lane + 32 * j] = v;
+                }
+                __syncwarp();
+            };
+            load_block(sg.t0);
+            store_block(buf);
+            for (int tb0 = sg.t0; tb0 < sg.t1; tb0 += kIdxBlock) {
+                const int tb1 = min(tb0 + kIdxBlock, sg.t1);
+                const bool more = tb1 < sg.t1;
+                if (more) load_block(tb1);
+                for (int t0 = tb0; t0 < tb1; t0 += G::kTok) {
+                    const int ntok = min(G::kTok, sg.t1 - t0);
+                    mbar_wait(smem_u32(&sh.empty[stage]), phase ^ 1u, p.err, dead, 1);
+                    const uint32_t full = smem_u32(&sh.full[stage]);
+                    if (lane == 0) mbar_expect_tx(full, (uint32_t)(ntok * G::kRowBytes));
+                    __syncwarp();
+                    const uint32_t dst0 = ring_base + stage * G::kStageBytes;
+#pragma unroll
+                    for (int j = 0; j < G::kRowsPerLane; ++j) {
+                        const int r = lane + 32 * j;
+                        if (r < ntok) {
+                            const int slot = sh.idx[buf][t0 - tb0 + r];
+                            bulk_row_g2s(dst0 + r * G::kRowStride, kpool + (size_t)slot * G::kRowBytes, G::kRowBytes,
+                                         full, pol);
+                        }
+                    }
+                    issued_mask |= 1u << stage;
+                    last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
+                    if (++stage == kScoreStages) { stage = 0; phase ^= 1u; }
+                }
+                if (more) { buf ^= 1; store_block(buf); }
+            }
+        }
+        // Do not leave the phase while copies into this CTA's shared memory may still be in flight.
+        for (int s = 0; s < kScoreStages; ++s)
+            if (issued_mask & (1u << s))
+                mbar_wait(smem_u32(&sh.full[s]), (last_parity_mask >> s) & 1u, p.err, dead, 2);
+        return;
+    }
+
+    // ---------------- consumers: 8 warps, one (16-token, kv-head) unit each ----------------
+    const int cw = warp - 1;
+    const int ctid = tid - 32;
+    const int kvh = cw % HKV;
+    const int tb = cw / HKV;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    // ldmatrix address of this lane inside a stage: matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15)
+    const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int lk = (lane >> 4) * 8;
+    const uint32_t lane_off = (uint32_t)((tb * 16 + lrow) * G::kRowStride + kvh * 256 + lk * 2);
+
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        // B fragments: column n = g is the g-th query head paired with kv head `kvh`
+        uint32_t bq[16];
+        {
+            const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)sg.b * hq * 128;
+            const int h = (p.gqa_map == TS_GQA_MOD) ? (kvh + HKV * g) : (kvh * group + g);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    uint32_t v = 0u;
+                    if (g < group) {
+                        const int e = ks * 16 + 2 * t4 + 8 * u;
+                        const __nv_bfloat16 lo = rotated_q<__nv_bfloat16>(p, q, h, e);
+                        const __nv_bfloat16 hi = rotated_q<__nv_bfloat16>(p, q, h, e + 1);
+                        v = (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+                    }
+                    bq[2 * ks + u] = v;
+                }
+            }
+        }
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float* lg_base = p.logits + (size_t)sh.plan.off[sg.b] * hq + kvh * group;
+        for (int t0 = sg.t0; t0 < sg.t1; t0 += G::kTok) {
+            const int ntok = min(G::kTok, sg.t1 - t0);
+            mbar_wait(smem_u32(&sh.full[stage]), phase, p.err, dead, 3);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint32_t a_base = ring_base + stage * G::kStageBytes + lane_off;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                ldmatrix_x4(a, a_base + ks * 32);
+                mma_bf16_16816(acc, a, bq[2 * ks], bq[2 * ks + 1]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh.empty[stage]));
+            if (++stage == kScoreStages) { stage = 0; phase ^= 1u; }
+
+            // epilogue: logits out, running (max, sum exp) per column
+            const int r0 = tb * 16 + g, r1 = r0 + 8;
+            const bool v0 = r0 < ntok, v1 = r1 < ntok;
+            float* out0 = lg_base + (size_t)(t0 + r0) * hq;
+            float* out1 = out0 + (size_t)8 * hq;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int c = 2 * t4 + j;
+                if (c < group) {
+                    const float x0 = acc[j], x1 = acc[2 + j];
+                    if (v0) out0[c] = x0;
+                    if (v1) out1[c] = x1;
+                    const float mx = fmaxf(v0 ? x0 : -INFINITY, v1 ? x1 : -INFINITY);
+                    if (mx > -INFINITY) {
+                        const float mn = fmaxf(m[j], mx);
+                        float sum = l[j] * exp2f((m[j] - mn) * kLog2e);
+                        if (v0) sum += exp2f((x0 - mn) * kLog2e);
+                        if (v1) sum += exp2f((x1 - mn) * kLog2e);
+                        l[j] = sum;
+                        m[j] = mn;
+                    }
+                }
+            }
+        }
+        // this CTA's statistics of request sg.b: lanes -> warp -> CTA
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) {
+                float mo = __shfl_xor_sync(0xffffffffu, m[j], o);
+                float lo = __shfl_xor_sync(0xffffffffu, l[j], o);
+                ml_merge(m[j], l[j], mo, lo);
+            }
+        }
+        if (g == 0) {
+            sh.stats[cw][2 * t4] = make_float2(m[0], l[0]);
+            sh.stats[cw][2 * t4 + 1] = make_float2(m[1], l[1]);
+        }
+        consumer_bar();
+        if (ctid < hq) {
+            const int kv = ctid / group, j = ctid - kv * group;
+            float mm = -INFINITY, ll = 0.f;
+            for (int w = kv; w < 8; w += HKV) ml_merge(mm, ll, sh.stats[w][j].x, sh.stats[w][j].y);
+            p.partials[((size_t)sg.b * p.grid + cta) * hq + ctid] = make_float2(mm, ll);
+        }
+        consumer_bar();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 1, plain loads: one warp per candidate.  q_s: rotated queries of the current request (fp32).
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ void score_phase_plain(const LayerParams& p, FusedShared& sh, float* q_s) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int d = p.d, hq = p.hq, hkv = p.hkv, group = p.group;
+    const T* kpool = reinterpret_cast<const T*>(p.k_pool);
+    float* red = reinterpret_cast<float*>(sh.hist);          // [kWarps][hq][2] scratch
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const T* q = reinterpret_cast<const T*>(p.q) + (size_t)sg.b * hq * d;
+        __syncthreads();
+        for (int e = tid; e < hq * d; e += kFusedThreads) q_s[e] = to_f32<T>(rotated_q<T>(p, q, e / d, e % d));
+        __syncthreads();
+        const int* row = p.rtt + (long long)p.req_pool_indices[sg.b] * p.rtt_stride + p.n_init;
+        // lane c (and c + 32) of every warp keeps the running statistics of column c
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        for (int t = sg.t0 + warp; t < sg.t1; t += kWarps) {
+            int slot = __ldg(row + t);
+            if ((unsigned long long)(long long)slot >= (unsigned long long)p.pool_rows) {
+                if (lane == 0) set_error(p.err, TS_ERR_BAD_SLOT, slot);
+                slot = 0;
+            }
+            float* out = p.logits + ((size_t)sh.plan.off[sg.b] + t) * hq;
+            for (int kv = 0; kv < hkv; ++kv) {
+                const T* krow = kpool + ((size_t)slot * hkv + kv) * d;
+                for (int j = 0; j < group; ++j) {
+                    const int h = (p.gqa_map == TS_GQA_MOD) ? (kv + hkv * j) : (kv * group + j);
+                    float acc = 0.f;
+                    for (int e = lane; e < d; e += 32) acc = fmaf(q_s[h * d + e], to_f32<T>(krow[e]), acc);
+#pragma unroll
+                    for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    const int c = kv * group + j;
+                    if (lane == 0) out[c] = acc;
+                    if (lane == (c & 31)) {
+                        const int u = c >> 5;
+                        const float mn = fmaxf(m[u], acc);
+                        l[u] = l[u] * exp2f((m[u] - mn) * kLog2e) + exp2f((acc - mn) * kLog2e);
+                        m[u] = mn;
+                    }
+                }
+            }
+        }
+        for (int u = 0; u < 2; ++u) {
+            const int c = lane + 32 * u;
+            if (c < hq) { red[(warp * hq + c) * 2] = m[u]; red[(warp * hq + c) * 2 + 1] = l[u]; }
+        }
+        __syncthreads();
+        if (tid < hq) {
+            float mm = -INFINITY, ll = 0.f;
+            for (int w = 0; w < kWarps; ++w) ml_merge(mm, ll, red[(w * hq + tid) * 2], red[(w * hq + tid) * 2 + 1]);
+            p.partials[((size_t)sg.b * p.grid + blockIdx.x) * hq + tid] = make_float2(mm, ll);
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 2: votes of the owned candidates (+ histogram)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void flush_hist(const LayerParams& p, FusedShared& sh, int b) {
+    __syncthreads();
+    unsigned* gh = p.hist + (size_t)b * kHistBins;
+    for (int i = threadIdx.x; i < kHistBins; i += kFusedThreads) {
+        const unsigned c = sh.hist[i];
+        if (c) { atomicAdd(gh + i, c); sh.hist[i] = 0u; }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh, bool with_hist) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hq = p.hq;
+    for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        __syncthreads();
+        // softmax statistics of the request: merge every CTA's (max, sum exp); one warp per head
+        for (int c = warp; c < hq; c += kWarps) {
+            float m = -INFINITY, l = 0.f;
+            for (int i = lane; i < p.grid; i += 32) {
+                const float2 v = __ldcg(p.partials + ((size_t)sg.b * p.grid + i) * hq + c);
+                ml_merge(m, l, v.x, v.y);
+            }
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) {
+                float mo = __shfl_xor_sync(0xffffffffu, m, o);
+                float lo = __shfl_xor_sync(0xffffffffu, l, o);
+                ml_merge(m, l, mo, lo);
+            }
+            if (lane == 0) { sh.s_m[c] = m; sh.s_inv[c] = 1.f / l; }
+        }
+        __syncthreads();
+        const float* lg = p.logits + (size_t)sh.plan.off[sg.b] * hq;
+        float* votes = p.votes + sh.plan.off[sg.b];
+        for (int t = sg.t0 + tid; t < sg.t1; t += kFusedThreads) {
+            const float* row = lg + (size_t)t * hq;
+            float v = 0.f;
+            if ((hq & 3) == 0) {
+                for (int c = 0; c < hq; c += 4) {
+                    const float4 x = __ldcg(reinterpret_cast<const float4*>(row + c));
+                    v += exp2f((x.x - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
+                    v += exp2f((x.y - sh.s_m[c + 1]) * kLog2e) * sh.s_inv[c + 1];
+                    v += exp2f((x.z - sh.s_m[c + 2]) * kLog2e) * sh.s_inv[c + 2];
+                    v += exp2f((x.w - sh.s_m[c + 3]) * kLog2e) * sh.s_inv[c + 3];
+                }
+            } else {
+                for (int c = 0; c < hq; ++c) v += exp2f((__ldcg(row + c) - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
+            }
+            votes[t] = v;
+            if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+        }
+        if (with_hist) flush_hist(p, sh, sg.b);
+    }
+}
+
+// Votes the selection reads for candidate t of a segment: the raw vote, or the sliding maximum over
+// [t - pad, t - pad + K - 1] clipped to the request (window K, padding (K-1)/2, stride 1).
+__device__ __forceinline__ float sel_vote(const LayerParams& p, const float* votes, int t, int nc) {
+    const int K = p.kernel_size;
+    if (K <= 0) return __ldcg(votes + t);
+    const int pad = (K - 1) / 2;
+    const int lo = max(t - pad, 0), hi = min(t - pad + K - 1, nc - 1);
+    float v = __ldcg(votes + lo);
+    for (int j = lo + 1; j <= hi; ++j) v = fmaxf(v, __ldcg(votes + j));
+    return v;
+}
+
+// phase 2': histogram from final votes (after a tensor-parallel sum and/or max-pool); pooled votes
+// are also written out for inspection.
+__device__ __forceinline__ void hist_phase(const LayerParams& p, FusedShared& sh) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
+    __syncthreads();
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const int nc = sh.plan.nc[sg.b];
+        const int ne = pooled_len(nc, p.kernel_size);
+        const float* votes = p.votes + sh.plan.off[sg.b];
+        for (int t = sg.t0 + tid; t < min(sg.t1, ne); t += kFusedThreads) {
+            const float v = sel_vote(p, votes, t, nc);
+            if (p.kernel_size > 0) p.votes_pool[sh.plan.off[sg.b] + t] = v;
+            atomicAdd(&sh.hist[vote_bin(v)], 1u);
+        }
+        flush_hist(p, sh, sg.b);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 3: threshold bin; count the sure winners, list the threshold bin's members
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void load_threshold(const LayerParams& p, FusedShared& sh, int b) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kHistBins; i += kFusedThreads) sh.hist[i] = __ldcg(p.hist + (size_t)b * kHistBins + i);
+    __syncthreads();
+    find_threshold(sh, (unsigned)p.top_k);
+}
+
+__device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& sh) {
+    const int tid = threadIdx.x;
+    // requests this CTA owns nothing of still need a zero in their per-CTA winner count
+    for (int b = tid; b < p.batch; b += kFusedThreads)
+        if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE) p.sure_count[(size_t)b * p.grid + blockIdx.x] = 0u;
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        load_threshold(p, sh, sg.b);
+        const unsigned b1 = (unsigned)sh.res_bin;
+        const int nc = sh.plan.nc[sg.b];
+        const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
+        const float* votes = p.votes + sh.plan.off[sg.b];
+        uint2* cand = p.cand + sh.plan.off[sg.b];
+        // pass 1: counts
+        unsigned sure = 0, eq = 0;
+        for (int t = sg.t0 + tid; t < t1; t += kFusedThreads) {
+            const unsigned bin = vote_bin(sel_vote(p, votes, t, nc));
+            sure += bin > b1;
+            eq += bin == b1;
+        }
+        const unsigned long long packed =
+            block_inclusive_scan(((unsigned long long)sure << 32) | eq, sh.warp_sum64);
+        if (tid == kFusedThreads - 1) {
+            sh.tmp_u[0] = (unsigned)(packed >> 32);
+            sh.tmp_u[1] = (unsigned)packed;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            p.sure_count[(size_t)sg.b * p.grid + blockIdx.x] = sh.tmp_u[0];
+            sh.tmp_u[2] = sh.tmp_u[1] ? atomicAdd(p.cand_count + sg.b, sh.tmp_u[1]) : 0u;
+        }
+        __syncthreads();
+        // pass 2: append this CTA's members of the threshold bin (order inside the list is free)
+        unsigned at = sh.tmp_u[2] + (unsigned)packed - eq;
+        if (sh.tmp_u[1]) {
+            for (int t = sg.t0 + tid; t < t1; t += kFusedThreads) {
+                const float v = sel_vote(p, votes, t, nc);
+                if (vote_bin(v) == b1) cand[at++] = make_uint2((unsigned)t, __float_as_uint(v));
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 4: remaining radix levels (every CTA for itself), ordered emission
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh) {
+    const int tid = threadIdx.x;
+    const int k = p.top_k;
+    // windows, dense requests and cached index sets: request b is handled by CTA b % grid
+    for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+        const int n = sh.plan.n[b];
+        const int flag = sh.plan.flag[b];
+        const int req = p.req_pool_indices[b];
+        if (n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs) {
+            if (tid == 0) p.sel_count[b] = 0;
+            continue;
+        }
+        const int* row = p.rtt + (long long)req * p.rtt_stride;
+        int* out_slots = p.sel_slots + (size_t)b * p.n_sel;
+        int* out_pos = p.sel_pos + (size_t)b * p.n_sel;
+        if (flag == TS_FLAG_DENSE) {                       // every token, position order (:329-330)
+            for (int i = tid; i < n; i += kFusedThreads) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
+            if (tid == 0) p.sel_count[b] = n;
+            continue;
+        }
+        for (int i = tid; i < p.n_init; i += kFusedThreads) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
+        for (int i = tid; i < p.n_local; i += kFusedThreads) {   // (:438-444)
+            const int pos = n - p.n_local + i;
+            out_pos[p.n_init + k + i] = pos;
+            out_slots[p.n_init + k + i] = checked_slot(p, row, pos);
+        }
+        if (tid == 0) p.sel_count[b] = p.n_sel;
+        if (flag == TS_FLAG_REUSE) {                       // cached positions (:419)
+            const int* cache_pos = p.pos_cache + ((size_t)req * p.n_layers + p.layer) * k;
+            for (int i = tid; i < k; i += kFusedThreads) {
+                const int pos = cache_pos[i];
+                out_pos[p.n_init + i] = pos;
+                out_slots[p.n_init + i] = checked_slot(p, row, pos);
+            }
+        }
+    }
+
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const int req = p.req_pool_indices[sg.b];
+        load_threshold(p, sh, sg.b);
+        const unsigned b1 = (unsigned)sh.res_bin;
+        const unsigned k1 = (unsigned)k - sh.res_above;    // still to take from the threshold bin
+        const unsigned n_c = __ldcg(p.cand_count + sg.b);
+        if (n_c != sh.res_cnt && tid == 0) set_error(p.err, TS_ERR_INTERNAL, (int)n_c);
+        const uint2* cand = p.cand + sh.plan.off[sg.b];
+
+        // further levels on (low 20 vote bits | inverted index): 10, 10, 11, 11, 10 bits from the top
+        unsigned long long prefix = 0ull, mask_above = 0ull;
+        unsigned k_rem = k1, active = n_c;
+        const int shifts[5] = {42, 32, 21, 10, 0};
+        const unsigned widths[5] = {10, 10, 11, 11, 10};
+#pragma unroll 1
+        for (int lv = 0; lv < 5; ++lv) {
+            if (k_rem >= active) break;                    // everything still active is taken
+            __syncthreads();
+            for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
+            __syncthreads();
+            const unsigned long long dmask = (1ull << widths[lv]) - 1ull;
+            for (unsigned i = tid; i < n_c; i += kFusedThreads) {
+                const unsigned long long key = cand_key(__ldcg(cand + i));
+                if ((key & mask_above) == prefix) atomicAdd(&sh.hist[(unsigned)((key >> shifts[lv]) & dmask)], 1u);
+            }
+            __syncthreads();
+            find_threshold(sh, k_rem);
+            prefix |= (unsigned long long)(unsigned)sh.res_bin << shifts[lv];
+            mask_above |= dmask << shifts[lv];
+            k_rem -= sh.res_above;
+            active = sh.res_cnt;
+        }
+
+        // winners before this CTA's range: sure winners of lower CTAs + winning candidates below t0
+        unsigned before = 0;
+        for (int c = tid; c < (int)blockIdx.x; c += kFusedThreads) before += __ldcg(p.sure_count + (size_t)sg.b * p.grid + c);
+        for (unsigned i = tid; i < n_c; i += kFusedThreads) {
+            const uint2 c = __ldcg(cand + i);
+            if ((int)c.x < sg.t0 && (cand_key(c) & mask_above) >= prefix) ++before;
+        }
+        const unsigned before_all = block_inclusive_scan(before, sh.warp_sum);
+        if (tid == kFusedThreads - 1) sh.tmp_u[3] = before_all;
+        __syncthreads();
+        unsigned base = sh.tmp_u[3];
+
+        // ordered emission of the owned range, kFusedThreads candidates at a time
+        const int nc = sh.plan.nc[sg.b];
+        const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
+        const float* votes = p.votes + sh.plan.off[sg.b];
+        const int* row = p.rtt + (long long)req * p.rtt_stride;
+        int* out_slots = p.sel_slots + (size_t)sg.b * p.n_sel;
+        int* out_pos = p.sel_pos + (size_t)sg.b * p.n_sel;
+        int* cache_pos = p.pos_cache + ((size_t)req * p.n_layers + p.layer) * k;
+        for (int c0 = sg.t0; c0 < t1; c0 += kFusedThreads) {
+            const int t = c0 + tid;
+            unsigned sel = 0;
+            if (t < t1) {
+                const float v = sel_vote(p, votes, t, nc);
+                const unsigned bin = vote_bin(v);
+                if (bin > b1) sel = 1;
+                else if (bin == b1)
+                    sel = (cand_key(make_uint2((unsigned)t, __float_as_uint(v))) & mask_above) >= prefix;
+            }
+            const unsigned incl = block_inclusive_scan(sel, sh.warp_sum);
+            if (sel) {
+                const unsigned rank = base + incl - 1;
+                if (rank < (unsigned)k) {
+                    const int pos = p.n_init + t;
+                    out_pos[p.n_init + rank] = pos;
+                    out_slots[p.n_init + rank] = checked_slot(p, row, pos);
+                    if (p.query_cache) cache_pos[rank] = pos;      // topk_indices_cache[layer] = ... (:415)
+                } else {
+                    set_error(p.err, TS_ERR_INTERNAL, (int)rank);
+                }
+            }
+            if (tid == kFusedThreads - 1) sh.tmp_u[3] = base + incl;
+            __syncthreads();
+            base = sh.tmp_u[3];
+        }
+        // the CTA owning the request's last candidates checks the total
+        if (sg.t1 >= nc && tid == 0 && base != (unsigned)k) set_error(p.err, TS_ERR_INTERNAL, (int)base);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// the kernel
+// ------------------------------------------------------------------------------------------
+// HKV > 0: bf16 TMA + mma scoring for that many local KV heads; HKV == 0: plain-load scoring.
+template <typename T, int HKV>
+__global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const LayerParams p, const int mode) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ FusedShared sh;
+    const int tid = threadIdx.x;
+    bool dead = false;
+
+    // ---- phase 0 ----
+    bool ok = *(volatile int*)p.err == 0;
+    const bool need_flags_barrier = p.query_cache != 0;
+    if (mode != kModeTpB) {
+        if (ok) {
+            for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+                if (mode == kModeAll) prepare_request<T, true>(p, b, sh.prep);
+                else if (p.query_cache) decide_request<T>(p, b, sh.prep);
+            }
+        }
+        if (need_flags_barrier) grid_barrier(p, dead);
+    }
+    // Flags: from the length guard alone when the selection cache is off (nothing to wait for).
+    if (need_flags_barrier || mode == kModeTpB) ok = build_plan<false>(p, sh.plan) && ok;
+    else ok = build_plan<true>(p, sh.plan) && ok;
+
+    // ---- ownership: contiguous tile range per CTA ----
+    if (tid == 0) {
+        const int tt = p.tile_tokens;
+        int acc = 0;
+        for (int b = 0; b < p.batch; ++b) { sh.tile_off[b] = acc; acc += (sh.plan.nc[b] + tt - 1) / tt; }
+        sh.tile_off[p.batch] = acc;
+        const long long total = acc;
+        const int lo = (int)(total * blockIdx.x / gridDim.x), hi = (int)(total * (blockIdx.x + 1) / gridDim.x);
+        int ns = 0;
+        for (int b = 0; b < p.batch && ok; ++b) {
+            const int a0 = max(lo, sh.tile_off[b]), a1 = min(hi, sh.tile_off[b + 1]);
+            if (a0 < a1) {
+                sh.seg[ns].b = b;
+                sh.seg[ns].t0 = (a0 - sh.tile_off[b]) * tt;
+                sh.seg[ns].t1 = min(sh.plan.nc[b], (a1 - sh.tile_off[b]) * tt);
+                ++ns;
+            }
+        }
+        sh.nseg = ns;
+        if (HKV > 0) {
+            for (int s = 0; s < kScoreStages; ++s) {
+                mbar_init(smem_u32(&sh.full[s]), 1);
+                mbar_init(smem_u32(&sh.empty[s]), 8);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    __syncthreads();
+
+    const bool pooled = p.kernel_size > 0;
+    if (mode != kModeTpB) {
+        // ---- phase 1: score ----
+        if (ok) {
+            // a CTA without candidates of request b still owes (-inf, 0) statistics for it
+            for (int i = tid; i < p.batch * p.hq; i += kFusedThreads) {
+                const int b = i / p.hq, c = i - b * p.hq;
+                bool mine = false;
+                for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
+                if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
+                    p.partials[((size_t)b * p.grid + blockIdx.x) * p.hq + c] = make_float2(-INFINITY, 0.f);
+            }
+            if constexpr (HKV > 0) score_phase_tma<HKV>(p, sh, ring, dead);
+            else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
+        }
+        grid_barrier(p, dead);
+        // ---- phase 2: votes ----
+        if (ok) vote_phase(p, sh, mode == kModeAll && !pooled);
+        if (mode == kModeTpA) return;
+        if (pooled) {
+            grid_barrier(p, dead);
+            if (ok) hist_phase(p, sh);
+        }
+    } else {
+        if (ok) hist_phase(p, sh);
+    }
+    grid_barrier(p, dead);
+    // ---- phase 3 ----
+    if (ok) filter_phase(p, sh);
+    grid_barrier(p, dead);
+    // ---- phase 4 ----
+    if (ok) emit_phase(p, sh);
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+int fused_grid_size(int num_sms) { return num_sms; }
+
+static bool use_tma(int dtype, unsigned flags, int hkv, int d, int group) {
+    return dtype == TS_DTYPE_BF16 && !(flags & TS_CFG_PLAIN_SCORE) && d == 128 && group <= 8 &&
+           (hkv == 1 || hkv == 2 || hkv == 4 || hkv == 8);
+}
+
+int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group) {
+    return use_tma(dtype, flags, hkv, d, group) ? kScoreStageUnits / hkv : 16;
+}
+
+template <typename T, int HKV>
+static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mode, size_t smem) {
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(fused_select_kernel<T, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    LayerParams pp = p;
+    int m = mode;
+    void* args[] = {&pp, &m};
+    stage_begin(l, mode == kModeTpB ? kStageSelectTpB : kStageSelect);
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fused_select_kernel<T, HKV>), dim3(p.grid),
+                                                dim3(kFusedThreads), args, smem, l.stream);
+    stage_end(l);
+    return e;
+}
+
+cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode) {
+    if (use_tma(l.dtype, l.flags, p.hkv, p.d, p.group)) {
+        switch (p.hkv) {
+            case 1: return launch_fused_t<__nv_bfloat16, 1>(p, l, mode, (size_t)kScoreStages * ScoreGeom<1>::kStageBytes);
+            case 2: return launch_fused_t<__nv_bfloat16, 2>(p, l, mode, (size_t)kScoreStages * ScoreGeom<2>::kStageBytes);
+            case 4: return launch_fused_t<__nv_bfloat16, 4>(p, l, mode, (size_t)kScoreStages * ScoreGeom<4>::kStageBytes);
+            default: return launch_fused_t<__nv_bfloat16, 8>(p, l, mode, (size_t)kScoreStages * ScoreGeom<8>::kStageBytes);
+        }
+    }
+    const size_t smem = (size_t)p.hq * p.d * sizeof(float);
+    if (l.dtype == TS_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, 0>(p, l, mode, smem);
+    return launch_fused_t<float, 0>(p, l, mode, smem);
+}
+
+}  // namespace ts

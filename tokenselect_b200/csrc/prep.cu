@@ -1,10 +1,6 @@
-// Per-request preparation of one layer step: K/V append, scoring-query rotation, cosine terms of
-// the selection cache and the recompute / reuse / dense decision.
-//
-// Replaces store_kv_cache (token_retrieval.py:844-854), the query rotation at :380-388 with
-// RotaryEmbedding.apply_rotary_pos_emb (:98-107), the guard at :376-378 and the (intended)
-// selection-cache rule at :394-421.
-#include "common.cuh"
+// Rotation tables and the stand-alone prepare kernel of the tensor-parallel form (the cosine terms
+// it publishes are summed over ranks before the decision).  See prep.cuh.
+#include "prep.cuh"
 
 namespace ts {
 
@@ -35,177 +31,20 @@ cudaError_t launch_rope_tables(float2* score_cs, float2* attn_cs, int d, int n_r
     return cudaGetLastError();
 }
 
-// Decision for one request given the three cosine terms.  Thread 0 of the block calls it.
-template <typename T>
-__device__ __forceinline__ int decide(const LayerParams& p, int b, int req, float dot, float qq, float cc) {
-    int flag = TS_FLAG_RECOMPUTE;
-    if (p.query_cache) {
-        int* valid = p.valid + (size_t)req * p.n_layers + p.layer;
-        bool recompute = true;
-        if (*valid) {
-            // cos = dot / (sqrt(qq) * sqrt(cc)), every operation rounded to fp32
-            float den = __fmul_rn(__fsqrt_rn(qq), __fsqrt_rn(cc));
-            float c = (den == 0.f) ? 0.f : __fdiv_rn(dot, den);
-            recompute = c < p.theta;                       // strict <, :397-400
-        }
-        flag = recompute ? TS_FLAG_RECOMPUTE : TS_FLAG_REUSE;
-        atomicAdd(p.counters + 2 * (size_t)req, 1ULL);     // retrieval_count, :421
-        if (!recompute) atomicAdd(p.counters + 2 * (size_t)req + 1, 1ULL);  // skip_count, :420
-        if (recompute) *valid = 1;                         // is_first_query = False, :417
-    }
-    return flag;
-}
-
 // grid = batch, block = 256.
-template <typename T, bool kFusedDecide>
-__global__ void __launch_bounds__(256) prep_kernel(const LayerParams p) {
-    const int b = blockIdx.x;
-    const int tid = threadIdx.x;
-    __shared__ int s_flag;
-    __shared__ float s_terms[3];
-    if (*(volatile int*)p.err != 0) return;
-
-    const int n = p.seq_lens[b];
-    const int req = p.req_pool_indices[b];
-    const int hd = p.hq * p.d;
-    if (n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs) {
-        if (tid == 0) { set_error(p.err, TS_ERR_BAD_LENGTH, n); p.flags[b] = TS_FLAG_DENSE; }
-        return;
-    }
-
-    // 1. append this step's K/V rows to the pools (:849-850)
-    if (p.k_new != nullptr) {
-        int loc = p.out_cache_loc[b];
-        if (loc < 0 || loc >= p.pool_rows) {
-            if (tid == 0) { set_error(p.err, TS_ERR_BAD_SLOT, loc); p.flags[b] = TS_FLAG_DENSE; }
-            return;
-        }
-        const int row_vec = p.hkv * p.d * (int)sizeof(T) / 16;
-        const uint4* ks = reinterpret_cast<const uint4*>(p.k_new) + (size_t)b * row_vec;
-        const uint4* vs = reinterpret_cast<const uint4*>(p.v_new) + (size_t)b * row_vec;
-        uint4* kd = reinterpret_cast<uint4*>(p.k_pool) + (size_t)loc * row_vec;
-        uint4* vd = reinterpret_cast<uint4*>(p.v_pool) + (size_t)loc * row_vec;
-        for (int i = tid; i < row_vec; i += blockDim.x) { kd[i] = ks[i]; vd[i] = vs[i]; }
-    }
-
-    // 2. clear this request's first-level histogram
-    for (int i = tid; i < kHistBins; i += blockDim.x) p.hist[(size_t)b * kHistBins + i] = 0u;
-
-    // 3. guard (:376-378): short requests attend to everything
-    if (p.n_sel >= n) {
-        if (tid == 0) p.flags[b] = TS_FLAG_DENSE;
-        return;
-    }
-
-    // 4. rotate the scoring query at the fixed position and round to the model dtype (:98-107).
-    //    out[i] = x[i]*cos + (-x[i+d/2])*sin ; out[i+d/2] = x[i+d/2]*cos + x[i]*sin, each product and
-    //    the sum rounded separately, as eager tensor arithmetic does.
-    const T* q = reinterpret_cast<const T*>(p.q) + (size_t)b * hd;
-    T* qr = reinterpret_cast<T*>(p.q_rot) + (size_t)b * hd;
-    const int half = p.d / 2;
-    for (int e = tid; e < p.hq * half; e += blockDim.x) {
-        int h = e / half, i = e % half;
-        float x1 = to_f32<T>(q[h * p.d + i]);
-        float x2 = to_f32<T>(q[h * p.d + i + half]);
-        float2 cs = p.score_cs[i];
-        float r1 = __fadd_rn(__fmul_rn(x1, cs.x), __fmul_rn(-x2, cs.y));
-        float r2 = __fadd_rn(__fmul_rn(x2, cs.x), __fmul_rn(x1, cs.y));
-        qr[h * p.d + i] = from_f32<T>(r1);
-        qr[h * p.d + i + half] = from_f32<T>(r2);
-    }
-    __syncthreads();
-
-    // 5. cosine terms against the cached query in a fixed order: lane j sums elements j + 32*i in
-    //    ascending i, then an XOR butterfly (16, 8, 4, 2, 1) joins the 32 partial sums.
-    const T* fp = reinterpret_cast<const T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
-    if (p.query_cache && tid < 32) {
-        float dot = 0.f, qq = 0.f, cc = 0.f;
-        const bool have = p.valid[(size_t)req * p.n_layers + p.layer] != 0;
-        if (have) {
-            for (int e = tid; e < hd; e += 32) {
-                float a = to_f32<T>(qr[e]);
-                float c = to_f32<T>(fp[e]);
-                dot = __fadd_rn(dot, __fmul_rn(a, c));
-                qq = __fadd_rn(qq, __fmul_rn(a, a));
-                cc = __fadd_rn(cc, __fmul_rn(c, c));
-            }
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                dot = __fadd_rn(dot, __shfl_xor_sync(0xffffffffu, dot, o));
-                qq = __fadd_rn(qq, __shfl_xor_sync(0xffffffffu, qq, o));
-                cc = __fadd_rn(cc, __shfl_xor_sync(0xffffffffu, cc, o));
-            }
-        }
-        if (tid == 0) {
-            s_terms[0] = dot; s_terms[1] = qq; s_terms[2] = cc;
-            if (!kFusedDecide) {
-                p.cos_terms[4 * b + 0] = dot; p.cos_terms[4 * b + 1] = qq;
-                p.cos_terms[4 * b + 2] = cc;  p.cos_terms[4 * b + 3] = 0.f;
-            }
-        }
-    }
-    if (!kFusedDecide) {
-        if (tid == 0) p.flags[b] = TS_FLAG_RECOMPUTE;   // provisional: decide_kernel overwrites it
-        return;
-    }
-    __syncthreads();
-
-    // 6. decision and cache update (:395-421)
-    if (tid == 0) {
-        int f = decide<T>(p, b, req, s_terms[0], s_terms[1], s_terms[2]);
-        p.flags[b] = f;
-        s_flag = f;
-    }
-    __syncthreads();
-    if (p.query_cache && s_flag == TS_FLAG_RECOMPUTE) {    // query_fingerprints_cache[layer] = q (:416)
-        T* fpw = reinterpret_cast<T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
-        for (int e = tid; e < hd; e += blockDim.x) fpw[e] = qr[e];
-    }
-}
-
-// Tensor-parallel form: the cosine terms were summed over ranks by the caller.
 template <typename T>
-__global__ void __launch_bounds__(256) decide_kernel(const LayerParams p) {
-    const int b = blockIdx.x;
-    const int tid = threadIdx.x;
-    __shared__ int s_flag;
+__global__ void __launch_bounds__(256) prep_kernel(const LayerParams p) {
+    __shared__ PrepShared ps;
     if (*(volatile int*)p.err != 0) return;
-    const int n = p.seq_lens[b];
-    const int req = p.req_pool_indices[b];
-    if (n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs) return;
-    if (p.n_sel >= n) return;                              // prep already wrote TS_FLAG_DENSE
-    const int hd = p.hq * p.d;
-    if (tid == 0) {
-        int f = decide<T>(p, b, req, p.cos_terms[4 * b], p.cos_terms[4 * b + 1], p.cos_terms[4 * b + 2]);
-        p.flags[b] = f;
-        s_flag = f;
-    }
-    __syncthreads();
-    if (p.query_cache && s_flag == TS_FLAG_RECOMPUTE) {
-        const T* qr = reinterpret_cast<const T*>(p.q_rot) + (size_t)b * hd;
-        T* fpw = reinterpret_cast<T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
-        for (int e = tid; e < hd; e += blockDim.x) fpw[e] = qr[e];
-    }
+    prepare_request<T, false>(p, blockIdx.x, ps);
 }
 
-cudaError_t launch_prep(const LayerParams& p, const Launch& l, bool fused_decide) {
+cudaError_t launch_prep(const LayerParams& p, const Launch& l) {
     dim3 grid(p.batch), block(256);
-    if (l.dtype == TS_DTYPE_BF16) {
-        if (fused_decide) prep_kernel<__nv_bfloat16, true><<<grid, block, 0, l.stream>>>(p);
-        else prep_kernel<__nv_bfloat16, false><<<grid, block, 0, l.stream>>>(p);
-    } else {
-        if (fused_decide) prep_kernel<float, true><<<grid, block, 0, l.stream>>>(p);
-        else prep_kernel<float, false><<<grid, block, 0, l.stream>>>(p);
-    }
-    ++*l.launch_count;
-    return cudaGetLastError();
-}
-
-cudaError_t launch_decide(const LayerParams& p, const Launch& l) {
-    dim3 grid(p.batch), block(256);
-    if (l.dtype == TS_DTYPE_BF16) decide_kernel<__nv_bfloat16><<<grid, block, 0, l.stream>>>(p);
-    else decide_kernel<float><<<grid, block, 0, l.stream>>>(p);
-    ++*l.launch_count;
+    stage_begin(l, kStagePrep);
+    if (l.dtype == TS_DTYPE_BF16) prep_kernel<__nv_bfloat16><<<grid, block, 0, l.stream>>>(p);
+    else prep_kernel<float><<<grid, block, 0, l.stream>>>(p);
+    stage_end(l);
     return cudaGetLastError();
 }
 

@@ -184,6 +184,19 @@ class TokenSelectEngine:
         check(self.lib.ts_launch_count(self._h, C.byref(n)), "ts_launch_count")
         return n.value
 
+    STAGES = ("prepare", "select", "select_tp_b", "attend_split", "attend_merge", "-", "-", "-")
+
+    def timing_begin(self, max_launches: int = 65536) -> None:
+        """Record a CUDA-event pair around every kernel of this handle until ``timing_end``."""
+        check(self.lib.ts_timing_begin(self._h, int(max_launches)), "ts_timing_begin", self._h)
+
+    def timing_end(self) -> dict:
+        """``{stage: (total_ms, launches)}`` since ``timing_begin`` (synchronises the device)."""
+        ms = (C.c_double * 8)()
+        n = (C.c_uint64 * 8)()
+        check(self.lib.ts_timing_end(self._h, ms, n), "ts_timing_end", self._h)
+        return {name: (ms[i], n[i]) for i, name in enumerate(self.STAGES)}
+
     def debug_read(self, which: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
         out = torch.empty(numel, dtype=dtype)
         check(self.lib.ts_debug_read(self._h, which, out.data_ptr(), out.numel() * out.element_size()),
