@@ -63,9 +63,11 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     const long long cap = cand_capacity_of(c);
     const int grid = fused_grid_size(num_sms);
     const size_t hd = (size_t)c->hq * c->head_dim;
-    // split the list so that one request's chunks cover the SMs about once
+    // split the list so that one request's chunks fill the SMs once (tokens go in groups of four;
+    // the staged K/V rows of a chunk must fit in shared memory)
     int ch = (n_sel + num_sms - 1) / num_sms;
-    ch = ch < 16 ? 16 : (ch + 7) / 8 * 8;
+    ch = ch < 16 ? 16 : (ch + 3) / 4 * 4;
+    while (ch > 4 && (size_t)ch * 2 * c->hkv * c->head_dim * elem > 160 * 1024) ch -= 4;
     const int chunks = (n_sel + ch - 1) / ch;
     Carve cv;
     size_t o_err = cv.take(16);
@@ -73,13 +75,15 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_flags = cv.take((size_t)c->max_batch * 4);
     size_t o_cos = cv.take((size_t)c->max_batch * 16);
     size_t o_logits = cv.take((size_t)cap * c->hq * 4);
-    size_t o_part = cv.take((size_t)c->max_batch * grid * c->hq * 8);
+    const int part_stride = (grid * c->hq + 1) & ~1;
+    size_t o_part = cv.take((size_t)c->max_batch * part_stride * 8);
     size_t o_votes = cv.take((size_t)cap * 4);
     size_t o_vpool = cv.take(c->kernel_size > 0 ? (size_t)cap * 4 : 16);
     size_t o_hist = cv.take((size_t)c->max_batch * kHistBins * 4);
     size_t o_ccount = cv.take((size_t)c->max_batch * 4);
     size_t o_sure = cv.take((size_t)c->max_batch * grid * 4);
     size_t o_bar = cv.take(16);
+    size_t o_ts = cv.take(16 * 8);
     size_t o_cand = cv.take((size_t)cap * 8);
     size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
     size_t o_pos = cv.take((size_t)c->max_batch * n_sel * 4);
@@ -108,6 +112,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.logits = reinterpret_cast<float*>(a + o_logits);
         p.partials = reinterpret_cast<float2*>(a + o_part);
         p.grid = grid;
+        p.part_stride = part_stride;
         p.tile_tokens = fused_tile_tokens(c->dtype, c->flags, c->hkv, c->head_dim, c->hq / c->hkv);
         p.votes = reinterpret_cast<float*>(a + o_votes);
         p.votes_pool = reinterpret_cast<float*>(a + o_vpool);
@@ -116,6 +121,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.cand_count = reinterpret_cast<unsigned*>(a + o_ccount);
         p.sure_count = reinterpret_cast<unsigned*>(a + o_sure);
         p.grid_bar = reinterpret_cast<unsigned*>(a + o_bar);
+        p.phase_ts = reinterpret_cast<unsigned long long*>(a + o_ts);
         p.cand = reinterpret_cast<uint2*>(a + o_cand);
         p.sel_slots = reinterpret_cast<int*>(a + o_slots);
         p.sel_pos = reinterpret_cast<int*>(a + o_pos);
@@ -376,6 +382,7 @@ int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes) {
         case 0: src = p.q_rot; avail = (size_t)h->cfg.max_batch * hd * h->elem; break;
         case 1: src = p.logits; avail = (size_t)h->cand_capacity * h->cfg.hq * 4; break;
         case 2: src = p.votes_sel; avail = (size_t)h->cand_capacity * 4; break;
+        case 3: src = p.phase_ts; avail = 16 * 8; break;
         default: return TS_ERR_INVALID_ARG;
     }
     if (bytes > avail) return TS_ERR_INVALID_ARG;

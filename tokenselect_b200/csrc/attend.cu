@@ -6,189 +6,301 @@
 // pairing, frequencies / rope_scale), logits * sm_scale, optional soft cap, fp32 softmax, values
 // un-rotated, KV head = h / group.
 //
-// Split kernel: grid (chunks, batch), 8 warps.  A warp owns one KV head (and, when fewer than 8 KV
-// heads are local, one residue class of the chunk's tokens); lane l holds elements
-// [P*l, P*l+P) and [D/2 + P*l, D/2 + P*l + P) of a row, i.e. both members of each rotation pair, so
-// the rotation needs no exchange; dot products are finished with warp shuffles.  All K/V rows of the
-// warp's tokens are requested before the first is used.
-#include "common.cuh"
+// Split kernel: grid (chunks, batch), 8 warps.  A warp works on one KV head and up to four of its
+// query heads; eight lanes share one K/V row (lane j holds elements [E*j, E*j+E) of both halves of the
+// row, i.e. both members of every rotation pair, as 16-byte loads), so a warp handles four listed
+// tokens per step and a dot product needs three shuffle steps.  Each group of eight lanes keeps its
+// own online-softmax state; groups, then warps, are merged at the end.  The rotated queries sit in
+// shared memory.
+#include "ptx.cuh"
 
 namespace ts {
 
 constexpr int kAttnWarps = kAttnThreads / 32;
+constexpr int kHeadsPerWarp = 4;
+constexpr float kLog2eA = 1.4426950408889634f;
 
-template <typename T, int P> struct RowFrag;           // the lane's 2*P elements of one row
-template <int P> struct RowFrag<__nv_bfloat16, P> {
-    uint32_t lo, hi;                                   // P bf16 values each, element 0 in the low half
-    __device__ __forceinline__ void load(const __nv_bfloat16* row, int lane, int half) {
-        if (P == 2) {
-            lo = *reinterpret_cast<const uint32_t*>(row + 2 * lane);
-            hi = *reinterpret_cast<const uint32_t*>(row + half + 2 * lane);
-        } else {
-            lo = *reinterpret_cast<const unsigned short*>(row + lane);
-            hi = *reinterpret_cast<const unsigned short*>(row + half + lane);
-        }
+// E consecutive elements of a row as fp32.
+template <typename T, int E> struct Half;
+template <> struct Half<__nv_bfloat16, 8> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ float get(int i) const {
+        const uint32_t w = i < 2 ? raw.x : i < 4 ? raw.y : i < 6 ? raw.z : raw.w;
+        return __uint_as_float((i & 1) ? (w & 0xFFFF0000u) : (w << 16));
     }
-    __device__ __forceinline__ float l(int e) const { return __uint_as_float(e == 0 ? (lo << 16) : (lo & 0xFFFF0000u)); }
-    __device__ __forceinline__ float h(int e) const { return __uint_as_float(e == 0 ? (hi << 16) : (hi & 0xFFFF0000u)); }
 };
-template <int P> struct RowFrag<float, P> {
-    float lo[P], hi[P];
-    __device__ __forceinline__ void load(const float* row, int lane, int half) {
-        if (P == 2) {
-            const float2 a = *reinterpret_cast<const float2*>(row + 2 * lane);
-            const float2 c = *reinterpret_cast<const float2*>(row + half + 2 * lane);
-            lo[0] = a.x; lo[P - 1] = a.y; hi[0] = c.x; hi[P - 1] = c.y;
-        } else {
-            lo[0] = row[lane];
-            hi[0] = row[half + lane];
-        }
+template <> struct Half<__nv_bfloat16, 4> {
+    uint2 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = *reinterpret_cast<const uint2*>(p); }
+    __device__ __forceinline__ float get(int i) const {
+        const uint32_t w = i < 2 ? raw.x : raw.y;
+        return __uint_as_float((i & 1) ? (w & 0xFFFF0000u) : (w << 16));
     }
-    __device__ __forceinline__ float l(int e) const { return lo[e]; }
-    __device__ __forceinline__ float h(int e) const { return hi[e]; }
+};
+template <> struct Half<float, 8> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = *reinterpret_cast<const float4*>(p);
+        b = *reinterpret_cast<const float4*>(p + 4);
+    }
+    __device__ __forceinline__ float get(int i) const {
+        return i == 0 ? a.x : i == 1 ? a.y : i == 2 ? a.z : i == 3 ? a.w : i == 4 ? b.x : i == 5 ? b.y : i == 6 ? b.z : b.w;
+    }
+};
+template <> struct Half<float, 4> {
+    float4 a;
+    __device__ __forceinline__ void load(const float* p) { a = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ float get(int i) const { return i == 0 ? a.x : i == 1 ? a.y : i == 2 ? a.z : a.w; }
 };
 
-template <typename T, int P, int GMAX>
+template <typename T, int E>
+struct RowPair {                      // one K or V row as seen by a lane: E elements of each half
+    Half<T, E> lo, hi;
+    __device__ __forceinline__ void load(const T* row, int j) {
+        lo.load(row + E * j);
+        hi.load(row + 8 * E + E * j);
+    }
+};
+
+// Shared-memory layout of the split kernel (bytes, every region 16-byte aligned).
+struct AttnSmem {
+    size_t q, o, ml, cs, k, v, bar, total;
+};
+__host__ __device__ inline AttnSmem attn_smem_layout(int hq, int hkv, int d, int ch, size_t elem) {
+    AttnSmem a;
+    size_t off = 0;
+    a.q = off;  off += (size_t)hq * d * 4;                         // rotated queries, fp32
+    a.o = off;  off += (size_t)kAttnWarps * kHeadsPerWarp * d * 4;  // per-warp partial outputs
+    a.ml = off; off += (size_t)kAttnWarps * kHeadsPerWarp * 8;      // per-warp (max, sum)
+    a.cs = off; off += (size_t)ch * (d / 2) * 8;                    // (cos, sin) rows of the chunk's positions
+    a.k = off;  off += (size_t)ch * hkv * d * elem;                 // key rows of the chunk
+    a.v = off;  off += (size_t)ch * hkv * d * elem;                 // value rows
+    a.bar = off; off += 16;
+    a.total = off;
+    return a;
+}
+
+template <typename T, int E>
 __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerParams p) {
-    constexpr int D = 64 * P, HALF = 32 * P;
-    constexpr int UNROLL = sizeof(T) == 2 ? 8 : 4;
-    __shared__ float sm_o[kAttnWarps][GMAX][D];
-    __shared__ float2 sm_ml[kAttnWarps][GMAX];
-    if (*(volatile int*)p.err != 0) return;
+    constexpr int D = 16 * E, HALF = 8 * E;
+    constexpr int GS = kHeadsPerWarp;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
 
     const int b = blockIdx.y, chunk = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int count = p.sel_count[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gi = lane >> 3, j = lane & 7;
     const int CH = p.attn_chunk_tokens;
-    const int base = chunk * CH;
-    if (base >= count) return;
-    const int cnt = min(CH, count - base);
     const int hkv = p.hkv, G = p.group, hq = p.hq;
-    const int nsub = hkv >= kAttnWarps ? 1 : kAttnWarps / hkv;
-    const int* slots = p.sel_slots + (size_t)b * p.n_sel + base;
-    const T* kpool = reinterpret_cast<const T*>(p.k_pool);
-    const T* vpool = reinterpret_cast<const T*>(p.v_pool);
-    const T* q = reinterpret_cast<const T*>(p.q) + (size_t)b * hq * D;
-    const float2* cs_q = p.attn_cs + (size_t)(count - 1) * HALF + P * lane;
+    const AttnSmem lay = attn_smem_layout(hq, hkv, D, CH, sizeof(T));
+    float* sm_q = reinterpret_cast<float*>(smem_raw + lay.q);
+    float* sm_o = reinterpret_cast<float*>(smem_raw + lay.o);
+    float2* sm_ml = reinterpret_cast<float2*>(smem_raw + lay.ml);
+    const float2* sm_cs = reinterpret_cast<const float2*>(smem_raw + lay.cs);
+    const T* sm_k = reinterpret_cast<const T*>(smem_raw + lay.k);
+    const T* sm_v = reinterpret_cast<const T*>(smem_raw + lay.v);
+    const uint32_t bar = smem_u32(smem_raw + lay.bar);
 
-    for (int unit = warp; unit < hkv * nsub; unit += kAttnWarps) {
-        const int kv = unit % hkv, sub = unit / hkv;
-        // query heads of this KV head, rotated at position count-1
-        float q1[GMAX][P], q2[GMAX][P];
-#pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
-            RowFrag<T, P> f;
-            if (g < G) f.load(q + (size_t)(kv * G + g) * D, lane, HALF);
-#pragma unroll
-            for (int e = 0; e < P; ++e) {
-                float x1 = g < G ? f.l(e) : 0.f, x2 = g < G ? f.h(e) : 0.f;
-                float2 cs = cs_q[e];
-                q1[g][e] = x1 * cs.x - x2 * cs.y;
-                q2[g][e] = x2 * cs.x + x1 * cs.y;
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // nothing above depends on the selection kernel; everything below does
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __syncthreads();
+
+    // one round trip: error word, sequence length, the chunk's pool rows
+    const int err = *(volatile int*)p.err;
+    const int n = p.seq_lens[b];
+    const int base = chunk * CH;
+    int my_slot = 0;
+    if (warp == 0 && lane < CH) my_slot = __ldcg(p.sel_slots + (size_t)b * p.n_sel + base + lane);
+    const int count = min(n, p.n_sel);                 // all tokens when the request is short (:376-378)
+    if (err != 0 || base >= count) return;
+    const int cnt = min(CH, count - base);
+
+    if (warp == 0) {
+        // stage the chunk's K and V rows and rotation rows with bulk asynchronous copies
+        const uint32_t row_bytes = (uint32_t)(hkv * D * sizeof(T));
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)cnt * (2u * row_bytes + (uint32_t)HALF * 8u));
+        __syncwarp();
+        const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
+        const unsigned char* vpool = reinterpret_cast<const unsigned char*>(p.v_pool);
+        for (int i = lane; i < cnt; i += 32) {
+            int slot = (i == lane) ? my_slot : __ldcg(p.sel_slots + (size_t)b * p.n_sel + base + i);
+            if ((unsigned long long)(long long)slot >= (unsigned long long)p.pool_rows) {
+                set_error(p.err, TS_ERR_BAD_SLOT, slot);
+                slot = 0;
             }
+            bulk_g2s(smem_u32(smem_raw + lay.k) + i * row_bytes, kpool + (size_t)slot * row_bytes, row_bytes, bar);
+            bulk_g2s(smem_u32(smem_raw + lay.v) + i * row_bytes, vpool + (size_t)slot * row_bytes, row_bytes, bar);
         }
-        float m[GMAX], l[GMAX], o1[GMAX][P], o2[GMAX][P];
+        if (lane == 0)
+            bulk_g2s(smem_u32(smem_raw + lay.cs), p.attn_cs + (size_t)base * HALF, (uint32_t)cnt * HALF * 8u, bar);
+    }
+    // meanwhile: rotated query of every head at position count-1
+    {
+        const T* q = reinterpret_cast<const T*>(p.q) + (size_t)b * hq * D;
+        const float2* cs_q = p.attn_cs + (size_t)(count - 1) * HALF;
+        for (int e = tid; e < hq * HALF; e += kAttnThreads) {
+            const int h = e / HALF, i = e - h * HALF;
+            const float x1 = to_f32<T>(q[h * D + i]), x2 = to_f32<T>(q[h * D + i + HALF]);
+            const float2 cs = cs_q[i];
+            sm_q[h * D + i] = x1 * cs.x - x2 * cs.y;
+            sm_q[h * D + i + HALF] = x2 * cs.x + x1 * cs.y;
+        }
+    }
+    __syncthreads();
+    {
+        bool dead = false;
+        mbar_wait(bar, 0u, p.err, dead, 20);
+    }
+
+    const int nsg = (G + GS - 1) / GS;                 // head subgroups per KV head
+    const int units = hkv * nsg;
+    const int nsub = units >= kAttnWarps ? 1 : kAttnWarps / units;   // warps sharing a unit split the tokens
+    const int slots_per_cta = units * nsub;            // <= 8 when units <= 8
+    const float cap = p.logit_cap;
+
+    for (int slot_id = warp; slot_id < slots_per_cta; slot_id += kAttnWarps) {
+        const int unit = slot_id % units, sub = slot_id / units;
+        const int kv = unit % hkv, sg = unit / hkv;
+        const int g0 = sg * GS;
+        const int ng = min(GS, G - g0);
+        const float* qh = sm_q + (size_t)(kv * G + g0) * D;
+
+        float m[GS], l[GS], o1[GS][E], o2[GS][E];
 #pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
+        for (int g = 0; g < GS; ++g) {
             m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
-            for (int e = 0; e < P; ++e) { o1[g][e] = 0.f; o2[g][e] = 0.f; }
+            for (int e = 0; e < E; ++e) { o1[g][e] = 0.f; o2[g][e] = 0.f; }
         }
-        // tokens of this unit: j = sub, sub + nsub, ... < cnt
-        for (int j0 = sub; j0 < cnt; j0 += nsub * UNROLL) {
-            RowFrag<T, P> kf[UNROLL], vf[UNROLL];
+        // this lane group's tokens: sub*4 + gi, then every 4*nsub
+#pragma unroll 2
+        for (int tk0 = sub * 4; tk0 < cnt; tk0 += 4 * nsub) {
+            const int tk = tk0 + gi;
+            const bool have = tk < cnt;
+            const int tkc = min(tk, cnt - 1);
+            RowPair<T, E> kf, vf;
+            kf.load(sm_k + ((size_t)tkc * hkv + kv) * D, j);
+            vf.load(sm_v + ((size_t)tkc * hkv + kv) * D, j);
+            float kr1[E], kr2[E];
+            {
+                const float4* cs4 = reinterpret_cast<const float4*>(sm_cs + (size_t)tkc * HALF + E * j);
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int j = j0 + u * nsub;
-                if (j < cnt) {
-                    const size_t r = ((size_t)__ldg(slots + j) * hkv + kv) * D;
-                    kf[u].load(kpool + r, lane, HALF);
-                    vf[u].load(vpool + r, lane, HALF);
+                for (int e = 0; e < E; e += 2) {
+                    const float4 cs = cs4[e / 2];            // (cos, sin) of elements e and e+1
+                    const float a1 = kf.lo.get(e), a2 = kf.hi.get(e);
+                    const float b1 = kf.lo.get(e + 1), b2 = kf.hi.get(e + 1);
+                    kr1[e] = a1 * cs.x - a2 * cs.y;
+                    kr2[e] = a2 * cs.x + a1 * cs.y;
+                    kr1[e + 1] = b1 * cs.z - b2 * cs.w;
+                    kr2[e + 1] = b2 * cs.z + b1 * cs.w;
                 }
             }
+            float s[GS];
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int j = j0 + u * nsub;
-                if (j >= cnt) break;
-                const float2* cs_k = p.attn_cs + (size_t)(base + j) * HALF + P * lane;
-                float kr1[P], kr2[P];
+            for (int g = 0; g < GS; ++g) {
+                float a = 0.f;
+                if (g < ng) {
+                    const float4* q1 = reinterpret_cast<const float4*>(qh + g * D + E * j);
+                    const float4* q2 = reinterpret_cast<const float4*>(qh + g * D + HALF + E * j);
 #pragma unroll
-                for (int e = 0; e < P; ++e) {
-                    float2 cs = cs_k[e];
-                    float x1 = kf[u].l(e), x2 = kf[u].h(e);
-                    kr1[e] = x1 * cs.x - x2 * cs.y;
-                    kr2[e] = x2 * cs.x + x1 * cs.y;
+                    for (int e = 0; e < E; e += 4) {
+                        const float4 x = q1[e / 4], y = q2[e / 4];
+                        a += x.x * kr1[e] + x.y * kr1[e + 1] + x.z * kr1[e + 2] + x.w * kr1[e + 3];
+                        a += y.x * kr2[e] + y.y * kr2[e + 1] + y.z * kr2[e + 2] + y.w * kr2[e + 3];
+                    }
                 }
-                float s[GMAX];
+                s[g] = a;
+            }
 #pragma unroll
-                for (int g = 0; g < GMAX; ++g) {
-                    float a = 0.f;
+            for (int o = 1; o <= 4; o <<= 1) {
 #pragma unroll
-                    for (int e = 0; e < P; ++e) a += q1[g][e] * kr1[e] + q2[g][e] * kr2[e];
-                    s[g] = a;
-                }
+                for (int g = 0; g < GS; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+            }
+            if (have) {
 #pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) {
-#pragma unroll
-                    for (int g = 0; g < GMAX; ++g)
-                        if (g < G) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-                }
-#pragma unroll
-                for (int g = 0; g < GMAX; ++g) {
-                    if (g < G) {
+                for (int g = 0; g < GS; ++g) {
+                    if (g < ng) {
                         float x = s[g] * p.sm_scale;
-                        if (p.logit_cap > 0.f) x = p.logit_cap * tanhf(x / p.logit_cap);
+                        if (cap > 0.f) x = cap * tanhf(x / cap);
                         const float mn = fmaxf(m[g], x);
-                        const float sc = expf(m[g] - mn);
-                        const float pe = expf(x - mn);
+                        const float sc = exp2f((m[g] - mn) * kLog2eA);
+                        const float pe = exp2f((x - mn) * kLog2eA);
                         l[g] = l[g] * sc + pe;
                         m[g] = mn;
 #pragma unroll
-                        for (int e = 0; e < P; ++e) {
-                            o1[g][e] = o1[g][e] * sc + pe * vf[u].l(e);
-                            o2[g][e] = o2[g][e] * sc + pe * vf[u].h(e);
+                        for (int e = 0; e < E; ++e) {
+                            o1[g][e] = o1[g][e] * sc + pe * vf.lo.get(e);
+                            o2[g][e] = o2[g][e] * sc + pe * vf.hi.get(e);
                         }
                     }
                 }
             }
         }
-        // partial of this warp -> shared memory
+        // merge the four lane groups (xor 8, 16)
 #pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
-            if (g < G) {
+        for (int off = 8; off <= 16; off <<= 1) {
 #pragma unroll
-                for (int e = 0; e < P; ++e) {
-                    sm_o[warp][g][P * lane + e] = o1[g][e];
-                    sm_o[warp][g][HALF + P * lane + e] = o2[g][e];
+            for (int g = 0; g < GS; ++g) {
+                const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
+                const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
+                const float mn = fmaxf(m[g], mo);
+                const float wa = (m[g] == -INFINITY) ? 0.f : exp2f((m[g] - mn) * kLog2eA);
+                const float wb = (mo == -INFINITY) ? 0.f : exp2f((mo - mn) * kLog2eA);
+                l[g] = l[g] * wa + lo * wb;
+                m[g] = mn;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const float x1 = __shfl_xor_sync(0xffffffffu, o1[g][e], off);
+                    const float x2 = __shfl_xor_sync(0xffffffffu, o2[g][e], off);
+                    o1[g][e] = o1[g][e] * wa + x1 * wb;
+                    o2[g][e] = o2[g][e] * wa + x2 * wb;
                 }
-                if (lane == 0) sm_ml[warp][g] = make_float2(m[g], l[g]);
             }
         }
-        if (hkv * nsub > kAttnWarps) {
-            // more units than warps (hkv > 8): write this unit straight out, no cross-warp merge
+        if (gi == 0) {
+#pragma unroll
+            for (int g = 0; g < GS; ++g) {
+                if (g < ng) {
+                    float* dst = sm_o + ((size_t)(slot_id % kAttnWarps) * GS + g) * D;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) { dst[E * j + e] = o1[g][e]; dst[HALF + E * j + e] = o2[g][e]; }
+                    if (j == 0) sm_ml[(slot_id % kAttnWarps) * GS + g] = make_float2(m[g], l[g]);
+                }
+            }
+        }
+        if (slots_per_cta > kAttnWarps) {
+            // more units than warps: no cross-warp merge, write this unit straight out
             __syncwarp();
-            for (int g = 0; g < G; ++g) {
-                const int h = kv * G + g;
+            for (int g = 0; g < ng; ++g) {
+                const int h = kv * G + g0 + g;
                 float* dst = p.attn_o + (((size_t)b * p.attn_chunks + chunk) * hq + h) * D;
-                for (int e = lane; e < D; e += 32) dst[e] = sm_o[warp][g][e];
-                if (lane == 0) p.attn_ml[((size_t)b * p.attn_chunks + chunk) * hq + h] = sm_ml[warp][g];
+                const float* src = sm_o + ((size_t)(slot_id % kAttnWarps) * GS + g) * D;
+                for (int e = lane; e < D; e += 32) dst[e] = src[e];
+                if (lane == 0)
+                    p.attn_ml[((size_t)b * p.attn_chunks + chunk) * hq + h] = sm_ml[(slot_id % kAttnWarps) * GS + g];
             }
             __syncwarp();
         }
     }
-    if (hkv * nsub > kAttnWarps) return;
+    if (slots_per_cta > kAttnWarps) return;
     __syncthreads();
-    // merge the nsub warps of each KV head and write the chunk's partial
-    for (int idx = threadIdx.x; idx < hq * D; idx += kAttnThreads) {
+    // merge the nsub warps of each unit and write the chunk's partial
+    for (int idx = tid; idx < hq * D; idx += kAttnThreads) {
         const int h = idx / D, e = idx - h * D;
-        const int kv = h / G, g = h - kv * G;
+        const int kv = h / G, gg = h - kv * G;
+        const int unit = kv + hkv * (gg / GS), g = gg % GS;
         float mm = -INFINITY;
-        for (int s = 0; s < nsub; ++s) mm = fmaxf(mm, sm_ml[kv + s * hkv][g].x);
+        for (int s = 0; s < nsub; ++s) mm = fmaxf(mm, sm_ml[(unit + s * units) * GS + g].x);
         float acc = 0.f, ll = 0.f;
         for (int s = 0; s < nsub; ++s) {
-            const float2 ml = sm_ml[kv + s * hkv][g];
-            const float w = (ml.x == -INFINITY) ? 0.f : expf(ml.x - mm);
-            acc += sm_o[kv + s * hkv][g][e] * w;
+            const float2 ml = sm_ml[(unit + s * units) * GS + g];
+            const float w = (ml.x == -INFINITY) ? 0.f : exp2f((ml.x - mm) * kLog2eA);
+            acc += sm_o[((size_t)(unit + s * units) * GS + g) * D + e] * w;
             ll += ml.y * w;
         }
         p.attn_o[(((size_t)b * p.attn_chunks + chunk) * hq + h) * D + e] = acc;
@@ -196,50 +308,152 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
     }
 }
 
-// grid = (hq, batch), block = D.
-template <typename T>
-__global__ void attend_merge_kernel(const LayerParams p) {
-    if (*(volatile int*)p.err != 0) return;
-    const int h = blockIdx.x, b = blockIdx.y, e = threadIdx.x;
-    const int D = p.d, hq = p.hq;
-    const int count = p.sel_count[b];
+// grid = (hq, batch), block = 512: warp w takes chunks w, w+16, ...; lane i takes elements
+// [VEC*i, VEC*i + VEC).  The partial outputs are requested before the weights are known.
+constexpr int kMergeThreads = 512;
+constexpr int kMergeBatch = 12;
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kMergeThreads) attend_merge_kernel(const LayerParams p) {
+    constexpr int D = 32 * VEC;
+    constexpr int NW = kMergeThreads / 32;
+    __shared__ float s_w[kMergeThreads];
+    __shared__ float s_acc[NW][D];
+    __shared__ float s_red[2 * NW];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hq = p.hq;
+    const int err = *(volatile int*)p.err;
+    const int count = min(p.seq_lens[b], p.n_sel);
+    if (err != 0 || count < 1) return;
     const int chunks = (count + p.attn_chunk_tokens - 1) / p.attn_chunk_tokens;
     const float2* ml = p.attn_ml + (size_t)b * p.attn_chunks * hq + h;
-    const float* o = p.attn_o + ((size_t)b * p.attn_chunks * hq + h) * D + e;
-    float mm = -INFINITY;
-    for (int c = 0; c < chunks; ++c) mm = fmaxf(mm, ml[(size_t)c * hq].x);
-    float acc = 0.f, ll = 0.f;
-    for (int c = 0; c < chunks; ++c) {
-        const float2 v = ml[(size_t)c * hq];
-        const float w = (v.x == -INFINITY) ? 0.f : expf(v.x - mm);
-        acc += o[(size_t)c * hq * D] * w;
-        ll += v.y * w;
+    const float* o = p.attn_o + ((size_t)b * p.attn_chunks * hq + h) * D + VEC * lane;
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+    float mm_run = -INFINITY, ll_run = 0.f;            // running (max, sum) over chunk rounds
+    for (int c0 = 0; c0 < chunks; c0 += kMergeThreads) {
+        // the (max, sum) of up to 512 chunks and this warp's partial outputs travel together
+        const int c = c0 + tid;
+        float2 mine = make_float2(-INFINITY, 0.f);
+        if (c < chunks) mine = __ldcg(ml + (size_t)c * hq);
+        float xo[kMergeBatch][VEC];
+        const int nround = min(kMergeThreads, chunks - c0);
+#pragma unroll
+        for (int u = 0; u < kMergeBatch; ++u) {
+            const int cc = warp + NW * u;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) xo[u][v] = 0.f;
+            if (cc < nround) {
+                const float* src = o + (size_t)(c0 + cc) * hq * D;
+                if (VEC == 4) {
+                    const float4 x = __ldcg(reinterpret_cast<const float4*>(src));
+                    xo[u][0] = x.x; xo[u][1] = x.y; xo[u][VEC - 2] = x.z; xo[u][VEC - 1] = x.w;
+                } else {
+                    const float2 x = __ldcg(reinterpret_cast<const float2*>(src));
+                    xo[u][0] = x.x; xo[u][VEC - 1] = x.y;
+                }
+            }
+        }
+        float mm = mine.x;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, off));
+        if (lane == 0) s_red[warp] = mm;
+        __syncthreads();
+        mm = mm_run;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, s_red[w]);
+        const float wgt = (mine.x == -INFINITY) ? 0.f : exp2f((mine.x - mm) * kLog2eA);
+        s_w[tid] = wgt;
+        float ll = mine.y * wgt;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
+        if (lane == 0) s_red[NW + warp] = ll;
+        __syncthreads();
+        const float rescale = (mm_run == -INFINITY) ? 0.f : exp2f((mm_run - mm) * kLog2eA);
+        ll = ll_run * rescale;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) ll += s_red[NW + w];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] *= rescale;
+#pragma unroll
+        for (int u = 0; u < kMergeBatch; ++u) {
+            const int cc = warp + NW * u;
+            if (cc < nround) {
+                const float w = s_w[cc];
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) acc[v] += w * xo[u][v];
+            }
+        }
+        // chunks of this round beyond the register batch (only with very long lists)
+        for (int cc = warp + NW * kMergeBatch; cc < nround; cc += NW) {
+            const float w = s_w[cc];
+            const float* src = o + (size_t)(c0 + cc) * hq * D;
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) acc[v] += w * __ldcg(src + v);
+        }
+        mm_run = mm;
+        ll_run = ll;
+        __syncthreads();
     }
-    reinterpret_cast<T*>(p.out)[((size_t)b * hq + h) * D + e] = from_f32<T>(acc / ll);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) s_acc[warp][VEC * lane + v] = acc[v];
+    __syncthreads();
+    for (int e = tid; e < D; e += kMergeThreads) {
+        float r = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) r += s_acc[w][e];
+        reinterpret_cast<T*>(p.out)[((size_t)b * hq + h) * D + e] = from_f32<T>(r / ll_run);
+    }
 }
 
-template <typename T, int P>
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor
+// drains; it waits (griddepcontrol.wait) before touching anything the predecessor wrote.
+template <typename... Args>
+static cudaError_t launch_pdl(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
+template <typename T, int E>
 static cudaError_t launch_attend_t(const LayerParams& p, const Launch& l) {
-    dim3 grid(p.attn_chunks, p.batch);
+    constexpr int D = 16 * E;
+    const size_t smem = attn_smem_layout(p.hq, p.hkv, D, p.attn_chunk_tokens, sizeof(T)).total;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(attend_split_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
     stage_begin(l, kStageAttendSplit);
-    if (p.group <= 4) attend_split_kernel<T, P, 4><<<grid, kAttnThreads, 0, l.stream>>>(p);
-    else attend_split_kernel<T, P, 8><<<grid, kAttnThreads, 0, l.stream>>>(p);
+    cudaError_t e = launch_pdl(attend_split_kernel<T, E>, dim3(p.attn_chunks, p.batch), dim3(kAttnThreads), smem,
+                               l.stream, p);
     stage_end(l);
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     stage_begin(l, kStageAttendMerge);
-    attend_merge_kernel<T><<<dim3(p.hq, p.batch), p.d, 0, l.stream>>>(p);
+    e = launch_pdl(attend_merge_kernel<T, D / 32>, dim3(p.hq, p.batch), dim3(kMergeThreads), 0, l.stream, p);
     stage_end(l);
-    return cudaGetLastError();
+    return e;
 }
 
 cudaError_t launch_attend(const LayerParams& p, const Launch& l) {
     if (l.dtype == TS_DTYPE_BF16) {
-        if (p.d == 128) return launch_attend_t<__nv_bfloat16, 2>(p, l);
-        return launch_attend_t<__nv_bfloat16, 1>(p, l);
+        if (p.d == 128) return launch_attend_t<__nv_bfloat16, 8>(p, l);
+        return launch_attend_t<__nv_bfloat16, 4>(p, l);
     }
-    if (p.d == 128) return launch_attend_t<float, 2>(p, l);
-    return launch_attend_t<float, 1>(p, l);
+    if (p.d == 128) return launch_attend_t<float, 8>(p, l);
+    return launch_attend_t<float, 4>(p, l);
 }
 
 }  // namespace ts

@@ -17,6 +17,7 @@ constexpr int kFusedThreads = 288;    // 1 copy-issuing warp + 8 mma warps
 constexpr int kScoreStages = 5;
 constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stage
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
+constexpr int kFusedDynSmem = 174080; // dynamic shared memory of the selection kernel (5 stages of 34 KB)
 constexpr int kAttnThreads = 256;
 constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
 
@@ -48,7 +49,8 @@ struct LayerParams {
     int* flags;                // [max_batch] TS_FLAG_*
     float* cos_terms;          // [max_batch, 4] (q.c, |q|^2, |c|^2, -)
     float* logits;             // [cand_capacity, hq]
-    float2* partials;          // [max_batch, grid, hq] per-CTA (max, sum exp)
+    float2* partials;          // [max_batch, part_stride]: per-CTA (max, sum exp) as [grid, hq]
+    int part_stride;           // grid*hq rounded up to an even number of float2
     int grid;                  // CTAs of the selection kernel (one per SM)
     int tile_tokens;           // candidates per work tile; fixes which CTA owns which candidates
     float* votes;              // [cand_capacity] head-summed softmax
@@ -59,6 +61,7 @@ struct LayerParams {
     unsigned* cand_count;      // [max_batch] entries of `cand` per request
     unsigned* sure_count;      // [max_batch, grid] winners above the threshold bin, per CTA
     unsigned* grid_bar;        // [1] self-resetting grid barrier word
+    unsigned long long* phase_ts;  // [16] nanosecond timestamps of CTA 0 at the phase boundaries
     int* sel_slots;            // [max_batch, n_sel]
     int* sel_pos;              // [max_batch, n_sel]
     int* sel_count;            // [max_batch]

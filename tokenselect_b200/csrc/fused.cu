@@ -37,75 +37,22 @@
 #include <cooperative_groups.h>
 
 #include "prep.cuh"
+#include "ptx.cuh"
 
 namespace ts {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kWarps = kFusedThreads / 32;
 
-// ------------------------------------------------------------------------------------------
-// PTX wrappers
-// ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after kWaitCycles, records TS_ERR_DEVICE_TIMEOUT and lets the caller carry
-// on (control flow stays uniform so no barrier is left short of a participant).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead, int where) {
-    if (mbar_try_wait(bar, parity)) return;
-    if (dead) return;
-    const long long t0 = clock64();
-    unsigned spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 1023u) == 0u) {
-            if (clock64() - t0 > kWaitCycles) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); dead = true; return; }
-            if (*(volatile int*)err != 0) { dead = true; return; }
-        }
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// CTA 0 leaves a nanosecond timestamp at every phase boundary (read back with ts_debug_read).
+__device__ __forceinline__ void stamp(const LayerParams& p, int i) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.phase_ts[i] = t;
     }
 }
-__device__ __forceinline__ uint64_t l2_evict_first_policy() {
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-// One row, global -> shared, completion counted in bytes on an mbarrier; streamed through L2.
-__device__ __forceinline__ void bulk_row_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t pol) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar), "l"(pol)
-        : "memory");
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-        "{%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------
 // shared state
@@ -126,6 +73,8 @@ struct FusedShared {
     int res_bin;
     unsigned res_above, res_cnt;
     unsigned tmp_u[4];
+    int seg_b1[kMaxBatch];
+    unsigned seg_above[kMaxBatch], seg_cnt[kMaxBatch];
     unsigned long long full[kScoreStages];
     unsigned long long empty[kScoreStages];
     int idx[2][kIdxBlock];
@@ -138,6 +87,7 @@ struct ScoreGeom {
     static constexpr int kRowStride = kRowBytes + 16;       // padded row in shared memory
     static constexpr int kStageBytes = kTok * kRowStride;
     static constexpr int kRowsPerLane = (kTok + 31) / 32;
+    static_assert(kScoreStages * kStageBytes <= kFusedDynSmem, "ring must fit the dynamic shared memory");
 };
 
 // Self-resetting grid barrier (bounded).  Every CTA of the grid must call it the same number of
@@ -425,7 +375,7 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
             const int kv = ctid / group, j = ctid - kv * group;
             float mm = -INFINITY, ll = 0.f;
             for (int w = kv; w < 8; w += HKV) ml_merge(mm, ll, sh.stats[w][j].x, sh.stats[w][j].y);
-            p.partials[((size_t)sg.b * p.grid + cta) * hq + ctid] = make_float2(mm, ll);
+            p.partials[(size_t)sg.b * p.part_stride + (size_t)cta * hq + ctid] = make_float2(mm, ll);
         }
         consumer_bar();
     }
@@ -483,72 +433,36 @@ __device__ __forceinline__ void score_phase_plain(const LayerParams& p, FusedSha
         if (tid < hq) {
             float mm = -INFINITY, ll = 0.f;
             for (int w = 0; w < kWarps; ++w) ml_merge(mm, ll, red[(w * hq + tid) * 2], red[(w * hq + tid) * 2 + 1]);
-            p.partials[((size_t)sg.b * p.grid + blockIdx.x) * hq + tid] = make_float2(mm, ll);
+            p.partials[(size_t)sg.b * p.part_stride + (size_t)blockIdx.x * hq + tid] = make_float2(mm, ll);
         }
         __syncthreads();
     }
 }
 
 // ------------------------------------------------------------------------------------------
-// phase 2: votes of the owned candidates (+ histogram)
+// helpers of phases 2-4: few dependent memory round trips, everything a thread needs requested at once
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void flush_hist(const LayerParams& p, FusedShared& sh, int b) {
-    __syncthreads();
-    unsigned* gh = p.hist + (size_t)b * kHistBins;
-    for (int i = threadIdx.x; i < kHistBins; i += kFusedThreads) {
-        const unsigned c = sh.hist[i];
-        if (c) { atomicAdd(gh + i, c); sh.hist[i] = 0u; }
-    }
-    __syncthreads();
+constexpr int kTokBatch = 8;          // candidates a thread holds in registers at a time
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
 }
 
-__device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh, bool with_hist) {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int hq = p.hq;
-    for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
-    for (int s = 0; s < sh.nseg; ++s) {
-        const Seg sg = sh.seg[s];
-        __syncthreads();
-        // softmax statistics of the request: merge every CTA's (max, sum exp); one warp per head
-        for (int c = warp; c < hq; c += kWarps) {
-            float m = -INFINITY, l = 0.f;
-            for (int i = lane; i < p.grid; i += 32) {
-                const float2 v = __ldcg(p.partials + ((size_t)sg.b * p.grid + i) * hq + c);
-                ml_merge(m, l, v.x, v.y);
-            }
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) {
-                float mo = __shfl_xor_sync(0xffffffffu, m, o);
-                float lo = __shfl_xor_sync(0xffffffffu, l, o);
-                ml_merge(m, l, mo, lo);
-            }
-            if (lane == 0) { sh.s_m[c] = m; sh.s_inv[c] = 1.f / l; }
-        }
-        __syncthreads();
-        const float* lg = p.logits + (size_t)sh.plan.off[sg.b] * hq;
-        float* votes = p.votes + sh.plan.off[sg.b];
-        for (int t = sg.t0 + tid; t < sg.t1; t += kFusedThreads) {
-            const float* row = lg + (size_t)t * hq;
-            float v = 0.f;
-            if ((hq & 3) == 0) {
-                for (int c = 0; c < hq; c += 4) {
-                    const float4 x = __ldcg(reinterpret_cast<const float4*>(row + c));
-                    v += exp2f((x.x - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
-                    v += exp2f((x.y - sh.s_m[c + 1]) * kLog2e) * sh.s_inv[c + 1];
-                    v += exp2f((x.z - sh.s_m[c + 2]) * kLog2e) * sh.s_inv[c + 2];
-                    v += exp2f((x.w - sh.s_m[c + 3]) * kLog2e) * sh.s_inv[c + 3];
-                }
-            } else {
-                for (int c = 0; c < hq; ++c) v += exp2f((__ldcg(row + c) - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
-            }
-            votes[t] = v;
-            if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
-        }
-        if (with_hist) flush_hist(p, sh, sg.b);
-    }
+// Shared-memory stride of a staged logit row: a multiple of 16 B whose 16-byte index is odd, so that
+// eight consecutive threads reading their own rows with 16-byte loads hit distinct banks.
+__host__ __device__ __forceinline__ int logit_row_stride(int hq) {
+    int rs = (hq * 4 + 15) / 16 * 16;
+    if (((rs / 16) & 1) == 0) rs += 16;
+    return rs;
 }
 
-// Votes the selection reads for candidate t of a segment: the raw vote, or the sliding maximum over
+// Votes the selection reads for candidate t: the raw vote, or the sliding maximum over
 // [t - pad, t - pad + K - 1] clipped to the request (window K, padding (K-1)/2, stride 1).
 __device__ __forceinline__ float sel_vote(const LayerParams& p, const float* votes, int t, int nc) {
     const int K = p.kernel_size;
@@ -560,6 +474,110 @@ __device__ __forceinline__ float sel_vote(const LayerParams& p, const float* vot
     return v;
 }
 
+// Thread `tid` owns the consecutive candidates [own0, own1) of a segment [t0, t1).
+__device__ __forceinline__ void own_range(int t0, int t1, int& own0, int& own1, int& per) {
+    per = (t1 - t0 + kFusedThreads - 1) / kFusedThreads;
+    own0 = min(t1, t0 + (int)threadIdx.x * per);
+    own1 = min(t1, own0 + per);
+}
+
+__device__ __forceinline__ void load_vote_batch(const LayerParams& p, const float* votes, int nc, int beg, int end,
+                                                float (&v)[kTokBatch]) {
+#pragma unroll
+    for (int i = 0; i < kTokBatch; ++i) v[i] = (beg + i < end) ? sel_vote(p, votes, beg + i, nc) : 0.f;
+}
+
+__device__ __forceinline__ void flush_hist(const LayerParams& p, FusedShared& sh, int b) {
+    __syncthreads();
+    unsigned* gh = p.hist + (size_t)b * kHistBins;
+    for (int i = threadIdx.x; i < kHistBins; i += kFusedThreads) {
+        const unsigned c = sh.hist[i];
+        if (c) { atomicAdd(gh + i, c); sh.hist[i] = 0u; }
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 2: votes of the owned candidates (+ histogram).  The request's per-CTA statistics and the
+// CTA's own logit rows are staged in shared memory with asynchronous copies issued together.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist) {
+    const int tid = threadIdx.x;
+    const int hq = p.hq;
+    const int part_elems = (p.grid * hq + 1) & ~1;                 // float2 entries, 16-byte multiple
+    float2* part_s = reinterpret_cast<float2*>(dyn);
+    const int rs = logit_row_stride(hq);
+    unsigned char* rows_s = dyn + (size_t)part_elems * 8;
+    const int cap_rows = (kFusedDynSmem - part_elems * 8) / rs;
+    const bool vec = (hq & 3) == 0;
+    for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const float* lg = p.logits + (size_t)sh.plan.off[sg.b] * hq;
+        float* votes = p.votes + sh.plan.off[sg.b];
+        for (int r0 = sg.t0; r0 < sg.t1; r0 += cap_rows) {
+            const int r1 = min(sg.t1, r0 + cap_rows);
+            __syncthreads();
+            if (r0 == sg.t0) {
+                const float2* src = p.partials + (size_t)sg.b * p.part_stride;
+                for (int i = tid; i < part_elems / 2; i += kFusedThreads) cp_async_16(part_s + 2 * i, src + 2 * i);
+            }
+            if (vec) {
+                const int per_row = hq / 4;
+                for (int i = tid; i < (r1 - r0) * per_row; i += kFusedThreads) {
+                    const int r = i / per_row, c = i - r * per_row;
+                    cp_async_16(rows_s + (size_t)r * rs + c * 16, lg + (size_t)(r0 + r) * hq + c * 4);
+                }
+            } else {
+                for (int i = tid; i < (r1 - r0) * hq; i += kFusedThreads) {
+                    const int r = i / hq, c = i - r * hq;
+                    cp_async_4(rows_s + (size_t)r * rs + c * 4, lg + (size_t)(r0 + r) * hq + c);
+                }
+            }
+            cp_async_wait_all();
+            __syncthreads();
+            if (r0 == sg.t0) {
+                // softmax statistics of the request: merge every CTA's (max, sum exp) in two levels
+                const int nsl = kFusedThreads / hq;                 // slices per head
+                const int c = tid % hq, sl = tid / hq;
+                float2* lvl = reinterpret_cast<float2*>(sh.idx);   // [nsl][hq] scratch
+                if (sl < nsl) {
+                    float m = -INFINITY, l = 0.f;
+                    for (int i = sl; i < p.grid; i += nsl) ml_merge(m, l, part_s[i * hq + c].x, part_s[i * hq + c].y);
+                    lvl[sl * hq + c] = make_float2(m, l);
+                }
+                __syncthreads();
+                if (tid < hq) {
+                    float m = -INFINITY, l = 0.f;
+                    for (int i = 0; i < nsl; ++i) ml_merge(m, l, lvl[i * hq + tid].x, lvl[i * hq + tid].y);
+                    sh.s_m[tid] = m;
+                    sh.s_inv[tid] = 1.f / l;
+                }
+                __syncthreads();
+            }
+            for (int t = r0 + tid; t < r1; t += kFusedThreads) {
+                const unsigned char* row = rows_s + (size_t)(t - r0) * rs;
+                float v = 0.f;
+                if (vec) {
+                    for (int c = 0; c < hq; c += 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(row + c * 4);
+                        v += exp2f((x.x - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
+                        v += exp2f((x.y - sh.s_m[c + 1]) * kLog2e) * sh.s_inv[c + 1];
+                        v += exp2f((x.z - sh.s_m[c + 2]) * kLog2e) * sh.s_inv[c + 2];
+                        v += exp2f((x.w - sh.s_m[c + 3]) * kLog2e) * sh.s_inv[c + 3];
+                    }
+                } else {
+                    const float* rf = reinterpret_cast<const float*>(row);
+                    for (int c = 0; c < hq; ++c) v += exp2f((rf[c] - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
+                }
+                votes[t] = v;
+                if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+            }
+        }
+        if (with_hist) flush_hist(p, sh, sg.b);
+    }
+}
+
 // phase 2': histogram from final votes (after a tensor-parallel sum and/or max-pool); pooled votes
 // are also written out for inspection.
 __device__ __forceinline__ void hist_phase(const LayerParams& p, FusedShared& sh) {
@@ -569,12 +587,20 @@ __device__ __forceinline__ void hist_phase(const LayerParams& p, FusedShared& sh
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
         const int nc = sh.plan.nc[sg.b];
-        const int ne = pooled_len(nc, p.kernel_size);
+        const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
         const float* votes = p.votes + sh.plan.off[sg.b];
-        for (int t = sg.t0 + tid; t < min(sg.t1, ne); t += kFusedThreads) {
-            const float v = sel_vote(p, votes, t, nc);
-            if (p.kernel_size > 0) p.votes_pool[sh.plan.off[sg.b] + t] = v;
-            atomicAdd(&sh.hist[vote_bin(v)], 1u);
+        int own0, own1, per;
+        own_range(sg.t0, t1, own0, own1, per);
+        for (int beg = own0; beg < own1; beg += kTokBatch) {
+            float v[kTokBatch];
+            load_vote_batch(p, votes, nc, beg, own1, v);
+#pragma unroll
+            for (int i = 0; i < kTokBatch; ++i) {
+                if (beg + i < own1) {
+                    if (p.kernel_size > 0) p.votes_pool[sh.plan.off[sg.b] + beg + i] = v[i];
+                    atomicAdd(&sh.hist[vote_bin(v[i])], 1u);
+                }
+            }
         }
         flush_hist(p, sh, sg.b);
     }
@@ -583,13 +609,6 @@ __device__ __forceinline__ void hist_phase(const LayerParams& p, FusedShared& sh
 // ------------------------------------------------------------------------------------------
 // phase 3: threshold bin; count the sure winners, list the threshold bin's members
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void load_threshold(const LayerParams& p, FusedShared& sh, int b) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < kHistBins; i += kFusedThreads) sh.hist[i] = __ldcg(p.hist + (size_t)b * kHistBins + i);
-    __syncthreads();
-    find_threshold(sh, (unsigned)p.top_k);
-}
-
 __device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& sh) {
     const int tid = threadIdx.x;
     // requests this CTA owns nothing of still need a zero in their per-CTA winner count
@@ -597,18 +616,44 @@ __device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& 
         if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE) p.sure_count[(size_t)b * p.grid + blockIdx.x] = 0u;
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
-        load_threshold(p, sh, sg.b);
-        const unsigned b1 = (unsigned)sh.res_bin;
         const int nc = sh.plan.nc[sg.b];
         const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
         const float* votes = p.votes + sh.plan.off[sg.b];
         uint2* cand = p.cand + sh.plan.off[sg.b];
+        int own0, own1, per;
+        own_range(sg.t0, t1, own0, own1, per);
+        // the first batch of own votes and the request's histogram travel together
+        float v0[kTokBatch];
+        load_vote_batch(p, votes, nc, own0, own1, v0);
+        unsigned hreg[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int bin = tid + kFusedThreads * i;
+            hreg[i] = bin < kHistBins ? __ldcg(p.hist + (size_t)sg.b * kHistBins + bin) : 0u;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int bin = tid + kFusedThreads * i;
+            if (bin < kHistBins) sh.hist[bin] = hreg[i];
+        }
+        __syncthreads();
+        find_threshold(sh, (unsigned)p.top_k);
+        const unsigned b1 = (unsigned)sh.res_bin;
+        if (tid == 0) { sh.seg_b1[s] = sh.res_bin; sh.seg_above[s] = sh.res_above; sh.seg_cnt[s] = sh.res_cnt; }
         // pass 1: counts
         unsigned sure = 0, eq = 0;
-        for (int t = sg.t0 + tid; t < t1; t += kFusedThreads) {
-            const unsigned bin = vote_bin(sel_vote(p, votes, t, nc));
-            sure += bin > b1;
-            eq += bin == b1;
+#pragma unroll
+        for (int i = 0; i < kTokBatch; ++i) {
+            if (own0 + i < own1) { const unsigned bin = vote_bin(v0[i]); sure += bin > b1; eq += bin == b1; }
+        }
+        for (int beg = own0 + kTokBatch; beg < own1; beg += kTokBatch) {
+            float v[kTokBatch];
+            load_vote_batch(p, votes, nc, beg, own1, v);
+#pragma unroll
+            for (int i = 0; i < kTokBatch; ++i) {
+                if (beg + i < own1) { const unsigned bin = vote_bin(v[i]); sure += bin > b1; eq += bin == b1; }
+            }
         }
         const unsigned long long packed =
             block_inclusive_scan(((unsigned long long)sure << 32) | eq, sh.warp_sum64);
@@ -623,20 +668,29 @@ __device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& 
         }
         __syncthreads();
         // pass 2: append this CTA's members of the threshold bin (order inside the list is free)
-        unsigned at = sh.tmp_u[2] + (unsigned)packed - eq;
         if (sh.tmp_u[1]) {
-            for (int t = sg.t0 + tid; t < t1; t += kFusedThreads) {
-                const float v = sel_vote(p, votes, t, nc);
-                if (vote_bin(v) == b1) cand[at++] = make_uint2((unsigned)t, __float_as_uint(v));
+            unsigned at = sh.tmp_u[2] + (unsigned)packed - eq;
+#pragma unroll
+            for (int i = 0; i < kTokBatch; ++i)
+                if (own0 + i < own1 && vote_bin(v0[i]) == b1)
+                    cand[at++] = make_uint2((unsigned)(own0 + i), __float_as_uint(v0[i]));
+            for (int beg = own0 + kTokBatch; beg < own1; beg += kTokBatch) {
+                float v[kTokBatch];
+                load_vote_batch(p, votes, nc, beg, own1, v);
+#pragma unroll
+                for (int i = 0; i < kTokBatch; ++i)
+                    if (beg + i < own1 && vote_bin(v[i]) == b1)
+                        cand[at++] = make_uint2((unsigned)(beg + i), __float_as_uint(v[i]));
             }
         }
+        __syncthreads();
     }
 }
 
 // ------------------------------------------------------------------------------------------
 // phase 4: remaining radix levels (every CTA for itself), ordered emission
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh) {
+__device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& sh) {
     const int tid = threadIdx.x;
     const int k = p.top_k;
     // windows, dense requests and cached index sets: request b is handled by CTA b % grid
@@ -672,16 +726,51 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
             }
         }
     }
+}
 
+constexpr int kCandSmem = 8192;       // threshold-bin members staged in shared memory (64 KB)
+
+__device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn) {
+    const int tid = threadIdx.x;
+    const int k = p.top_k;
+    uint2* cand_s = reinterpret_cast<uint2*>(dyn);
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
         const int req = p.req_pool_indices[sg.b];
-        load_threshold(p, sh, sg.b);
-        const unsigned b1 = (unsigned)sh.res_bin;
-        const unsigned k1 = (unsigned)k - sh.res_above;    // still to take from the threshold bin
-        const unsigned n_c = __ldcg(p.cand_count + sg.b);
-        if (n_c != sh.res_cnt && tid == 0) set_error(p.err, TS_ERR_INTERNAL, (int)n_c);
-        const uint2* cand = p.cand + sh.plan.off[sg.b];
+        const unsigned b1 = (unsigned)sh.seg_b1[s];
+        const unsigned k1 = (unsigned)k - sh.seg_above[s];       // still to take from the threshold bin
+        const unsigned n_c = sh.seg_cnt[s];                      // members of the threshold bin
+        const uint2* cand_g = p.cand + sh.plan.off[sg.b];
+        const int nc = sh.plan.nc[sg.b];
+        const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
+        const float* votes = p.votes + sh.plan.off[sg.b];
+        int own0, own1, per;
+        own_range(sg.t0, t1, own0, own1, per);
+
+        // one round trip: first batch of own votes, lower CTAs' winner counts, the candidate list
+        float v0[kTokBatch];
+        load_vote_batch(p, votes, nc, own0, own1, v0);
+        unsigned before = 0;
+        for (int c = tid; c < (int)blockIdx.x; c += kFusedThreads) before += __ldcg(p.sure_count + (size_t)sg.b * p.grid + c);
+        const bool staged = n_c <= (unsigned)kCandSmem;
+        __syncthreads();
+        if (staged) {
+            uint2 creg[kTokBatch];
+            for (unsigned i0 = 0; i0 < n_c; i0 += kFusedThreads * kTokBatch) {
+#pragma unroll
+                for (int u = 0; u < kTokBatch; ++u) {
+                    const unsigned i = i0 + tid + kFusedThreads * u;
+                    creg[u] = i < n_c ? __ldcg(cand_g + i) : make_uint2(0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < kTokBatch; ++u) {
+                    const unsigned i = i0 + tid + kFusedThreads * u;
+                    if (i < n_c) cand_s[i] = creg[u];
+                }
+            }
+        }
+        __syncthreads();
+        auto get_cand = [&](unsigned i) -> uint2 { return staged ? cand_s[i] : __ldcg(cand_g + i); };
 
         // further levels on (low 20 vote bits | inverted index): 10, 10, 11, 11, 10 bits from the top
         unsigned long long prefix = 0ull, mask_above = 0ull;
@@ -696,7 +785,7 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
             __syncthreads();
             const unsigned long long dmask = (1ull << widths[lv]) - 1ull;
             for (unsigned i = tid; i < n_c; i += kFusedThreads) {
-                const unsigned long long key = cand_key(__ldcg(cand + i));
+                const unsigned long long key = cand_key(get_cand(i));
                 if ((key & mask_above) == prefix) atomicAdd(&sh.hist[(unsigned)((key >> shifts[lv]) & dmask)], 1u);
             }
             __syncthreads();
@@ -707,54 +796,65 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
             active = sh.res_cnt;
         }
 
-        // winners before this CTA's range: sure winners of lower CTAs + winning candidates below t0
-        unsigned before = 0;
-        for (int c = tid; c < (int)blockIdx.x; c += kFusedThreads) before += __ldcg(p.sure_count + (size_t)sg.b * p.grid + c);
+        // winners before this thread's candidates: lower CTAs' sure winners, winning threshold-bin
+        // members below this CTA's range, own-range winners of lower threads
         for (unsigned i = tid; i < n_c; i += kFusedThreads) {
-            const uint2 c = __ldcg(cand + i);
+            const uint2 c = get_cand(i);
             if ((int)c.x < sg.t0 && (cand_key(c) & mask_above) >= prefix) ++before;
         }
-        const unsigned before_all = block_inclusive_scan(before, sh.warp_sum);
-        if (tid == kFusedThreads - 1) sh.tmp_u[3] = before_all;
+        auto selected = [&](int t, float v) -> bool {
+            const unsigned bin = vote_bin(v);
+            if (bin > b1) return true;
+            if (bin < b1) return false;
+            return (cand_key(make_uint2((unsigned)t, __float_as_uint(v))) & mask_above) >= prefix;
+        };
+        unsigned mine = 0;
+#pragma unroll
+        for (int i = 0; i < kTokBatch; ++i) mine += (own0 + i < own1) && selected(own0 + i, v0[i]);
+        for (int beg = own0 + kTokBatch; beg < own1; beg += kTokBatch) {
+            float v[kTokBatch];
+            load_vote_batch(p, votes, nc, beg, own1, v);
+#pragma unroll
+            for (int i = 0; i < kTokBatch; ++i) mine += (beg + i < own1) && selected(beg + i, v[i]);
+        }
+        const unsigned long long packed =
+            block_inclusive_scan(((unsigned long long)before << 32) | mine, sh.warp_sum64);
+        if (tid == kFusedThreads - 1) {
+            sh.tmp_u[0] = (unsigned)(packed >> 32);
+            sh.tmp_u[1] = (unsigned)packed;
+        }
         __syncthreads();
-        unsigned base = sh.tmp_u[3];
+        unsigned rank = sh.tmp_u[0] + (unsigned)packed - mine;     // rank of this thread's first winner
+        const unsigned total_here = sh.tmp_u[0] + sh.tmp_u[1];
 
-        // ordered emission of the owned range, kFusedThreads candidates at a time
-        const int nc = sh.plan.nc[sg.b];
-        const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
-        const float* votes = p.votes + sh.plan.off[sg.b];
         const int* row = p.rtt + (long long)req * p.rtt_stride;
         int* out_slots = p.sel_slots + (size_t)sg.b * p.n_sel;
         int* out_pos = p.sel_pos + (size_t)sg.b * p.n_sel;
         int* cache_pos = p.pos_cache + ((size_t)req * p.n_layers + p.layer) * k;
-        for (int c0 = sg.t0; c0 < t1; c0 += kFusedThreads) {
-            const int t = c0 + tid;
-            unsigned sel = 0;
-            if (t < t1) {
-                const float v = sel_vote(p, votes, t, nc);
-                const unsigned bin = vote_bin(v);
-                if (bin > b1) sel = 1;
-                else if (bin == b1)
-                    sel = (cand_key(make_uint2((unsigned)t, __float_as_uint(v))) & mask_above) >= prefix;
+        auto put = [&](int t) {
+            if (rank < (unsigned)k) {
+                const int pos = p.n_init + t;
+                out_pos[p.n_init + rank] = pos;
+                out_slots[p.n_init + rank] = checked_slot(p, row, pos);
+                if (p.query_cache) cache_pos[rank] = pos;          // topk_indices_cache[layer] = ... (:415)
+            } else {
+                set_error(p.err, TS_ERR_INTERNAL, (int)rank);
             }
-            const unsigned incl = block_inclusive_scan(sel, sh.warp_sum);
-            if (sel) {
-                const unsigned rank = base + incl - 1;
-                if (rank < (unsigned)k) {
-                    const int pos = p.n_init + t;
-                    out_pos[p.n_init + rank] = pos;
-                    out_slots[p.n_init + rank] = checked_slot(p, row, pos);
-                    if (p.query_cache) cache_pos[rank] = pos;      // topk_indices_cache[layer] = ... (:415)
-                } else {
-                    set_error(p.err, TS_ERR_INTERNAL, (int)rank);
-                }
-            }
-            if (tid == kFusedThreads - 1) sh.tmp_u[3] = base + incl;
-            __syncthreads();
-            base = sh.tmp_u[3];
+            ++rank;
+        };
+#pragma unroll
+        for (int i = 0; i < kTokBatch; ++i)
+            if (own0 + i < own1 && selected(own0 + i, v0[i])) put(own0 + i);
+        for (int beg = own0 + kTokBatch; beg < own1; beg += kTokBatch) {
+            float v[kTokBatch];
+            load_vote_batch(p, votes, nc, beg, own1, v);
+#pragma unroll
+            for (int i = 0; i < kTokBatch; ++i)
+                if (beg + i < own1 && selected(beg + i, v[i])) put(beg + i);
         }
         // the CTA owning the request's last candidates checks the total
-        if (sg.t1 >= nc && tid == 0 && base != (unsigned)k) set_error(p.err, TS_ERR_INTERNAL, (int)base);
+        if (sg.t1 >= nc && tid == 0 && total_here != (unsigned)k) set_error(p.err, TS_ERR_INTERNAL, (int)total_here);
+        __syncthreads();
     }
 }
 
@@ -769,7 +869,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     const int tid = threadIdx.x;
     bool dead = false;
 
+    // The attention kernels that follow are launched with programmatic serialization: let them be
+    // scheduled as soon as SMs free up; they wait for this grid to finish before reading anything.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- phase 0 ----
+    stamp(p, 0);
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (blockIdx.x == 0) { p.phase_ts[9] = t; p.phase_ts[10] = t; }
+        else atomicMin(p.phase_ts + 11, t);
+    }
     bool ok = *(volatile int*)p.err == 0;
     const bool need_flags_barrier = p.query_cache != 0;
     if (mode != kModeTpB) {
@@ -815,6 +925,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     __syncthreads();
 
     const bool pooled = p.kernel_size > 0;
+    stamp(p, 1);
     if (mode != kModeTpB) {
         // ---- phase 1: score ----
         if (ok) {
@@ -824,14 +935,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
                 bool mine = false;
                 for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
                 if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
-                    p.partials[((size_t)b * p.grid + blockIdx.x) * p.hq + c] = make_float2(-INFINITY, 0.f);
+                    p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
             }
             if constexpr (HKV > 0) score_phase_tma<HKV>(p, sh, ring, dead);
             else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
         }
+        stamp(p, 2);
         grid_barrier(p, dead);
+        stamp(p, 3);
         // ---- phase 2: votes ----
-        if (ok) vote_phase(p, sh, mode == kModeAll && !pooled);
+        if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled);
+        stamp(p, 4);
         if (mode == kModeTpA) return;
         if (pooled) {
             grid_barrier(p, dead);
@@ -841,11 +955,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         if (ok) hist_phase(p, sh);
     }
     grid_barrier(p, dead);
+    stamp(p, 5);
     // ---- phase 3 ----
     if (ok) filter_phase(p, sh);
+    stamp(p, 6);
     grid_barrier(p, dead);
+    stamp(p, 7);
     // ---- phase 4 ----
-    if (ok) emit_phase(p, sh);
+    if (ok) {
+        emit_windows(p, sh);
+        emit_phase(p, sh, ring);
+    }
+    stamp(p, 8);
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        atomicMax(p.phase_ts + 12, t);
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -863,9 +989,10 @@ int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group) {
 }
 
 template <typename T, int HKV>
-static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mode, size_t smem) {
+static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mode) {
+    const size_t smem = kFusedDynSmem;
     static bool configured = false;
-    if (!configured && smem > 48 * 1024) {
+    if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(fused_select_kernel<T, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
@@ -884,15 +1011,14 @@ static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mod
 cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode) {
     if (use_tma(l.dtype, l.flags, p.hkv, p.d, p.group)) {
         switch (p.hkv) {
-            case 1: return launch_fused_t<__nv_bfloat16, 1>(p, l, mode, (size_t)kScoreStages * ScoreGeom<1>::kStageBytes);
-            case 2: return launch_fused_t<__nv_bfloat16, 2>(p, l, mode, (size_t)kScoreStages * ScoreGeom<2>::kStageBytes);
-            case 4: return launch_fused_t<__nv_bfloat16, 4>(p, l, mode, (size_t)kScoreStages * ScoreGeom<4>::kStageBytes);
-            default: return launch_fused_t<__nv_bfloat16, 8>(p, l, mode, (size_t)kScoreStages * ScoreGeom<8>::kStageBytes);
+            case 1: return launch_fused_t<__nv_bfloat16, 1>(p, l, mode);
+            case 2: return launch_fused_t<__nv_bfloat16, 2>(p, l, mode);
+            case 4: return launch_fused_t<__nv_bfloat16, 4>(p, l, mode);
+            default: return launch_fused_t<__nv_bfloat16, 8>(p, l, mode);
         }
     }
-    const size_t smem = (size_t)p.hq * p.d * sizeof(float);
-    if (l.dtype == TS_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, 0>(p, l, mode, smem);
-    return launch_fused_t<float, 0>(p, l, mode, smem);
+    if (l.dtype == TS_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, 0>(p, l, mode);
+    return launch_fused_t<float, 0>(p, l, mode);
 }
 
 }  // namespace ts
