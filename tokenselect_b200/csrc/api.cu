@@ -83,7 +83,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_ccount = cv.take((size_t)c->max_batch * 4);
     size_t o_sure = cv.take((size_t)c->max_batch * grid * 4);
     size_t o_bar = cv.take(16);
-    size_t o_ts = cv.take(16 * 8);
+    size_t o_ts = cv.take(64 * 8);
     size_t o_cand = cv.take((size_t)cap * 8);
     size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
     size_t o_pos = cv.take((size_t)c->max_batch * n_sel * 4);
@@ -92,6 +92,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_aml = cv.take((size_t)c->max_batch * chunks * c->hq * 8);
     size_t o_scs = cv.take((size_t)(c->head_dim / 2) * 8);
     size_t o_acs = cv.take((size_t)(n_sel + 1) * (c->head_dim / 2) * 8);
+    size_t o_acsl = cv.take((size_t)(n_sel + 1) * (c->head_dim / 2) * 8);
     size_t o_fp = cv.take((size_t)c->max_reqs * c->n_layers * hd * elem);
     size_t o_pc = cv.take((size_t)c->max_reqs * c->n_layers * c->top_k * 4);
     size_t o_valid = cv.take((size_t)c->max_reqs * c->n_layers * 4);
@@ -131,6 +132,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.attn_chunks = chunks; p.attn_chunk_tokens = ch;
         p.score_cs = reinterpret_cast<const float2*>(a + o_scs);
         p.attn_cs = reinterpret_cast<const float2*>(a + o_acs);
+        p.attn_cs_lane = reinterpret_cast<const float2*>(a + o_acsl);
         p.cand_capacity = cap;
         p.fp_cache = a + o_fp;
         p.pos_cache = reinterpret_cast<int*>(a + o_pc);
@@ -274,6 +276,8 @@ int ts_create(const ts_config* cfg, ts_handle** out) {
     if (e == cudaSuccess && cfg->attn_cos_sin)
         e = cudaMemcpy(const_cast<float2*>(p.attn_cs), cfg->attn_cos_sin, (size_t)(h->n_sel + 1) * half * 8,
                        cudaMemcpyHostToDevice);
+    if (e == cudaSuccess)
+        e = launch_lane_order_table(p.attn_cs, const_cast<float2*>(p.attn_cs_lane), cfg->head_dim, h->n_sel + 1, 0);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { cudaFree(h->arena); delete h; return TS_ERR_CUDA; }
     *out = h;
@@ -382,7 +386,7 @@ int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes) {
         case 0: src = p.q_rot; avail = (size_t)h->cfg.max_batch * hd * h->elem; break;
         case 1: src = p.logits; avail = (size_t)h->cand_capacity * h->cfg.hq * 4; break;
         case 2: src = p.votes_sel; avail = (size_t)h->cand_capacity * 4; break;
-        case 3: src = p.phase_ts; avail = 16 * 8; break;
+        case 3: src = p.phase_ts; avail = 64 * 8; break;
         default: return TS_ERR_INVALID_ARG;
     }
     if (bytes > avail) return TS_ERR_INVALID_ARG;

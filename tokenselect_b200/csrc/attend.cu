@@ -6,12 +6,15 @@
 // pairing, frequencies / rope_scale), logits * sm_scale, optional soft cap, fp32 softmax, values
 // un-rotated, KV head = h / group.
 //
-// Split kernel: grid (chunks, batch), 8 warps.  A warp works on one KV head and up to four of its
-// query heads; eight lanes share one K/V row (lane j holds elements [E*j, E*j+E) of both halves of the
-// row, i.e. both members of every rotation pair, as 16-byte loads), so a warp handles four listed
-// tokens per step and a dot product needs three shuffle steps.  Each group of eight lanes keeps its
-// own online-softmax state; groups, then warps, are merged at the end.  The rotated queries sit in
-// shared memory.
+// Split kernel: grid (chunks, batch), 16 warps.  The chunk's K and V rows and the rotation rows of its
+// positions are staged in shared memory with bulk asynchronous copies (TMA engine, one mbarrier).  A
+// warp works on one KV head and up to four of its query heads; eight lanes share one K/V row (lane j
+// holds elements [E*j, E*j+E) of both halves of the row, i.e. both members of every rotation pair, as
+// 16-byte loads), so a warp handles four listed tokens per step and a dot product needs three shuffle
+// steps.  Scores of up to four steps are computed first, then one rescale and the value accumulation
+// (two-pass softmax inside a group of steps).  Each group of eight lanes keeps its own softmax state;
+// groups, then warps, are merged at the end.  The rotated queries sit in shared memory, laid out (like
+// the rotation rows) so that the eight lanes' 16-byte loads are contiguous.
 #include "ptx.cuh"
 
 namespace ts {
@@ -72,7 +75,7 @@ __host__ __device__ inline AttnSmem attn_smem_layout(int hq, int hkv, int d, int
     size_t off = 0;
     a.q = off;  off += (size_t)hq * d * 4;                         // rotated queries, fp32
     a.o = off;  off += (size_t)kAttnWarps * kHeadsPerWarp * d * 4;  // per-warp partial outputs
-    a.ml = off; off += (size_t)kAttnWarps * kHeadsPerWarp * 8;      // per-warp (max, sum)
+    a.ml = off; off += (size_t)kAttnWarps * kHeadsPerWarp * 8;      // per-warp (max in base-2 units, sum)
     a.cs = off; off += (size_t)ch * (d / 2) * 8;                    // (cos, sin) rows of the chunk's positions
     a.k = off;  off += (size_t)ch * hkv * d * elem;                 // key rows of the chunk
     a.v = off;  off += (size_t)ch * hkv * d * elem;                 // value rows
@@ -81,6 +84,7 @@ __host__ __device__ inline AttnSmem attn_smem_layout(int hq, int hkv, int d, int
     return a;
 }
 
+#define ATT_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.phase_ts[(i)] = t_; } } while (0)
 template <typename T, int E>
 __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerParams p) {
     constexpr int D = 16 * E, HALF = 8 * E;
@@ -105,8 +109,10 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
         mbar_init(bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    ATT_STAMP(32);
     // nothing above depends on the selection kernel; everything below does
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    ATT_STAMP(33);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __syncthreads();
 
@@ -119,6 +125,7 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
     const int count = min(n, p.n_sel);                 // all tokens when the request is short (:376-378)
     if (err != 0 || base >= count) return;
     const int cnt = min(CH, count - base);
+    ATT_STAMP(34);
 
     if (warp == 0) {
         // stage the chunk's K and V rows and rotation rows with bulk asynchronous copies
@@ -137,7 +144,7 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
             bulk_g2s(smem_u32(smem_raw + lay.v) + i * row_bytes, vpool + (size_t)slot * row_bytes, row_bytes, bar);
         }
         if (lane == 0)
-            bulk_g2s(smem_u32(smem_raw + lay.cs), p.attn_cs + (size_t)base * HALF, (uint32_t)cnt * HALF * 8u, bar);
+            bulk_g2s(smem_u32(smem_raw + lay.cs), p.attn_cs_lane + (size_t)base * HALF, (uint32_t)cnt * HALF * 8u, bar);
     }
     // meanwhile: rotated query of every head at position count-1
     {
@@ -147,15 +154,20 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
             const int h = e / HALF, i = e - h * HALF;
             const float x1 = to_f32<T>(q[h * D + i]), x2 = to_f32<T>(q[h * D + i + HALF]);
             const float2 cs = cs_q[i];
-            sm_q[h * D + i] = x1 * cs.x - x2 * cs.y;
-            sm_q[h * D + i + HALF] = x2 * cs.x + x1 * cs.y;
+            // element E*j + r of a half goes to float ((r/4)*8 + j)*4 + r%4 of that half
+            const int jj = i / E, r = i - jj * E;
+            const int at = ((r >> 2) * 8 + jj) * 4 + (r & 3);
+            sm_q[h * D + at] = x1 * cs.x - x2 * cs.y;
+            sm_q[h * D + HALF + at] = x2 * cs.x + x1 * cs.y;
         }
     }
     __syncthreads();
+    ATT_STAMP(35);
     {
         bool dead = false;
         mbar_wait(bar, 0u, p.err, dead, 20);
     }
+    ATT_STAMP(36);
 
     const int nsg = (G + GS - 1) / GS;                 // head subgroups per KV head
     const int units = hkv * nsg;
@@ -177,65 +189,101 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
 #pragma unroll
             for (int e = 0; e < E; ++e) { o1[g][e] = 0.f; o2[g][e] = 0.f; }
         }
-        // this lane group's tokens: sub*4 + gi, then every 4*nsub
-#pragma unroll 2
-        for (int tk0 = sub * 4; tk0 < cnt; tk0 += 4 * nsub) {
-            const int tk = tk0 + gi;
-            const bool have = tk < cnt;
-            const int tkc = min(tk, cnt - 1);
-            RowPair<T, E> kf, vf;
-            kf.load(sm_k + ((size_t)tkc * hkv + kv) * D, j);
-            vf.load(sm_v + ((size_t)tkc * hkv + kv) * D, j);
-            float kr1[E], kr2[E];
-            {
-                const float4* cs4 = reinterpret_cast<const float4*>(sm_cs + (size_t)tkc * HALF + E * j);
+        // this lane group's tokens: sub*4 + gi, then every 4*nsub; up to kSteps steps form a group whose
+        // scores are all computed before the values are accumulated
+        constexpr int kSteps = 1;
+        const int stride = 4 * nsub;
+        for (int tg0 = sub * 4; tg0 < cnt; tg0 += kSteps * stride) {
+            float sc_all[kSteps][GS];
+            // pass 1: scores
 #pragma unroll
-                for (int e = 0; e < E; e += 2) {
-                    const float4 cs = cs4[e / 2];            // (cos, sin) of elements e and e+1
-                    const float a1 = kf.lo.get(e), a2 = kf.hi.get(e);
-                    const float b1 = kf.lo.get(e + 1), b2 = kf.hi.get(e + 1);
-                    kr1[e] = a1 * cs.x - a2 * cs.y;
-                    kr2[e] = a2 * cs.x + a1 * cs.y;
-                    kr1[e + 1] = b1 * cs.z - b2 * cs.w;
-                    kr2[e + 1] = b2 * cs.z + b1 * cs.w;
-                }
-            }
-            float s[GS];
+            for (int st = 0; st < kSteps; ++st) {
+                const int tk0 = tg0 + st * stride;
 #pragma unroll
-            for (int g = 0; g < GS; ++g) {
-                float a = 0.f;
-                if (g < ng) {
-                    const float4* q1 = reinterpret_cast<const float4*>(qh + g * D + E * j);
-                    const float4* q2 = reinterpret_cast<const float4*>(qh + g * D + HALF + E * j);
+                for (int g = 0; g < GS; ++g) sc_all[st][g] = -INFINITY;
+                if (tk0 < cnt) {                       // warp-uniform
+                    const int tk = tk0 + gi;
+                    const int tkc = min(tk, cnt - 1);
+                    RowPair<T, E> kf;
+                    kf.load(sm_k + ((size_t)tkc * hkv + kv) * D, j);
+                    float kr1[E], kr2[E];
+                    const float4* cs4 = reinterpret_cast<const float4*>(sm_cs + (size_t)tkc * HALF) + j;
 #pragma unroll
-                    for (int e = 0; e < E; e += 4) {
-                        const float4 x = q1[e / 4], y = q2[e / 4];
-                        a += x.x * kr1[e] + x.y * kr1[e + 1] + x.z * kr1[e + 2] + x.w * kr1[e + 3];
-                        a += y.x * kr2[e] + y.y * kr2[e + 1] + y.z * kr2[e + 2] + y.w * kr2[e + 3];
+                    for (int e = 0; e < E; e += 2) {
+                        const float4 cs = cs4[(e / 2) * 8];  // (cos, sin) of elements E*j+e and E*j+e+1
+                        const float a1 = kf.lo.get(e), a2 = kf.hi.get(e);
+                        const float b1 = kf.lo.get(e + 1), b2 = kf.hi.get(e + 1);
+                        kr1[e] = a1 * cs.x - a2 * cs.y;
+                        kr2[e] = a2 * cs.x + a1 * cs.y;
+                        kr1[e + 1] = b1 * cs.z - b2 * cs.w;
+                        kr2[e + 1] = b2 * cs.z + b1 * cs.w;
+                    }
+                    float s[GS];
+#pragma unroll
+                    for (int g = 0; g < GS; ++g) {
+                        float a = 0.f;
+                        if (g < ng) {
+                            const float4* q1 = reinterpret_cast<const float4*>(qh + g * D) + j;
+                            const float4* q2 = reinterpret_cast<const float4*>(qh + g * D + HALF) + j;
+#pragma unroll
+                            for (int e = 0; e < E; e += 4) {
+                                const float4 x = q1[(e / 4) * 8], y = q2[(e / 4) * 8];
+                                a += x.x * kr1[e] + x.y * kr1[e + 1] + x.z * kr1[e + 2] + x.w * kr1[e + 3];
+                                a += y.x * kr2[e] + y.y * kr2[e + 1] + y.z * kr2[e + 2] + y.w * kr2[e + 3];
+                            }
+                        }
+                        s[g] = a;
+                    }
+#pragma unroll
+                    for (int o = 1; o <= 4; o <<= 1) {
+#pragma unroll
+                        for (int g = 0; g < GS; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+                    }
+                    if (tk < cnt) {
+#pragma unroll
+                        for (int g = 0; g < GS; ++g) {
+                            float x = s[g] * p.sm_scale;
+                            if (cap > 0.f) x = cap * tanhf(x / cap);
+                            sc_all[st][g] = x * kLog2eA;        // base-2 logits
+                        }
                     }
                 }
-                s[g] = a;
             }
+            // one rescale per group of steps
+            float nm[GS];
 #pragma unroll
-            for (int o = 1; o <= 4; o <<= 1) {
+            for (int g = 0; g < GS; ++g) {
+                float mx = m[g];
 #pragma unroll
-                for (int g = 0; g < GS; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+                for (int st = 0; st < kSteps; ++st) mx = fmaxf(mx, sc_all[st][g]);
+                nm[g] = mx;
+                const float sc = (mx == -INFINITY) ? 1.f : exp2f(m[g] - mx);
+                l[g] *= sc;
+#pragma unroll
+                for (int e = 0; e < E; ++e) { o1[g][e] *= sc; o2[g][e] *= sc; }
+                m[g] = mx;
             }
-            if (have) {
+            // pass 2: values
 #pragma unroll
-                for (int g = 0; g < GS; ++g) {
-                    if (g < ng) {
-                        float x = s[g] * p.sm_scale;
-                        if (cap > 0.f) x = cap * tanhf(x / cap);
-                        const float mn = fmaxf(m[g], x);
-                        const float sc = exp2f((m[g] - mn) * kLog2eA);
-                        const float pe = exp2f((x - mn) * kLog2eA);
-                        l[g] = l[g] * sc + pe;
-                        m[g] = mn;
+            for (int st = 0; st < kSteps; ++st) {
+                const int tk = tg0 + st * stride + gi;
+                if (tg0 + st * stride < cnt) {           // warp-uniform
+                    const int tkc = min(tk, cnt - 1);
+                    RowPair<T, E> vf;
+                    vf.load(sm_v + ((size_t)tkc * hkv + kv) * D, j);
+                    float pe[GS];
 #pragma unroll
-                        for (int e = 0; e < E; ++e) {
-                            o1[g][e] = o1[g][e] * sc + pe * vf.lo.get(e);
-                            o2[g][e] = o2[g][e] * sc + pe * vf.hi.get(e);
+                    for (int g = 0; g < GS; ++g) {
+                        pe[g] = (sc_all[st][g] == -INFINITY) ? 0.f : exp2f(sc_all[st][g] - nm[g]);
+                        l[g] += pe[g];
+                    }
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        const float v1 = vf.lo.get(e), v2 = vf.hi.get(e);
+#pragma unroll
+                        for (int g = 0; g < GS; ++g) {
+                            o1[g][e] += pe[g] * v1;
+                            o2[g][e] += pe[g] * v2;
                         }
                     }
                 }
@@ -249,8 +297,8 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
                 const float mo = __shfl_xor_sync(0xffffffffu, m[g], off);
                 const float lo = __shfl_xor_sync(0xffffffffu, l[g], off);
                 const float mn = fmaxf(m[g], mo);
-                const float wa = (m[g] == -INFINITY) ? 0.f : exp2f((m[g] - mn) * kLog2eA);
-                const float wb = (mo == -INFINITY) ? 0.f : exp2f((mo - mn) * kLog2eA);
+                const float wa = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn);
+                const float wb = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
                 l[g] = l[g] * wa + lo * wb;
                 m[g] = mn;
 #pragma unroll
@@ -262,7 +310,26 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
                 }
             }
         }
-        if (gi == 0) {
+        if (nsub == 1) {
+            // the warp owns its heads' whole chunk: write the partial straight from registers
+            if (gi == 0) {
+#pragma unroll
+                for (int g = 0; g < GS; ++g) {
+                    if (g < ng) {
+                        const int h = kv * G + g0 + g;
+                        float* dst = p.attn_o + (((size_t)b * p.attn_chunks + chunk) * hq + h) * D;
+#pragma unroll
+                        for (int e = 0; e < E; e += 4) {
+                            *reinterpret_cast<float4*>(dst + E * j + e) =
+                                make_float4(o1[g][e], o1[g][e + 1], o1[g][e + 2], o1[g][e + 3]);
+                            *reinterpret_cast<float4*>(dst + HALF + E * j + e) =
+                                make_float4(o2[g][e], o2[g][e + 1], o2[g][e + 2], o2[g][e + 3]);
+                        }
+                        if (j == 0) p.attn_ml[((size_t)b * p.attn_chunks + chunk) * hq + h] = make_float2(m[g], l[g]);
+                    }
+                }
+            }
+        } else if (gi == 0) {
 #pragma unroll
             for (int g = 0; g < GS; ++g) {
                 if (g < ng) {
@@ -273,22 +340,10 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
                 }
             }
         }
-        if (slots_per_cta > kAttnWarps) {
-            // more units than warps: no cross-warp merge, write this unit straight out
-            __syncwarp();
-            for (int g = 0; g < ng; ++g) {
-                const int h = kv * G + g0 + g;
-                float* dst = p.attn_o + (((size_t)b * p.attn_chunks + chunk) * hq + h) * D;
-                const float* src = sm_o + ((size_t)(slot_id % kAttnWarps) * GS + g) * D;
-                for (int e = lane; e < D; e += 32) dst[e] = src[e];
-                if (lane == 0)
-                    p.attn_ml[((size_t)b * p.attn_chunks + chunk) * hq + h] = sm_ml[(slot_id % kAttnWarps) * GS + g];
-            }
-            __syncwarp();
-        }
     }
-    if (slots_per_cta > kAttnWarps) return;
+    if (nsub == 1) { ATT_STAMP(37); ATT_STAMP(38); return; }
     __syncthreads();
+    ATT_STAMP(37);
     // merge the nsub warps of each unit and write the chunk's partial
     for (int idx = tid; idx < hq * D; idx += kAttnThreads) {
         const int h = idx / D, e = idx - h * D;
@@ -299,13 +354,14 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
         float acc = 0.f, ll = 0.f;
         for (int s = 0; s < nsub; ++s) {
             const float2 ml = sm_ml[(unit + s * units) * GS + g];
-            const float w = (ml.x == -INFINITY) ? 0.f : exp2f((ml.x - mm) * kLog2eA);
+            const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - mm);
             acc += sm_o[((size_t)(unit + s * units) * GS + g) * D + e] * w;
             ll += ml.y * w;
         }
         p.attn_o[(((size_t)b * p.attn_chunks + chunk) * hq + h) * D + e] = acc;
         if (e == 0) p.attn_ml[((size_t)b * p.attn_chunks + chunk) * hq + h] = make_float2(mm, ll);
     }
+    ATT_STAMP(38);
 }
 
 // grid = (hq, batch), block = 512: warp w takes chunks w, w+16, ...; lane i takes elements
@@ -363,14 +419,14 @@ __global__ void __launch_bounds__(kMergeThreads) attend_merge_kernel(const Layer
         mm = mm_run;
 #pragma unroll
         for (int w = 0; w < NW; ++w) mm = fmaxf(mm, s_red[w]);
-        const float wgt = (mine.x == -INFINITY) ? 0.f : exp2f((mine.x - mm) * kLog2eA);
+        const float wgt = (mine.x == -INFINITY) ? 0.f : exp2f(mine.x - mm);
         s_w[tid] = wgt;
         float ll = mine.y * wgt;
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, off);
         if (lane == 0) s_red[NW + warp] = ll;
         __syncthreads();
-        const float rescale = (mm_run == -INFINITY) ? 0.f : exp2f((mm_run - mm) * kLog2eA);
+        const float rescale = (mm_run == -INFINITY) ? 0.f : exp2f(mm_run - mm);
         ll = ll_run * rescale;
 #pragma unroll
         for (int w = 0; w < NW; ++w) ll += s_red[NW + w];

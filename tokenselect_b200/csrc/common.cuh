@@ -71,6 +71,7 @@ struct LayerParams {
     int attn_chunk_tokens;
     const float2* score_cs;    // [d/2] (cos, sin) of the scoring position
     const float2* attn_cs;     // [n_sel+1, d/2]
+    const float2* attn_cs_lane; // same rows, entries in the order the attention kernel's lanes read them
     long long cand_capacity;
     // per-request selection cache
     void* fp_cache;            // [max_reqs, n_layers, hq*d] dtype
@@ -202,6 +203,15 @@ inline void stage_end(const Launch& l) {
 
 cudaError_t launch_rope_tables(float2* score_cs, float2* attn_cs, int d, int n_rows, double base,
                                double rope_scale, int n_local, cudaStream_t stream);
+cudaError_t launch_lane_order_table(const float2* attn_cs, float2* attn_cs_lane, int d, int n_rows, cudaStream_t stream);
+
+// Position of rotation entry i (0 <= i < d/2) inside a lane-ordered table row: lane j = i / E of an
+// eight-lane group owns entries [E*j, E*j+E); its f-th 16-byte load covers entries E*j+2f, E*j+2f+1, and
+// the eight lanes' f-th loads are contiguous.  E = d/16.
+__host__ __device__ __forceinline__ int lane_order_slot(int i, int e_per_lane) {
+    const int j = i / e_per_lane, r = i - j * e_per_lane;
+    return ((r >> 1) * 8 + j) * 2 + (r & 1);
+}
 // Phases the selection kernel runs in one launch.
 enum FusedMode {
     kModeAll = 0,   // prepare, score, vote, top-k, emit (single GPU)

@@ -34,7 +34,6 @@
 // breaks exact ties in favour of the lowest position.
 //
 // Logits are stored token-major, [candidate][hq], with column c = kv_head*group + j.
-#include <cooperative_groups.h>
 
 #include "prep.cuh"
 #include "ptx.cuh"
@@ -66,7 +65,8 @@ struct FusedShared {
     int nseg;
     PrepShared prep;
     float2 stats[8][8];               // [mma warp][column]
-    float s_m[kMaxHq], s_inv[kMaxHq];
+    __align__(16) float s_m[kMaxHq];   // per-head bias of the vote exponent
+    unsigned long long stage_bar;      // mbarrier of the vote phase's staging copies
     unsigned hist[kHistBins];
     unsigned warp_sum[32];
     unsigned long long warp_sum64[32];
@@ -499,82 +499,178 @@ __device__ __forceinline__ void flush_hist(const LayerParams& p, FusedShared& sh
 
 // ------------------------------------------------------------------------------------------
 // phase 2: votes of the owned candidates (+ histogram).  The request's per-CTA statistics and the
-// CTA's own logit rows are staged in shared memory with asynchronous copies issued together.
+// CTA's own logit rows are staged in shared memory: bulk asynchronous copies when a row is a multiple
+// of 16 bytes (the rows of a CTA are one contiguous block), 4-byte asynchronous copies otherwise.
+// The first block of rows is requested before the grid barrier that precedes this phase.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist) {
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+struct VoteGeom {
+    int part_bytes, row_bytes, cap_rows;
+    bool bulk;
+};
+__device__ __forceinline__ VoteGeom vote_geom(const LayerParams& p) {
+    VoteGeom g;
+    g.part_bytes = ((p.grid * p.hq + 1) & ~1) * 8;
+    g.bulk = (p.hq & 3) == 0;
+    g.row_bytes = g.bulk ? p.hq * 4 : logit_row_stride(p.hq);
+    g.cap_rows = (kFusedDynSmem - g.part_bytes) / g.row_bytes;
+    return g;
+}
+
+// Thread 0: request rows [r0, r1) of a segment's logits (and, with `parts`, the request's statistics).
+// `armed` says the mbarrier already expects these bytes.
+__device__ __forceinline__ void vote_issue(const LayerParams& p, FusedShared& sh, unsigned char* dyn, const VoteGeom& g,
+                                           const Seg& sg, int r0, int r1, bool rows, bool parts, bool arm) {
+    const uint32_t bar = smem_u32(&sh.stage_bar);
+    const uint32_t row_total = (uint32_t)(r1 - r0) * (uint32_t)g.row_bytes;
+    asm volatile("fence.proxy.async;" ::: "memory");
+    if (arm) mbar_expect_tx(bar, row_total + (r0 == sg.t0 ? (uint32_t)g.part_bytes : 0u));
+    if (rows) {
+        const unsigned char* src =
+            reinterpret_cast<const unsigned char*>(p.logits + ((size_t)sh.plan.off[sg.b] + r0) * p.hq);
+        const uint32_t dst = smem_u32(dyn + g.part_bytes);
+        for (uint32_t o = 0; o < row_total; o += 32768u)
+            bulk_g2s(dst + o, src + o, min(32768u, row_total - o), bar);
+    }
+    if (parts)
+        bulk_g2s(smem_u32(dyn), p.partials + (size_t)sg.b * p.part_stride, (uint32_t)g.part_bytes, bar);
+}
+
+// Called by all threads after the scoring phase and before the grid barrier.
+__device__ __forceinline__ void vote_prefetch(const LayerParams& p, FusedShared& sh, unsigned char* dyn) {
+    const VoteGeom g = vote_geom(p);
+    __syncthreads();                                   // this CTA's logit stores are done
+    if (g.bulk && sh.nseg > 0 && threadIdx.x == 0) {
+        const Seg sg = sh.seg[0];
+        vote_issue(p, sh, dyn, g, sg, sg.t0, min(sg.t1, sg.t0 + g.cap_rows), true, false, true);
+    }
+}
+
+__device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist,
+                                           uint32_t& stage_parity, bool& dead) {
     const int tid = threadIdx.x;
     const int hq = p.hq;
-    const int part_elems = (p.grid * hq + 1) & ~1;                 // float2 entries, 16-byte multiple
-    float2* part_s = reinterpret_cast<float2*>(dyn);
-    const int rs = logit_row_stride(hq);
-    unsigned char* rows_s = dyn + (size_t)part_elems * 8;
-    const int cap_rows = (kFusedDynSmem - part_elems * 8) / rs;
-    const bool vec = (hq & 3) == 0;
+    const VoteGeom g = vote_geom(p);
+    const float2* part_s = reinterpret_cast<const float2*>(dyn);
+    const unsigned char* rows_s = dyn + g.part_bytes;
+    const int nch = hq / 4;
+    int rot_shift = 0;                                 // log2(8 / gcd(nch, 8)): see the row loop
+    for (int gg = nch; (gg & 1) == 0 && rot_shift < 3; gg >>= 1) ++rot_shift;
+    rot_shift = 3 - rot_shift;
+    const bool pow2 = (nch & (nch - 1)) == 0;
     for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
         const float* lg = p.logits + (size_t)sh.plan.off[sg.b] * hq;
         float* votes = p.votes + sh.plan.off[sg.b];
-        for (int r0 = sg.t0; r0 < sg.t1; r0 += cap_rows) {
-            const int r1 = min(sg.t1, r0 + cap_rows);
+        for (int r0 = sg.t0; r0 < sg.t1; r0 += g.cap_rows) {
+            const int r1 = min(sg.t1, r0 + g.cap_rows);
+            const bool first = r0 == sg.t0;
             __syncthreads();
-            if (r0 == sg.t0) {
-                const float2* src = p.partials + (size_t)sg.b * p.part_stride;
-                for (int i = tid; i < part_elems / 2; i += kFusedThreads) cp_async_16(part_s + 2 * i, src + 2 * i);
-            }
-            if (vec) {
-                const int per_row = hq / 4;
-                for (int i = tid; i < (r1 - r0) * per_row; i += kFusedThreads) {
-                    const int r = i / per_row, c = i - r * per_row;
-                    cp_async_16(rows_s + (size_t)r * rs + c * 16, lg + (size_t)(r0 + r) * hq + c * 4);
-                }
+            if (g.bulk) {
+                const bool prefetched = s == 0 && first;
+                if (tid == 0) vote_issue(p, sh, dyn, g, sg, r0, r1, !prefetched, first, !prefetched);
+                mbar_wait(smem_u32(&sh.stage_bar), stage_parity, p.err, dead, 4);
+                stage_parity ^= 1u;
             } else {
+                if (first) {
+                    const float2* src = p.partials + (size_t)sg.b * p.part_stride;
+                    float2* dstp = reinterpret_cast<float2*>(dyn);
+                    for (int i = tid; i < g.part_bytes / 16; i += kFusedThreads) cp_async_16(dstp + 2 * i, src + 2 * i);
+                }
                 for (int i = tid; i < (r1 - r0) * hq; i += kFusedThreads) {
                     const int r = i / hq, c = i - r * hq;
-                    cp_async_4(rows_s + (size_t)r * rs + c * 4, lg + (size_t)(r0 + r) * hq + c);
+                    cp_async_4(dyn + g.part_bytes + (size_t)r * g.row_bytes + c * 4, lg + (size_t)(r0 + r) * hq + c);
                 }
+                cp_async_wait_all();
             }
-            cp_async_wait_all();
             __syncthreads();
-            if (r0 == sg.t0) {
-                // softmax statistics of the request: merge every CTA's (max, sum exp) in two levels
+            stamp(p, 20);
+            if (first) {
+                // softmax statistics of the request: merge every CTA's (max, sum exp) in two levels, each
+                // as a max pass followed by independent exponentials; head c then contributes
+                // exp2(x*log2e + bias_c) with bias_c = -(M_c*log2e + log2 L_c)
                 const int nsl = kFusedThreads / hq;                 // slices per head
                 const int c = tid % hq, sl = tid / hq;
                 float2* lvl = reinterpret_cast<float2*>(sh.idx);   // [nsl][hq] scratch
                 if (sl < nsl) {
-                    float m = -INFINITY, l = 0.f;
-                    for (int i = sl; i < p.grid; i += nsl) ml_merge(m, l, part_s[i * hq + c].x, part_s[i * hq + c].y);
+                    float m = -INFINITY;
+#pragma unroll 6
+                    for (int i = sl; i < p.grid; i += nsl) m = fmaxf(m, part_s[i * hq + c].x);
+                    float l = 0.f;
+                    if (m > -INFINITY) {
+#pragma unroll 6
+                        for (int i = sl; i < p.grid; i += nsl) {
+                            const float2 v = part_s[i * hq + c];
+                            l += v.y * ex2_approx((v.x - m) * kLog2e);
+                        }
+                    }
                     lvl[sl * hq + c] = make_float2(m, l);
                 }
                 __syncthreads();
                 if (tid < hq) {
-                    float m = -INFINITY, l = 0.f;
-                    for (int i = 0; i < nsl; ++i) ml_merge(m, l, lvl[i * hq + tid].x, lvl[i * hq + tid].y);
-                    sh.s_m[tid] = m;
-                    sh.s_inv[tid] = 1.f / l;
+                    float m = -INFINITY;
+#pragma unroll 4
+                    for (int i = 0; i < nsl; ++i) m = fmaxf(m, lvl[i * hq + tid].x);
+                    float l = 0.f;
+#pragma unroll 4
+                    for (int i = 0; i < nsl; ++i) {
+                        const float2 v = lvl[i * hq + tid];
+                        if (v.x > -INFINITY) l += v.y * ex2_approx((v.x - m) * kLog2e);
+                    }
+                    sh.s_m[tid] = -(m * kLog2e + log2f(l));
                 }
                 __syncthreads();
             }
-            for (int t = r0 + tid; t < r1; t += kFusedThreads) {
-                const unsigned char* row = rows_s + (size_t)(t - r0) * rs;
-                float v = 0.f;
-                if (vec) {
-                    for (int c = 0; c < hq; c += 4) {
-                        const float4 x = *reinterpret_cast<const float4*>(row + c * 4);
-                        v += exp2f((x.x - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
-                        v += exp2f((x.y - sh.s_m[c + 1]) * kLog2e) * sh.s_inv[c + 1];
-                        v += exp2f((x.z - sh.s_m[c + 2]) * kLog2e) * sh.s_inv[c + 2];
-                        v += exp2f((x.w - sh.s_m[c + 3]) * kLog2e) * sh.s_inv[c + 3];
-                    }
-                } else {
-                    const float* rf = reinterpret_cast<const float*>(row);
-                    for (int c = 0; c < hq; ++c) v += exp2f((rf[c] - sh.s_m[c]) * kLog2e) * sh.s_inv[c];
+            stamp(p, 21);
+            if (g.bulk && nch <= 16) {
+                // Rows are unpadded: every thread starts at a different 16-byte chunk so that eight
+                // consecutive threads hit distinct banks (chunk counts that are not a power of two are
+                // odd here and need no rotation).  A thread's rows are kFusedThreads apart, a multiple
+                // of eight, so its rotation is fixed and the biases can sit in registers in that order.
+                const int rot = pow2 ? ((tid >> rot_shift) & (nch - 1)) : 0;
+                float4 bbr[16];
+#pragma unroll
+                for (int k = 0; k < 16; ++k) {
+                    const int c4 = pow2 ? ((k + rot) & (nch - 1)) : k;
+                    bbr[k] = k < nch ? *reinterpret_cast<const float4*>(&sh.s_m[c4 * 4]) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
-                votes[t] = v;
-                if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+                for (int t = r0 + tid; t < r1; t += kFusedThreads) {
+                    const unsigned char* row = rows_s + (size_t)(t - r0) * g.row_bytes;
+                    float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+#pragma unroll
+                    for (int k = 0; k < 16; ++k) {
+                        if (k < nch) {
+                            const int c4 = pow2 ? ((k + rot) & (nch - 1)) : k;
+                            const float4 x = *reinterpret_cast<const float4*>(row + c4 * 16);
+                            v0 += ex2_approx(fmaf(x.x, kLog2e, bbr[k].x));
+                            v1 += ex2_approx(fmaf(x.y, kLog2e, bbr[k].y));
+                            v2 += ex2_approx(fmaf(x.z, kLog2e, bbr[k].z));
+                            v3 += ex2_approx(fmaf(x.w, kLog2e, bbr[k].w));
+                        }
+                    }
+                    const float v = (v0 + v1) + (v2 + v3);
+                    votes[t] = v;
+                    if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+                }
+            } else {
+                for (int t = r0 + tid; t < r1; t += kFusedThreads) {
+                    const float* rf = reinterpret_cast<const float*>(rows_s + (size_t)(t - r0) * g.row_bytes);
+                    float v = 0.f;
+                    for (int c = 0; c < hq; ++c) v += ex2_approx(fmaf(rf[c], kLog2e, sh.s_m[c]));
+                    votes[t] = v;
+                    if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+                }
             }
         }
+        stamp(p, 22);
         if (with_hist) flush_hist(p, sh, sg.b);
+        stamp(p, 23);
     }
 }
 
@@ -914,15 +1010,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
             }
         }
         sh.nseg = ns;
+        mbar_init(smem_u32(&sh.stage_bar), 1);
         if (HKV > 0) {
             for (int s = 0; s < kScoreStages; ++s) {
                 mbar_init(smem_u32(&sh.full[s]), 1);
                 mbar_init(smem_u32(&sh.empty[s]), 8);
             }
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    uint32_t stage_parity = 0;
 
     const bool pooled = p.kernel_size > 0;
     stamp(p, 1);
@@ -940,11 +1038,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
             if constexpr (HKV > 0) score_phase_tma<HKV>(p, sh, ring, dead);
             else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
         }
+        if (ok) vote_prefetch(p, sh, ring);
         stamp(p, 2);
         grid_barrier(p, dead);
         stamp(p, 3);
         // ---- phase 2: votes ----
-        if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled);
+        if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead);
         stamp(p, 4);
         if (mode == kModeTpA) return;
         if (pooled) {
@@ -1000,10 +1099,20 @@ static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mod
     }
     LayerParams pp = p;
     int m = mode;
-    void* args[] = {&pp, &m};
     stage_begin(l, mode == kModeTpB ? kStageSelectTpB : kStageSelect);
-    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(fused_select_kernel<T, HKV>), dim3(p.grid),
-                                                dim3(kFusedThreads), args, smem, l.stream);
+    // cooperative launch (all CTAs co-resident: the grid barriers need it) through the extensible
+    // launch call, which queues behind the previous kernel more tightly than the dedicated call
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, fused_select_kernel<T, HKV>, pp, m);
     stage_end(l);
     return e;
 }

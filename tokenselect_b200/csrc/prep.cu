@@ -31,6 +31,19 @@ cudaError_t launch_rope_tables(float2* score_cs, float2* attn_cs, int d, int n_r
     return cudaGetLastError();
 }
 
+__global__ void lane_order_kernel(const float2* src, float2* dst, int half, int n_rows) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_rows * half) return;
+    const int row = idx / half, i = idx - row * half;
+    dst[(size_t)row * half + lane_order_slot(i, half / 8)] = src[idx];
+}
+
+cudaError_t launch_lane_order_table(const float2* attn_cs, float2* attn_cs_lane, int d, int n_rows, cudaStream_t stream) {
+    const int total = n_rows * (d / 2);
+    lane_order_kernel<<<(total + 255) / 256, 256, 0, stream>>>(attn_cs, attn_cs_lane, d / 2, n_rows);
+    return cudaGetLastError();
+}
+
 // grid = batch, block = 256.
 template <typename T>
 __global__ void __launch_bounds__(256) prep_kernel(const LayerParams p) {
