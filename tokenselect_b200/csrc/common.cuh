@@ -13,7 +13,7 @@ constexpr int kMaxBatch = 256;        // requests per call (plan arrays live in 
 constexpr int kMaxHq = 64;            // query heads per rank
 constexpr int kCandAlign = 128;       // each request's candidate region starts on this multiple
 constexpr int kHistBins = 2048;       // first radix level: vote bits [30:20]
-constexpr int kFusedThreads = 288;    // 1 copy-issuing warp + 8 mma warps
+constexpr int kFusedThreads = 512;    // 1 copy-issuing warp + 8 mma warps + 7 warps that join after scoring
 constexpr int kScoreStages = 5;
 constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stage
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time

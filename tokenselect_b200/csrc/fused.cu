@@ -279,6 +279,7 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
         return;
     }
 
+    if (warp > 8) return;                              // only warps 1..8 multiply
     // ---------------- consumers: 8 warps, one (16-token, kv-head) unit each ----------------
     const int cw = warp - 1;
     const int ctid = tid - 32;
@@ -508,6 +509,18 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// Flush-to-zero form: one MUFU instruction, no range fix-up around it.  Callers keep the argument above
+// -126 where the result matters (see kVoteShift).
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Vote terms are 2^(x*log2e + bias) with a non-positive exponent that can reach far below -126.  The bias
+// carries +kVoteShift and the summed vote is multiplied by 2^-kVoteShift afterwards, so terms down to
+// 2^-149 (the smallest fp32 denormal) are still represented exactly as the plain evaluation would.
+constexpr float kVoteShift = 64.f;
+constexpr float kVoteUnshift = 5.421010862427522e-20f;   // 2^-64
 
 struct VoteGeom {
     int part_bytes, row_bytes, cap_rows;
@@ -623,7 +636,7 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                         const float2 v = lvl[i * hq + tid];
                         if (v.x > -INFINITY) l += v.y * ex2_approx((v.x - m) * kLog2e);
                     }
-                    sh.s_m[tid] = -(m * kLog2e + log2f(l));
+                    sh.s_m[tid] = kVoteShift - (m * kLog2e + log2f(l));
                 }
                 __syncthreads();
             }
@@ -640,21 +653,25 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                     const int c4 = pow2 ? ((k + rot) & (nch - 1)) : k;
                     bbr[k] = k < nch ? *reinterpret_cast<const float4*>(&sh.s_m[c4 * 4]) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
+                const uint32_t rows_u32 = smem_u32(rows_s);
                 for (int t = r0 + tid; t < r1; t += kFusedThreads) {
-                    const unsigned char* row = rows_s + (size_t)(t - r0) * g.row_bytes;
+                    const uint32_t row = rows_u32 + (uint32_t)(t - r0) * (uint32_t)g.row_bytes;
                     float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
 #pragma unroll
                     for (int k = 0; k < 16; ++k) {
                         if (k < nch) {
                             const int c4 = pow2 ? ((k + rot) & (nch - 1)) : k;
-                            const float4 x = *reinterpret_cast<const float4*>(row + c4 * 16);
-                            v0 += ex2_approx(fmaf(x.x, kLog2e, bbr[k].x));
-                            v1 += ex2_approx(fmaf(x.y, kLog2e, bbr[k].y));
-                            v2 += ex2_approx(fmaf(x.z, kLog2e, bbr[k].z));
-                            v3 += ex2_approx(fmaf(x.w, kLog2e, bbr[k].w));
+                            float4 x;
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                                         : "r"(row + c4 * 16));
+                            v0 += ex2_ftz(fmaf(x.x, kLog2e, bbr[k].x));
+                            v1 += ex2_ftz(fmaf(x.y, kLog2e, bbr[k].y));
+                            v2 += ex2_ftz(fmaf(x.z, kLog2e, bbr[k].z));
+                            v3 += ex2_ftz(fmaf(x.w, kLog2e, bbr[k].w));
                         }
                     }
-                    const float v = (v0 + v1) + (v2 + v3);
+                    const float v = ((v0 + v1) + (v2 + v3)) * kVoteUnshift;
                     votes[t] = v;
                     if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
                 }
@@ -662,7 +679,8 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                 for (int t = r0 + tid; t < r1; t += kFusedThreads) {
                     const float* rf = reinterpret_cast<const float*>(rows_s + (size_t)(t - r0) * g.row_bytes);
                     float v = 0.f;
-                    for (int c = 0; c < hq; ++c) v += ex2_approx(fmaf(rf[c], kLog2e, sh.s_m[c]));
+                    for (int c = 0; c < hq; ++c) v += ex2_ftz(fmaf(rf[c], kLog2e, sh.s_m[c]));
+                    v *= kVoteUnshift;
                     votes[t] = v;
                     if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
                 }
