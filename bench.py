@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072)
@@ -74,7 +74,7 @@ class ClockSampler:
     def _run(self):
         try:
             p = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                  "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                  "--format=csv,noheader,nounits", "-lms", "50"], stdout=subprocess.PIPE,
                                  stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
