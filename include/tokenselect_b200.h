@@ -203,6 +203,52 @@ int ts_launch_count(ts_handle* h, uint64_t* launches);
 int ts_timing_begin(ts_handle* h, int32_t max_launches);
 int ts_timing_end(ts_handle* h, double* ms_by_stage, uint64_t* launches_by_stage);
 
+/*
+ * Sparse paged decode attention over a caller-supplied list of pool rows, for callers that must not
+ * allocate.  It has no counterpart in the reference (which allocates freely through torch).
+ *
+ * Meant for code that runs where device allocation is off limits: a host callback or a serving loop that
+ * may not touch the allocator (cudaMalloc can synchronise the device), or a process whose device memory
+ * was handed out in full at start-up and whose owner gives out no more.  Such code cannot call ts_create() (one cudaMalloc), so this call takes no handle: the
+ * split kernel's partial results live in a fixed 4 MiB array inside the library image (every GPU that
+ * loads the library holds it until the process exits).  The call itself performs no cudaMalloc, cudaFree
+ * or other allocating call.
+ *
+ *   - one request per call; `rows` lists `count` pool rows in attention order (the j-th row sits at
+ *     position j, the query at position count-1); arithmetic as in ts_decode_layer's attention;
+ *   - limit: ceil(count/32) * hq * (head_dim + 2) * 4 bytes <= 4 MiB (e.g. count <= 8064 at hq = 32,
+ *     head_dim = 128); longer lists return TS_ERR_CAPACITY;
+ *   - the array is shared by all calls and keeps the last call's contents; nothing in it needs clearing
+ *     (each call writes every partial it later reads), but two calls whose kernels overlap on the GPU
+ *     race on it -- order them on one stream or with events;
+ *   - the first call on a device looks up the array's device address; make that first call before any
+ *     stream capture begins;
+ *   - `status`, if not NULL, is a device int the kernels set to TS_ERR_BAD_SLOT when a listed row lies
+ *     outside [0, pool_rows) (that row is then read as row 0).
+ */
+typedef struct ts_attend_static_args {
+    uint32_t struct_size;          /* sizeof(ts_attend_static_args), checked */
+    int32_t dtype;                 /* TS_DTYPE_* of q, the pools and out */
+    int32_t hq;                    /* query heads */
+    int32_t hkv;                   /* KV heads; hq / hkv <= 8 */
+    int32_t head_dim;              /* 64 or 128 */
+    int32_t count;                 /* listed rows */
+    const void* q;                 /* [hq*head_dim], un-rotated */
+    const void* k_pool;            /* [pool_rows, hkv, head_dim] */
+    const void* v_pool;            /* [pool_rows, hkv, head_dim] */
+    int64_t pool_rows;
+    const int32_t* rows;           /* [count] pool rows, device memory */
+    void* out;                     /* [hq*head_dim] */
+    float sm_scale;
+    float logit_cap;               /* soft cap, used when > 0 */
+    double rope_base;
+    double rope_scale;
+    int32_t* status;               /* optional device int, see above */
+    void* stream;                  /* cudaStream_t */
+} ts_attend_static_args;
+
+int ts_attend_rows_static(const ts_attend_static_args* args);
+
 #ifdef __cplusplus
 }
 #endif

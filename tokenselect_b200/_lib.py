@@ -23,7 +23,7 @@ EXPORTS = [
     "ts_abi_version", "ts_status_string", "ts_query_workspace", "ts_vote_buffer_elems", "ts_create",
     "ts_destroy", "ts_reset_request", "ts_decode_layer", "ts_tp_prepare", "ts_tp_score_vote",
     "ts_tp_select_attend", "ts_get_counters", "ts_last_error", "ts_last_cuda_error", "ts_debug_read",
-    "ts_launch_count", "ts_timing_begin", "ts_timing_end",
+    "ts_launch_count", "ts_timing_begin", "ts_timing_end", "ts_attend_rows_static",
 ]
 
 
@@ -49,6 +49,16 @@ class TsDecodeArgs(C.Structure):
         ("seq_lens", C.c_void_p), ("out", C.c_void_p), ("tp_votes", C.c_void_p), ("tp_cos", C.c_void_p),
         ("dbg_sel_slots", C.c_void_p), ("dbg_sel_pos", C.c_void_p), ("dbg_sel_count", C.c_void_p),
         ("dbg_flags", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class TsAttendStaticArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("dtype", C.c_int32), ("hq", C.c_int32), ("hkv", C.c_int32),
+        ("head_dim", C.c_int32), ("count", C.c_int32), ("q", C.c_void_p), ("k_pool", C.c_void_p),
+        ("v_pool", C.c_void_p), ("pool_rows", C.c_int64), ("rows", C.c_void_p), ("out", C.c_void_p),
+        ("sm_scale", C.c_float), ("logit_cap", C.c_float), ("rope_base", C.c_double), ("rope_scale", C.c_double),
+        ("status", C.c_void_p), ("stream", C.c_void_p),
     ]
 
 
@@ -85,6 +95,7 @@ def load() -> C.CDLL:
     lib.ts_launch_count.argtypes = [H, C.POINTER(C.c_uint64)]
     lib.ts_timing_begin.argtypes = [H, C.c_int32]
     lib.ts_timing_end.argtypes = [H, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
+    lib.ts_attend_rows_static.argtypes = [C.POINTER(TsAttendStaticArgs)]
     if lib.ts_abi_version() != TS_ABI_VERSION:
         raise RuntimeError("libtokenselect_b200.so was built from a different header; rebuild it")
     _lib = lib

@@ -309,3 +309,27 @@ class TokenSelectEngine:
             nc = max(int(n) - n_init - n_local, 0)
             total += (nc + 127) // 128 * 128
         return total
+
+
+def attend_rows_static(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, rows: torch.Tensor,
+                       out: torch.Tensor, sm_scale: float, rope_base: float, rope_scale: float = 1.0,
+                       logit_cap: float = 0.0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Attention of one request over the listed pool rows through ``ts_attend_rows_static``, the entry
+    point for callers that are not allowed to allocate device memory (a serving loop or callback that must
+    stay off the allocator, or a process whose memory another component owns in full): it needs no engine, writes its
+    intermediate results to a fixed array inside the library and allocates nothing.  ``out`` must be
+    supplied by the caller for the same reason.  At most ``4 MiB / (heads * (head_dim + 2) * 4)`` chunks
+    of 32 rows; calls that overlap on the GPU race on the shared array, so keep them on one stream."""
+    lib = _lib.load()
+    hq = q.numel() // k_pool.shape[2]
+    a = _lib.TsAttendStaticArgs()
+    a.struct_size = C.sizeof(_lib.TsAttendStaticArgs)
+    a.dtype = _lib.TS_DTYPE_BF16 if q.dtype == torch.bfloat16 else _lib.TS_DTYPE_F32
+    a.hq, a.hkv, a.head_dim, a.count = hq, k_pool.shape[1], k_pool.shape[2], rows.numel()
+    a.q, a.k_pool, a.v_pool, a.pool_rows = q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0]
+    a.rows, a.out = rows.data_ptr(), out.data_ptr()
+    a.sm_scale, a.logit_cap, a.rope_base, a.rope_scale = sm_scale, logit_cap, float(rope_base), float(rope_scale)
+    a.status = None if status is None else status.data_ptr()
+    a.stream = torch.cuda.current_stream(q.device).cuda_stream
+    check(lib.ts_attend_rows_static(C.byref(a)), "ts_attend_rows_static")
+    return out
