@@ -49,9 +49,14 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ctx", type=int, default=131072)
     ap.add_argument("--layers", type=int, default=LAYERS)
-    ap.add_argument("--query-cache", action="store_true", help="selection cache on (threshold 0.9)")
+    ap.add_argument("--query-cache", action="store_true", help="selection cache on")
+    ap.add_argument("--threshold", type=float, default=0.9, help="cosine threshold of the selection cache")
+    ap.add_argument("--rho", type=float, default=None,
+                    help="AR(1) correlation of consecutive decode queries, q_t = rho*q_(t-1) + sqrt(1-rho^2)*eps")
     ap.add_argument("--contiguous-slots", action="store_true", help="pool rows in position order")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp-split", action="store_true",
+                    help="tensor parallel: host-driven NCCL all-reduce between two kernels instead of the in-kernel sum")
     ap.add_argument("--seed", type=int, default=2024)
     return ap.parse_args()
 
@@ -246,6 +251,9 @@ def main():
     for li in range(layers):
         kv_of_h = torch.arange(hq, device=dev) % hkv
         qs[:, li] += 2.0 * (D ** 0.5) * dirs[li][kv_of_h] / 4
+    if args.rho is not None:          # cache-stress workload: consecutive queries of a layer are correlated
+        for t in range(1, total_steps):
+            qs[t] = args.rho * qs[t - 1] + (1.0 - args.rho ** 2) ** 0.5 * qs[t]
     qs = qs.to(torch.bfloat16).reshape(total_steps, layers, 1, hq * D).contiguous()
     ks = torch.randn(total_steps, layers, 1, hkv * D, generator=gr, device=dev).to(torch.bfloat16)
     vs = torch.randn(total_steps, layers, 1, hkv * D, generator=gr, device=dev).to(torch.bfloat16)
@@ -256,7 +264,9 @@ def main():
 
     cfg = TokenSelectConfig(rope_base=ROPE_BASE, max_n_tokens=max_ctx, top_k=TOP_K, n_init=N_INIT, n_local=N_LOCAL,
                             n_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=D, max_reqs=2, max_batch=1,
-                            max_total_tokens=max_ctx, query_cache=args.query_cache, tp_rank=rank, tp_size=tp)
+                            max_total_tokens=max_ctx, query_cache=args.query_cache,
+                            similarity_threshold=args.threshold, tp_rank=rank, tp_size=tp,
+                            tp_fused=not args.tp_split)
     eng = TokenSelectEngine(cfg, device=dev)
     eng.reset_request(1)
     ve = eng.vote_elems_for([max_ctx], N_INIT, N_LOCAL)
@@ -291,6 +301,7 @@ def main():
     clocks = sampler.stop()
     launches = eng.launch_count - launches0
     eng.raise_on_device_error()
+    retrievals, reuses = eng.counters(1) if args.query_cache else (0, 0)
     if tp > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -350,8 +361,10 @@ def main():
                                    f"attention), bs=1, ctx={ctx}, {layers} layers, top_k={TOP_K}, n_init={N_INIT}, "
                                    f"n_local={N_LOCAL}, page size 1, "
                                    f"{'contiguous' if args.contiguous_slots else 'permuted'} pool rows, "
-                                   f"query_cache={'on' if args.query_cache else 'off'}",
-                       "parallelism": f"tp{tp} by KV head" if tp > 1 else "single GPU",
+                                   f"query_cache={'on (threshold %g, rho %s)' % (args.threshold, args.rho) if args.query_cache else 'off'}",
+                       "parallelism": (f"tp{tp} by KV head, votes summed "
+                                       f"{'in the kernel over NVLink peer memory' if eng.fused_tp else 'by NCCL all-reduce'}")
+                       if tp > 1 else "single GPU",
                        "l2": "inputs larger than L2: each layer streams its own 268 MB of keys"},
             "us_per_layer": us_layer,
             "layer_roofline": {"bytes": ab["layer"], "achieved_gbs": ab["layer"] / (us_layer * 1e-6) / 1e9,
@@ -361,12 +374,19 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "fused_select_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                          "peak_source": peak_kind, "bytes_per_launch": ab["select"],
-                         "us_per_launch": score_us, "traffic": None},
+                         "us_per_launch": score_us,
+                         # dram read+write of one launch from the ncu capture in profiles/ (277.77 MB at
+                         # 267.68 MB algorithmic), scaled with the algorithmic bytes; single-GPU shape only
+                         "traffic": (ab["select"] * 277.77 / 267.68) if tp == 1 else None},
             "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if args.query_cache:
+            line["selection_cache"] = {"threshold": args.threshold, "rho": args.rho, "decisions": int(retrievals),
+                                       "reuses": int(reuses),
+                                       "reuse_rate": (reuses / retrievals) if retrievals else None}
         if tp == 1 and not args.no_cpu_baseline:
             times, threads = cpu_layer_times(ctx, 3, args.seed)
             mean = sum(times) / len(times)

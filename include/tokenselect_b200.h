@@ -153,7 +153,7 @@ int ts_destroy(ts_handle* h);
  * and counters.  Replaces get_token_retriever()'s fresh TokenRetriever (:147-163, :322-327). */
 int ts_reset_request(ts_handle* h, int32_t req_slot, void* stream);
 
-/* Whole layer step on one GPU: append K/V, select, attend.  Replaces
+/* Whole layer step in one call: append K/V, select, attend (with tp_size > 1: after ts_tp_attach_peers).  Replaces
  * patched_radix_attention_decode_forward_flashinfer (:777-825) with store_kv_cache (:844-854)
  * and retrieval_indices (:375-449). */
 int ts_decode_layer(ts_handle* h, const ts_decode_args* args);
@@ -167,6 +167,17 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* args);
 int ts_tp_prepare(ts_handle* h, const ts_decode_args* args);
 int ts_tp_score_vote(ts_handle* h, const ts_decode_args* args);
 int ts_tp_select_attend(ts_handle* h, const ts_decode_args* args);
+
+/* Tensor-parallel exchange inside the selection kernel (replaces the host-driven all-reduce of
+ * :363-364 with loads from the peers' memory over NVLink).  Every rank allocates a buffer of
+ * ts_tp_symmetric_bytes() that its peers can address (CUDA IPC / symmetric memory; zero-filled), then
+ * passes the device addresses of ALL ranks' buffers, in rank order, to ts_tp_attach_peers().  After that
+ * ts_decode_layer() works with tp_size > 1: each rank writes its raw votes to its own buffer, flags its
+ * peers, waits (bounded) for theirs and sums the ranks' votes in rank order, so all ranks select from
+ * bit-identical sums.  All ranks must issue the same sequence of calls.  Not available with the selection
+ * cache on (its cosine terms would need a second exchange): use the three ts_tp_* calls then. */
+int ts_tp_symmetric_bytes(const ts_config* cfg, size_t* bytes);
+int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count);
 
 /* Selection-cache counters of a request slot (retrieval_count / skip_count, :150-161, :420-421).
  * Synchronises the stream given. */

@@ -23,7 +23,7 @@ EXPORTS = [
     "ts_abi_version", "ts_status_string", "ts_query_workspace", "ts_vote_buffer_elems", "ts_create",
     "ts_destroy", "ts_reset_request", "ts_decode_layer", "ts_tp_prepare", "ts_tp_score_vote",
     "ts_tp_select_attend", "ts_get_counters", "ts_last_error", "ts_last_cuda_error", "ts_debug_read",
-    "ts_launch_count", "ts_timing_begin", "ts_timing_end", "ts_attend_rows_static",
+    "ts_launch_count", "ts_timing_begin", "ts_timing_end", "ts_attend_rows_static", "ts_tp_symmetric_bytes", "ts_tp_attach_peers",
 ]
 
 
@@ -96,6 +96,8 @@ def load() -> C.CDLL:
     lib.ts_timing_begin.argtypes = [H, C.c_int32]
     lib.ts_timing_end.argtypes = [H, C.POINTER(C.c_double), C.POINTER(C.c_uint64)]
     lib.ts_attend_rows_static.argtypes = [C.POINTER(TsAttendStaticArgs)]
+    lib.ts_tp_symmetric_bytes.argtypes = [C.POINTER(TsConfig), C.POINTER(C.c_size_t)]
+    lib.ts_tp_attach_peers.argtypes = [H, C.POINTER(C.c_uint64), C.c_int32]
     if lib.ts_abi_version() != TS_ABI_VERSION:
         raise RuntimeError("libtokenselect_b200.so was built from a different header; rebuild it")
     _lib = lib

@@ -22,6 +22,12 @@ struct ts_handle {
     LayerParams base;             // workspace pointers and configuration, call fields empty
     unsigned long long launches;
     StageTimer timer;
+    // tensor-parallel exchange through peer memory
+    bool peers_attached;
+    unsigned tp_epoch;
+    unsigned char* peer_base[kMaxTp];      // every rank's symmetric buffer (host copy)
+    float** dev_peer_votes;                 // [2][kMaxTp] device array of pointers
+    unsigned** dev_peer_flags;              // [kMaxTp]
     int last_batch;
     char cuda_msg[256];
 };
@@ -84,6 +90,8 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_sure = cv.take((size_t)c->max_batch * grid * 4);
     size_t o_bar = cv.take(16);
     size_t o_ts = cv.take(64 * 8);
+    size_t o_pv = cv.take(2 * kMaxTp * sizeof(void*));
+    size_t o_pf = cv.take(kMaxTp * sizeof(void*));
     size_t o_cand = cv.take((size_t)cap * 8);
     size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
     size_t o_pos = cv.take((size_t)c->max_batch * n_sel * 4);
@@ -118,11 +126,15 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.votes = reinterpret_cast<float*>(a + o_votes);
         p.votes_pool = reinterpret_cast<float*>(a + o_vpool);
         p.votes_sel = c->kernel_size > 0 ? p.votes_pool : p.votes;
+        p.votes_final = p.votes;
+        p.tp_rank = c->tp_rank;
         p.hist = reinterpret_cast<unsigned*>(a + o_hist);
         p.cand_count = reinterpret_cast<unsigned*>(a + o_ccount);
         p.sure_count = reinterpret_cast<unsigned*>(a + o_sure);
         p.grid_bar = reinterpret_cast<unsigned*>(a + o_bar);
         p.phase_ts = reinterpret_cast<unsigned long long*>(a + o_ts);
+        h->dev_peer_votes = reinterpret_cast<float**>(a + o_pv);
+        h->dev_peer_flags = reinterpret_cast<unsigned**>(a + o_pf);
         p.cand = reinterpret_cast<uint2*>(a + o_cand);
         p.sel_slots = reinterpret_cast<int*>(a + o_slots);
         p.sel_pos = reinterpret_cast<int*>(a + o_pos);
@@ -156,7 +168,11 @@ int num_sms_of(int device, int* out) {
     return TS_OK;
 }
 
-int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l) {
+size_t sym_flag_bytes() { return (size_t)2 * kMaxTp * kFlagPad * sizeof(unsigned); }
+size_t sym_votes_offset(long long cap, int parity) { return sym_flag_bytes() + (size_t)parity * (size_t)cap * sizeof(float); }
+size_t sym_total_bytes(long long cap) { return sym_votes_offset(cap, 2); }
+
+int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l, bool fused_tp = false) {
     if (!h || !a || a->struct_size != sizeof(ts_decode_args)) return TS_ERR_INVALID_ARG;
     if (a->layer < 0 || a->layer >= h->cfg.n_layers) return TS_ERR_INVALID_ARG;
     if (a->batch < 1) return TS_ERR_INVALID_ARG;
@@ -172,11 +188,24 @@ int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l) {
     p.k_pool = a->k_pool; p.v_pool = a->v_pool; p.pool_rows = a->pool_rows;
     p.rtt = a->req_to_token; p.rtt_stride = a->req_to_token_stride;
     p.req_pool_indices = a->req_pool_indices; p.seq_lens = a->seq_lens; p.out = a->out;
-    if (h->cfg.tp_size > 1) {
+    if (h->cfg.tp_size > 1 && !fused_tp) {
         if (!a->tp_votes || !a->tp_cos) return TS_ERR_INVALID_ARG;
         p.votes = a->tp_votes;
+        p.votes_final = a->tp_votes;
         p.cos_terms = a->tp_cos;
         if (h->cfg.kernel_size <= 0) p.votes_sel = p.votes;
+    }
+    if (fused_tp) {
+        // raw votes go to this rank's symmetric buffer (parity alternates per call so that a fast rank
+        // never overwrites votes a slow peer is still reading); the sum lands in the workspace
+        const unsigned epoch = ++h->tp_epoch;
+        const int parity = (int)(epoch & 1u);
+        p.epoch = epoch;
+        p.flag_parity = parity;
+        p.peer_votes = h->dev_peer_votes + parity * kMaxTp;
+        p.peer_flags = h->dev_peer_flags;
+        p.votes = reinterpret_cast<float*>(h->peer_base[h->cfg.tp_rank] + sym_votes_offset(h->cand_capacity, parity));
+        p.votes_final = h->base.votes;
     }
     l.stream = reinterpret_cast<cudaStream_t>(a->stream);
     l.num_sms = h->num_sms;
@@ -335,15 +364,43 @@ int ts_tp_select_attend(ts_handle* h, const ts_decode_args* a) {
     return copy_debug(h, a, p, l.stream);
 }
 
+int ts_tp_symmetric_bytes(const ts_config* cfg, size_t* bytes) {
+    int s = validate(cfg);
+    if (s != TS_OK) return s;
+    if (!bytes) return TS_ERR_INVALID_ARG;
+    *bytes = sym_total_bytes(cand_capacity_of(cfg));
+    return TS_OK;
+}
+
+int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count) {
+    if (!h || !peer_buffers || count != h->cfg.tp_size || count > kMaxTp) return TS_ERR_INVALID_ARG;
+    float* votes[2 * kMaxTp] = {nullptr};
+    unsigned* flags[kMaxTp] = {nullptr};
+    for (int r = 0; r < count; ++r) {
+        if (!peer_buffers[r]) return TS_ERR_INVALID_ARG;
+        h->peer_base[r] = reinterpret_cast<unsigned char*>(peer_buffers[r]);
+        flags[r] = reinterpret_cast<unsigned*>(h->peer_base[r]);
+        for (int par = 0; par < 2; ++par)
+            votes[par * kMaxTp + r] = reinterpret_cast<float*>(h->peer_base[r] + sym_votes_offset(h->cand_capacity, par));
+    }
+    TS_TRY(cudaMemcpy(h->dev_peer_votes, votes, sizeof(votes), cudaMemcpyHostToDevice), "peer table");
+    TS_TRY(cudaMemcpy(h->dev_peer_flags, flags, sizeof(flags), cudaMemcpyHostToDevice), "peer table");
+    h->peers_attached = true;
+    h->tp_epoch = 0;
+    return TS_OK;
+}
+
 int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
-    if (h && h->cfg.tp_size > 1) {
-        // single call without the exchange: each rank would select from its own votes only
-        return TS_ERR_INVALID_ARG;
+    const bool fused_tp = h && h->cfg.tp_size > 1;
+    if (fused_tp) {
+        // needs the peers' buffers; the cosine terms of the selection cache are not exchanged in this form
+        if (!h->peers_attached) return TS_ERR_INVALID_ARG;
+        if (h->cfg.query_cache) return TS_ERR_UNSUPPORTED;
     }
     LayerParams p; Launch l;
-    int s = fill(h, a, p, l);
+    int s = fill(h, a, p, l, fused_tp);
     if (s != TS_OK) return s;
-    TS_TRY(launch_fused(p, l, kModeAll), "select");
+    TS_TRY(launch_fused(p, l, fused_tp ? kModeTpFused : kModeAll), "select");
     TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);
 }

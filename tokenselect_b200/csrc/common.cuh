@@ -17,6 +17,8 @@ constexpr int kFusedThreads = 512;    // 1 copy-issuing warp + 8 mma warps + 7 w
 constexpr int kScoreStages = 5;
 constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stage
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
+constexpr int kFlagPad = 256;          // per-CTA flags per (parity, source rank) in the tensor-parallel flag pad
+constexpr int kMaxTp = 8;
 constexpr int kFusedDynSmem = 174080; // dynamic shared memory of the selection kernel (5 stages of 34 KB)
 constexpr int kAttnThreads = 256;
 constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
@@ -54,13 +56,19 @@ struct LayerParams {
     int grid;                  // CTAs of the selection kernel (one per SM)
     int tile_tokens;           // candidates per work tile; fixes which CTA owns which candidates
     float* votes;              // [cand_capacity] head-summed softmax
-    float* votes_sel;          // votes the selection reads (== votes, or the pooled copy)
+    float* votes_sel;          // votes exposed for inspection (== votes_final, or the pooled copy)
+    float* votes_final;        // votes the selection reads: == votes, or the tensor-parallel sum
     float* votes_pool;         // [cand_capacity] max-pooled votes
     unsigned* hist;            // [max_batch, kHistBins]
     uint2* cand;               // [cand_capacity] (candidate index, vote bits) of the threshold bin
     unsigned* cand_count;      // [max_batch] entries of `cand` per request
     unsigned* sure_count;      // [max_batch, grid] winners above the threshold bin, per CTA
     unsigned* grid_bar;        // [1] self-resetting grid barrier word
+    // tensor-parallel exchange over peer memory (mode kModeTpFused)
+    float* const* peer_votes;  // [tp_size] every rank's raw-vote buffer of this call's parity (own included)
+    unsigned* const* peer_flags;  // [tp_size] every rank's flag pad [2][tp_size][kFlagPad]
+    unsigned epoch;            // value the flags of this call carry
+    int tp_rank, flag_parity;
     unsigned long long* phase_ts;  // [16] nanosecond timestamps of CTA 0 at the phase boundaries
     int* sel_slots;            // [max_batch, n_sel]
     int* sel_pos;              // [max_batch, n_sel]
@@ -217,6 +225,7 @@ enum FusedMode {
     kModeAll = 0,   // prepare, score, vote, top-k, emit (single GPU)
     kModeTpA = 1,   // decide, score, vote -> raw votes (before the tensor-parallel sum)
     kModeTpB = 2,   // histogram of the summed votes, top-k, emit
+    kModeTpFused = 3,  // like kModeAll, with the vote sum over ranks done in the kernel through peer memory
 };
 
 cudaError_t launch_prep(const LayerParams& p, const Launch& l);

@@ -692,6 +692,59 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
     }
 }
 
+// phase 2x (tensor parallel, fused form): every CTA tells the same-numbered CTA of every peer that
+// its raw votes are written, waits for theirs, and sums the ranks' votes of its own candidates in rank
+// order (so every rank gets bit-identical sums).  Replaces dist.all_reduce (token_retrieval.py:363-364).
+// All ranks run the same plan, hence the same ownership.  The wait is bounded.
+__device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedShared& sh, bool with_hist, bool& dead) {
+    const int tid = threadIdx.x;
+    const int tp = p.tp_size, me = p.tp_rank;
+    __syncthreads();                                   // this CTA's raw votes are written
+    if (tid < tp && tid != me) {
+        __threadfence_system();
+        unsigned* dst = p.peer_flags[tid] + ((size_t)(p.flag_parity * tp + me) * kFlagPad + blockIdx.x);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(p.epoch) : "memory");
+        const unsigned* src = p.peer_flags[me] + ((size_t)(p.flag_parity * tp + tid) * kFlagPad + blockIdx.x);
+        const long long t0 = clock64();
+        unsigned v = 0, spins = 0;
+        while (!dead) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+            if (v == p.epoch) break;
+            if ((++spins & 63u) == 0u && clock64() - t0 > kWaitCycles) {
+                set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + tid);
+                dead = true;
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
+    __syncthreads();
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const size_t off = (size_t)sh.plan.off[sg.b];
+        float* out = p.votes_final + off;
+        for (int t = sg.t0 + 4 * tid; t < sg.t1; t += 4 * kFusedThreads) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < tp; ++r) {
+                const float* src = p.peer_votes[r] + off + t;
+                float4 x;
+                asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
+                             : "l"(src));
+                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+            }
+            *reinterpret_cast<float4*>(out + t) = acc;
+            if (with_hist) {
+                atomicAdd(&sh.hist[vote_bin(acc.x)], 1u);
+                if (t + 1 < sg.t1) atomicAdd(&sh.hist[vote_bin(acc.y)], 1u);
+                if (t + 2 < sg.t1) atomicAdd(&sh.hist[vote_bin(acc.z)], 1u);
+                if (t + 3 < sg.t1) atomicAdd(&sh.hist[vote_bin(acc.w)], 1u);
+            }
+        }
+        if (with_hist) flush_hist(p, sh, sg.b);
+    }
+}
+
 // phase 2': histogram from final votes (after a tensor-parallel sum and/or max-pool); pooled votes
 // are also written out for inspection.
 __device__ __forceinline__ void hist_phase(const LayerParams& p, FusedShared& sh) {
@@ -702,7 +755,7 @@ __device__ __forceinline__ void hist_phase(const LayerParams& p, FusedShared& sh
         const Seg sg = sh.seg[s];
         const int nc = sh.plan.nc[sg.b];
         const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
-        const float* votes = p.votes + sh.plan.off[sg.b];
+        const float* votes = p.votes_final + sh.plan.off[sg.b];
         int own0, own1, per;
         own_range(sg.t0, t1, own0, own1, per);
         for (int beg = own0; beg < own1; beg += kTokBatch) {
@@ -732,7 +785,7 @@ __device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& 
         const Seg sg = sh.seg[s];
         const int nc = sh.plan.nc[sg.b];
         const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
-        const float* votes = p.votes + sh.plan.off[sg.b];
+        const float* votes = p.votes_final + sh.plan.off[sg.b];
         uint2* cand = p.cand + sh.plan.off[sg.b];
         int own0, own1, per;
         own_range(sg.t0, t1, own0, own1, per);
@@ -857,7 +910,7 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
         const uint2* cand_g = p.cand + sh.plan.off[sg.b];
         const int nc = sh.plan.nc[sg.b];
         const int t1 = min(sg.t1, pooled_len(nc, p.kernel_size));
-        const float* votes = p.votes + sh.plan.off[sg.b];
+        const float* votes = p.votes_final + sh.plan.off[sg.b];
         int own0, own1, per;
         own_range(sg.t0, t1, own0, own1, per);
 
@@ -999,7 +1052,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     if (mode != kModeTpB) {
         if (ok) {
             for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
-                if (mode == kModeAll) prepare_request<T, true>(p, b, sh.prep);
+                if (mode == kModeAll || mode == kModeTpFused) prepare_request<T, true>(p, b, sh.prep);
                 else if (p.query_cache) decide_request<T>(p, b, sh.prep);
             }
         }
@@ -1042,6 +1095,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
 
     const bool pooled = p.kernel_size > 0;
     stamp(p, 1);
+    // Nothing recomputes (every request reuses its cached set or attends to everything): every CTA sees
+    // the same empty plan, so all of them skip the scoring phases and their barriers together.  In the
+    // fused tensor-parallel form the ranks decide alike for the same reason.
+    if (sh.tile_off[p.batch] == 0) {
+        if (ok && mode != kModeTpA) emit_windows(p, sh);
+        stamp(p, 8);
+        return;
+    }
     if (mode != kModeTpB) {
         // ---- phase 1: score ----
         if (ok) {
@@ -1064,6 +1125,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead);
         stamp(p, 4);
         if (mode == kModeTpA) return;
+        if (mode == kModeTpFused) tp_exchange_phase(p, sh, ok && !pooled, dead);
         if (pooled) {
             grid_barrier(p, dead);
             if (ok) hist_phase(p, sh);

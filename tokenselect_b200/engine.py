@@ -49,6 +49,7 @@ class TokenSelectConfig:
     tp_rank: int = 0
     tp_size: int = 1
     plain_score: bool = False              # diagnostic: plain-load scoring kernel for bf16 too
+    tp_fused: bool = True                  # tp_size > 1: sum the votes inside the kernel through peer memory
 
     @property
     def n_sel(self) -> int:
@@ -130,10 +131,37 @@ class TokenSelectEngine:
         with torch.cuda.device(self.device):
             check(self.lib.ts_create(C.byref(c), C.byref(self._h)), "ts_create")
         self.tp_votes = self.tp_cos = None
+        self.fused_tp = False
         if cfg.tp_size > 1:
             self.tp_votes = torch.zeros(self.vote_elems, dtype=torch.float32, device=self.device)
             self.tp_cos = torch.zeros(cfg.max_batch * 4, dtype=torch.float32, device=self.device)
+            if cfg.tp_fused and not cfg.query_cache:
+                self._attach_peers()
         self._rids: Dict[int, object] = {}
+
+    def _attach_peers(self) -> None:
+        """Give the library every rank's exchange buffer (torch symmetric memory over NVLink) so that the
+        selection kernel can sum the ranks' votes itself instead of the host calling all_reduce between
+        two kernels (token_retrieval.py:363-364).  Needs an initialised NCCL process group."""
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized():
+            return
+        import torch.distributed._symmetric_memory as symm_mem
+        nbytes = C.c_size_t()
+        check(self.lib.ts_tp_symmetric_bytes(C.byref(self._c), C.byref(nbytes)), "ts_tp_symmetric_bytes")
+        group = self.group if self.group is not None else dist.group.WORLD
+        self._symm = symm_mem.empty(nbytes.value, dtype=torch.uint8, device=self.device)
+        self._symm.zero_()
+        handle = symm_mem.rendezvous(self._symm, group)
+        ptrs = [int(x) for x in handle.buffer_ptrs]
+        if len(ptrs) != self.cfg.tp_size or handle.rank != self.cfg.tp_rank:
+            raise RuntimeError("symmetric-memory group does not match tp_rank / tp_size")
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)                 # every buffer is zeroed before anyone raises a flag
+        arr = (C.c_uint64 * len(ptrs))(*ptrs)
+        check(self.lib.ts_tp_attach_peers(self._h, arr, len(ptrs)), "ts_tp_attach_peers", self._h)
+        self._symm_handle = handle
+        self.fused_tp = True
 
     # ------------------------------------------------------------------------------------------
     def close(self) -> None:
@@ -272,7 +300,7 @@ class TokenSelectEngine:
             out = torch.empty_like(q)
         a = self._args(layer, q, k_new, v_new, out_cache_loc, k_pool, v_pool, req_to_token,
                        req_pool_indices, seq_lens, out, debug)
-        if self.cfg.tp_size == 1:
+        if self.cfg.tp_size == 1 or self.fused_tp:
             check(self.lib.ts_decode_layer(self._h, C.byref(a)), "ts_decode_layer", self._h)
             return out
         import torch.distributed as dist
