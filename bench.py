@@ -55,8 +55,13 @@ def parse_args():
                     help="AR(1) correlation of consecutive decode queries, q_t = rho*q_(t-1) + sqrt(1-rho^2)*eps")
     ap.add_argument("--contiguous-slots", action="store_true", help="pool rows in position order")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--score-path", default="auto", choices=["auto", "direct", "staged"])
     ap.add_argument("--tp-split", action="store_true",
                     help="tensor parallel: host-driven NCCL all-reduce between two kernels instead of the in-kernel sum")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="diagnostic: run ONE rank's share of an N-way KV-head split on a single GPU, no exchange")
+    ap.add_argument("--phase-times", action="store_true",
+                    help="print the selection kernel's phase split (CTA 0 timestamps of the last launch) to stderr")
     ap.add_argument("--seed", type=int, default=2024)
     return ap.parse_args()
 
@@ -224,7 +229,7 @@ def main():
     torch.cuda.set_device(dev)
     if tp > 1:
         dist.init_process_group("nccl", device_id=dev)
-    hq, hkv = HQ // tp, HKV // tp
+    hq, hkv = HQ // (tp * args.shard_of), HKV // (tp * args.shard_of)
     ctx, layers, total_steps = args.ctx, args.layers, args.warmup + args.steps
     n_sel = N_INIT + TOP_K + N_LOCAL
     rows = ctx + 2 * total_steps + 64
@@ -266,7 +271,7 @@ def main():
                             n_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=D, max_reqs=2, max_batch=1,
                             max_total_tokens=max_ctx, query_cache=args.query_cache,
                             similarity_threshold=args.threshold, tp_rank=rank, tp_size=tp,
-                            tp_fused=not args.tp_split)
+                            tp_fused=not args.tp_split, score_path=args.score_path)
     eng = TokenSelectEngine(cfg, device=dev)
     eng.reset_request(1)
     ve = eng.vote_elems_for([max_ctx], N_INIT, N_LOCAL)
@@ -343,6 +348,13 @@ def main():
     stages = eng.timing_end()
     eng.raise_on_device_error()
 
+    if args.phase_times:
+        ts = eng.debug_read(3, 64, torch.int64).tolist()
+        names = ["prepare+plan", "score", "barrier", "vote", "barrier/exchange", "filter", "barrier", "emit"]
+        split = {n: (ts[i + 1] - ts[i]) / 1e3 for i, n in enumerate(names)}
+        if tp > 1 and eng.fused_tp:
+            split["vote->exchange done"] = (ts[24] - ts[4]) / 1e3
+        print(f"[rank {rank}] selection kernel phases (us): {split}", file=sys.stderr, flush=True)
     if rank == 0:
         ab = algorithmic_bytes(ctx + args.warmup + args.steps // 2, hq, hkv, D)
         peak, peak_kind = hbm_peak()

@@ -27,6 +27,11 @@ SHAPES = [
     ("llama_tp8_bf16", 4, 1, 128, 5000, 16, 64, 256, 5e5, BF16, {}),
     ("qwen_tp4_bf16", 7, 1, 128, 3001, 16, 64, 300, 1e6, BF16, {}),
     ("divmap_bf16", 8, 2, 128, 2500, 16, 64, 256, 5e5, BF16, {"gqa_map": "div"}),
+    # the two bf16 scoring paths forced against their default row sizes
+    ("direct_llama_tp1", 32, 8, 128, 8192, 128, 512, 1024, 5e5, BF16, {"score_path": "direct"}),
+    ("direct_qwen_tp1", 28, 4, 128, 4096, 128, 512, 512, 1e6, BF16, {"score_path": "direct"}),
+    ("direct_llama_tp4", 8, 2, 128, 3000, 16, 64, 256, 5e5, BF16, {"score_path": "direct"}),
+    ("direct_llama_tp8", 4, 1, 128, 5000, 16, 64, 256, 5e5, BF16, {"score_path": "direct"}),
     ("plain_bf16", 8, 2, 128, 2048, 16, 64, 256, 5e5, BF16, {"plain_score": True}),
     ("fp32_check", 32, 8, 128, 8192, 128, 512, 1024, 5e5, F32, {}),
     ("fp32_d64_mha", 4, 4, 64, 1024, 8, 32, 128, 1e4, F32, {}),

@@ -42,6 +42,7 @@ namespace ts {
 
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kWarps = kFusedThreads / 32;
+constexpr int kBulkMinHkv = 4;        // staged scoring: bulk copies for rows of more than this many KV heads
 
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // CTA 0 leaves a nanosecond timestamp at every phase boundary (read back with ts_debug_read).
@@ -64,7 +65,7 @@ struct FusedShared {
     Seg seg[kMaxBatch];
     int nseg;
     PrepShared prep;
-    float2 stats[8][8];               // [mma warp][column]
+    float2 stats[16][8];              // [warp][column]
     __align__(16) float s_m[kMaxHq];   // per-head bias of the vote exponent
     unsigned long long stage_bar;      // mbarrier of the vote phase's staging copies
     unsigned hist[kHistBins];
@@ -202,7 +203,20 @@ __device__ __forceinline__ T rotated_q(const LayerParams& p, const T* q, int h, 
 // ------------------------------------------------------------------------------------------
 // phase 1, bf16: TMA ring + mma
 // ------------------------------------------------------------------------------------------
-template <int HKV>
+__device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_16_stream(uint32_t dst, const void* src, uint64_t pol) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(pol) : "memory");
+}
+// This thread's arrival on the mbarrier happens when all its earlier cp.async copies have landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// kBulk: one bulk copy (TMA engine) per key row, issued by warp 0 -- right for long rows.
+// !kBulk: the eight warps that do not multiply (0 and 9..15) copy the rows in 16-byte pieces with
+// cp.async, each thread arriving on the stage's mbarrier when its pieces have landed -- right for short
+// rows, where the per-copy cost of the bulk engine would bound the rate.
+template <int HKV, bool kBulk>
 __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShared& sh, unsigned char* ring, bool& dead) {
     using G = ScoreGeom<HKV>;
     const int tid = threadIdx.x;
@@ -211,7 +225,54 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
     const int cta = blockIdx.x;
     const int hq = p.hq, group = p.group;
 
-    if (warp == 0) {
+    if (!kBulk && (warp == 0 || warp > 8)) {
+        // ---------------- eight copying warps ----------------
+        const int ptid = (warp == 0 ? 0 : warp - 8) * 32 + lane;         // 0..255
+        const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
+        const uint64_t pol = l2_evict_first_policy();
+        constexpr int kChunksPerRow = HKV * 16;                           // 16-byte pieces of a key row
+        constexpr int kChunksPerThread = kScoreStageUnits * 16 / 256;     // 8
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int s = 0; s < sh.nseg; ++s) {
+            const Seg sg = sh.seg[s];
+            const int* row = p.rtt + (long long)p.req_pool_indices[sg.b] * p.rtt_stride + p.n_init;
+            for (int tb0 = sg.t0; tb0 < sg.t1; tb0 += 2 * kIdxBlock) {
+                const int nidx = min(2 * kIdxBlock, sg.t1 - tb0);
+                int* idx = &sh.idx[0][0];
+                producer_bar();                                          // the previous block's rows are all issued
+                for (int i = ptid; i < nidx; i += 256) {
+                    int v = __ldg(row + tb0 + i);
+                    if ((unsigned long long)(long long)v >= (unsigned long long)p.pool_rows) {
+                        set_error(p.err, TS_ERR_BAD_SLOT, v);
+                        v = 0;
+                    }
+                    idx[i] = v;
+                }
+                producer_bar();
+                for (int t0 = 0; t0 < nidx; t0 += G::kTok) {
+                    const int ntok = min(G::kTok, nidx - t0);
+                    if (lane == 0) mbar_wait(smem_u32(&sh.empty[stage]), phase ^ 1u, p.err, dead, 1);
+                    __syncwarp();
+                    const uint32_t dst0 = ring_base + stage * G::kStageBytes;
+#pragma unroll
+                    for (int j = 0; j < kChunksPerThread; ++j) {
+                        const int c = ptid + 256 * j;
+                        const int r = c / kChunksPerRow, o16 = c - r * kChunksPerRow;
+                        if (r < ntok)
+                            cp_async_16_stream(dst0 + r * G::kRowStride + o16 * 16,
+                                               kpool + (size_t)idx[t0 + r] * G::kRowBytes + o16 * 16, pol);
+                    }
+                    cp_async_arrive_noinc(smem_u32(&sh.full[stage]));
+                    if (++stage == kScoreStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");                 // nothing of ours is still in flight
+        return;
+    }
+
+    if (kBulk && warp == 0) {
         // ---------------- producer ----------------
         const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
         const uint64_t pol = l2_evict_first_policy();
@@ -379,6 +440,150 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
             p.partials[(size_t)sg.b * p.part_stride + (size_t)cta * hq + ctid] = make_float2(mm, ll);
         }
         consumer_bar();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// phase 1, bf16, register path: every warp loads its (16-token, kv-head) units straight from the pool
+// into mma A fragments with 16-byte loads (no shared-memory staging), two units in flight per warp.
+// A lane's 16 bytes are eight consecutive elements of one row; the k index of an mma is only a
+// summation index, so the query fragments are built in the matching permuted order:
+// step s (0..3), mma m (0..1) of lane quad position t covers elements 32s + 8t + 4m + {0,1 | 2,3}.
+// Used where key rows are short (few KV heads per GPU) and one bulk copy per row would be
+// copy-rate bound.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_stream_128(const void* p, uint64_t pol) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p), "l"(pol));
+    return v;
+}
+
+template <int HKV>
+__device__ __forceinline__ void score_phase_direct(const LayerParams& p, FusedShared& sh) {
+    constexpr int WPK = kWarps / HKV;                   // warps per KV head
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int kvh = warp % HKV, wsub = warp / HKV;
+    const int hq = p.hq, group = p.group;
+    const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
+    const uint64_t pol = l2_evict_first_policy();
+
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        uint32_t bq[16];
+        {
+            const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)sg.b * hq * 128;
+            const int h = (p.gqa_map == TS_GQA_MOD) ? (kvh + HKV * g) : (kvh * group + g);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                uint32_t v = 0u;
+                if (g < group) {
+                    const int e = 32 * (i >> 2) + 8 * t4 + 4 * ((i >> 1) & 1) + 2 * (i & 1);
+                    const __nv_bfloat16 lo = rotated_q<__nv_bfloat16>(p, q, h, e);
+                    const __nv_bfloat16 hi = rotated_q<__nv_bfloat16>(p, q, h, e + 1);
+                    v = (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+                }
+                bq[i] = v;
+            }
+        }
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float* lg_base = p.logits + (size_t)sh.plan.off[sg.b] * hq + kvh * group;
+        const int* row = p.rtt + (long long)p.req_pool_indices[sg.b] * p.rtt_stride + p.n_init;
+
+        for (int blk0 = sg.t0; blk0 < sg.t1; blk0 += 2 * kIdxBlock) {
+            const int nvalid = min(2 * kIdxBlock, sg.t1 - blk0);
+            __syncthreads();
+            int* idx = &sh.idx[0][0];                   // both index buffers as one block of 2*kIdxBlock
+            for (int i = tid; i < nvalid; i += kFusedThreads) {
+                int v = __ldg(row + blk0 + i);
+                if ((unsigned long long)(long long)v >= (unsigned long long)p.pool_rows) {
+                    set_error(p.err, TS_ERR_BAD_SLOT, v);
+                    v = 0;
+                }
+                idx[i] = v;
+            }
+            __syncthreads();
+            const int nblk = (nvalid + 15) / 16;
+            auto issue = [&](int jb, uint4 (&buf)[8]) {
+                const int ra = min(jb * 16 + g, nvalid - 1), rb = min(jb * 16 + g + 8, nvalid - 1);
+                const unsigned char* pa = kpool + ((size_t)idx[ra] * HKV + kvh) * 256 + t4 * 16;
+                const unsigned char* pb = kpool + ((size_t)idx[rb] * HKV + kvh) * 256 + t4 * 16;
+#pragma unroll
+                for (int st = 0; st < 4; ++st) {
+                    buf[2 * st] = ldg_stream_128(pa + st * 64, pol);
+                    buf[2 * st + 1] = ldg_stream_128(pb + st * 64, pol);
+                }
+            };
+            auto consume = [&](int jb, const uint4 (&buf)[8]) {
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int st = 0; st < 4; ++st) {
+                    const uint32_t a0[4] = {buf[2 * st].x, buf[2 * st + 1].x, buf[2 * st].y, buf[2 * st + 1].y};
+                    const uint32_t a1[4] = {buf[2 * st].z, buf[2 * st + 1].z, buf[2 * st].w, buf[2 * st + 1].w};
+                    mma_bf16_16816(acc, a0, bq[4 * st], bq[4 * st + 1]);
+                    mma_bf16_16816(acc, a1, bq[4 * st + 2], bq[4 * st + 3]);
+                }
+                const int r0 = jb * 16 + g, r1 = r0 + 8;
+                const bool v0 = r0 < nvalid, v1 = r1 < nvalid;
+                float* out0 = lg_base + (size_t)(blk0 + r0) * hq;
+                float* out1 = out0 + (size_t)8 * hq;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int c = 2 * t4 + j;
+                    if (c < group) {
+                        const float x0 = acc[j], x1 = acc[2 + j];
+                        if (v0) out0[c] = x0;
+                        if (v1) out1[c] = x1;
+                        const float mx = fmaxf(v0 ? x0 : -INFINITY, v1 ? x1 : -INFINITY);
+                        if (mx > -INFINITY) {
+                            const float mn = fmaxf(m[j], mx);
+                            float sum = l[j] * exp2f((m[j] - mn) * kLog2e);
+                            if (v0) sum += exp2f((x0 - mn) * kLog2e);
+                            if (v1) sum += exp2f((x1 - mn) * kLog2e);
+                            l[j] = sum;
+                            m[j] = mn;
+                        }
+                    }
+                }
+            };
+            uint4 bufa[8], bufb[8];
+            int jb = wsub;
+            if (jb < nblk) issue(jb, bufa);
+            while (jb < nblk) {
+                if (jb + WPK < nblk) issue(jb + WPK, bufb);
+                consume(jb, bufa);
+                jb += WPK;
+                if (jb >= nblk) break;
+                if (jb + WPK < nblk) issue(jb + WPK, bufa);
+                consume(jb, bufb);
+                jb += WPK;
+            }
+        }
+        // this CTA's statistics of request sg.b: lanes -> warp -> CTA
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int o = 4; o <= 16; o <<= 1) {
+                float mo = __shfl_xor_sync(0xffffffffu, m[j], o);
+                float lo = __shfl_xor_sync(0xffffffffu, l[j], o);
+                ml_merge(m[j], l[j], mo, lo);
+            }
+        }
+        __syncthreads();
+        if (g == 0) {
+            sh.stats[warp][2 * t4] = make_float2(m[0], l[0]);
+            sh.stats[warp][2 * t4 + 1] = make_float2(m[1], l[1]);
+        }
+        __syncthreads();
+        if (tid < hq) {
+            const int kv = tid / group, j = tid - kv * group;
+            float mm = -INFINITY, ll = 0.f;
+            for (int w = kv; w < kWarps; w += HKV) ml_merge(mm, ll, sh.stats[w][j].x, sh.stats[w][j].y);
+            p.partials[(size_t)sg.b * p.part_stride + (size_t)blockIdx.x * hq + tid] = make_float2(mm, ll);
+        }
+        __syncthreads();
     }
 }
 
@@ -1028,8 +1233,9 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
 // ------------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------------
-// HKV > 0: bf16 TMA + mma scoring for that many local KV heads; HKV == 0: plain-load scoring.
-template <typename T, int HKV>
+// HKV > 0: bf16 mma scoring for that many local KV heads, keys staged by bulk copies (DIRECT = false) or
+// loaded straight into registers (DIRECT = true); HKV == 0: plain-load scoring.
+template <typename T, int HKV, bool DIRECT>
 __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const LayerParams p, const int mode) {
     extern __shared__ __align__(128) unsigned char ring[];
     __shared__ FusedShared sh;
@@ -1084,7 +1290,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         mbar_init(smem_u32(&sh.stage_bar), 1);
         if (HKV > 0) {
             for (int s = 0; s < kScoreStages; ++s) {
-                mbar_init(smem_u32(&sh.full[s]), 1);
+                mbar_init(smem_u32(&sh.full[s]), (HKV > kBulkMinHkv) ? 1 : 256);
                 mbar_init(smem_u32(&sh.empty[s]), 8);
             }
         }
@@ -1114,7 +1320,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
                 if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
                     p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
             }
-            if constexpr (HKV > 0) score_phase_tma<HKV>(p, sh, ring, dead);
+            if constexpr (HKV > 0 && DIRECT) score_phase_direct<HKV>(p, sh);
+            else if constexpr (HKV > 0) score_phase_tma<HKV, (HKV > kBulkMinHkv)>(p, sh, ring, dead);
             else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
         }
         if (ok) vote_prefetch(p, sh, ring);
@@ -1126,6 +1333,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         stamp(p, 4);
         if (mode == kModeTpA) return;
         if (mode == kModeTpFused) tp_exchange_phase(p, sh, ok && !pooled, dead);
+        stamp(p, 24);
         if (pooled) {
             grid_barrier(p, dead);
             if (ok) hist_phase(p, sh);
@@ -1158,21 +1366,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
 // ------------------------------------------------------------------------------------------
 int fused_grid_size(int num_sms) { return num_sms; }
 
-static bool use_tma(int dtype, unsigned flags, int hkv, int d, int group) {
+static bool use_mma(int dtype, unsigned flags, int hkv, int d, int group) {
     return dtype == TS_DTYPE_BF16 && !(flags & TS_CFG_PLAIN_SCORE) && d == 128 && group <= 8 &&
            (hkv == 1 || hkv == 2 || hkv == 4 || hkv == 8);
 }
-
-int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group) {
-    return use_tma(dtype, flags, hkv, d, group) ? kScoreStageUnits / hkv : 16;
+// The register path is an option only: staging through shared memory (bulk copies for long rows,
+// cp.async pieces for short ones) measured faster at every row size (1.8x at 256-byte rows).
+static bool use_direct(unsigned flags, int hkv) {
+    (void)hkv;
+    return (flags & TS_CFG_DIRECT_SCORE) != 0;
 }
 
-template <typename T, int HKV>
+int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group) {
+    if (!use_mma(dtype, flags, hkv, d, group) || use_direct(flags, hkv)) return 16;
+    return kScoreStageUnits / hkv;
+}
+
+template <typename T, int HKV, bool DIRECT>
 static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mode) {
     const size_t smem = kFusedDynSmem;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fused_select_kernel<T, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(fused_select_kernel<T, HKV, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);
         if (e != cudaSuccess) return e;
         configured = true;
@@ -1192,22 +1407,23 @@ static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mod
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, fused_select_kernel<T, HKV>, pp, m);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, fused_select_kernel<T, HKV, DIRECT>, pp, m);
     stage_end(l);
     return e;
 }
 
 cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode) {
-    if (use_tma(l.dtype, l.flags, p.hkv, p.d, p.group)) {
+    if (use_mma(l.dtype, l.flags, p.hkv, p.d, p.group)) {
+        const bool direct = use_direct(l.flags, p.hkv);
         switch (p.hkv) {
-            case 1: return launch_fused_t<__nv_bfloat16, 1>(p, l, mode);
-            case 2: return launch_fused_t<__nv_bfloat16, 2>(p, l, mode);
-            case 4: return launch_fused_t<__nv_bfloat16, 4>(p, l, mode);
-            default: return launch_fused_t<__nv_bfloat16, 8>(p, l, mode);
+            case 1: return direct ? launch_fused_t<__nv_bfloat16, 1, true>(p, l, mode) : launch_fused_t<__nv_bfloat16, 1, false>(p, l, mode);
+            case 2: return direct ? launch_fused_t<__nv_bfloat16, 2, true>(p, l, mode) : launch_fused_t<__nv_bfloat16, 2, false>(p, l, mode);
+            case 4: return direct ? launch_fused_t<__nv_bfloat16, 4, true>(p, l, mode) : launch_fused_t<__nv_bfloat16, 4, false>(p, l, mode);
+            default: return direct ? launch_fused_t<__nv_bfloat16, 8, true>(p, l, mode) : launch_fused_t<__nv_bfloat16, 8, false>(p, l, mode);
         }
     }
-    if (l.dtype == TS_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, 0>(p, l, mode);
-    return launch_fused_t<float, 0>(p, l, mode);
+    if (l.dtype == TS_DTYPE_BF16) return launch_fused_t<__nv_bfloat16, 0, false>(p, l, mode);
+    return launch_fused_t<float, 0, false>(p, l, mode);
 }
 
 }  // namespace ts

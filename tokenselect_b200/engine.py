@@ -49,6 +49,7 @@ class TokenSelectConfig:
     tp_rank: int = 0
     tp_size: int = 1
     plain_score: bool = False              # diagnostic: plain-load scoring kernel for bf16 too
+    score_path: str = "auto"               # "auto" | "direct" (keys to registers) | "staged" (bulk copies to smem)
     tp_fused: bool = True                  # tp_size > 1: sum the votes inside the kernel through peer memory
 
     @property
@@ -117,7 +118,7 @@ class TokenSelectEngine:
         c.max_reqs, c.max_batch, c.max_ctx = cfg.max_reqs, cfg.max_batch, cfg.max_n_tokens
         c.max_total_tokens = max_total
         c.tp_rank, c.tp_size = cfg.tp_rank, cfg.tp_size
-        c.flags = _lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0
+        c.flags = (_lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0) | {"auto": 0, "direct": 2, "staged": 4}[cfg.score_path]
         c.score_cos_sin = score_cs.data_ptr()
         c.attn_cos_sin = attn_cs.data_ptr()
         self._c = c
