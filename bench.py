@@ -353,7 +353,9 @@ def main():
         names = ["prepare+plan", "score", "barrier", "vote", "barrier/exchange", "filter", "barrier", "emit"]
         split = {n: (ts[i + 1] - ts[i]) / 1e3 for i, n in enumerate(names)}
         if tp > 1 and eng.fused_tp:
-            split["vote->exchange done"] = (ts[24] - ts[4]) / 1e3
+            split["exchange: signal sent"] = (ts[26] - ts[4]) / 1e3
+            split["exchange: flags"] = (ts[25] - ts[4]) / 1e3
+            split["exchange: sum"] = (ts[24] - ts[25]) / 1e3
         print(f"[rank {rank}] selection kernel phases (us): {split}", file=sys.stderr, flush=True)
     if rank == 0:
         ab = algorithmic_bytes(ctx + args.warmup + args.steps // 2, hq, hkv, D)

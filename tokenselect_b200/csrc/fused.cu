@@ -906,9 +906,11 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
     const int tp = p.tp_size, me = p.tp_rank;
     __syncthreads();                                   // this CTA's raw votes are written
     if (tid < tp && tid != me) {
-        __threadfence_system();
+        // release at system scope: the CTA's votes (ordered before this store by the barrier above) are
+        // visible to the peer that observes the flag
         unsigned* dst = p.peer_flags[tid] + ((size_t)(p.flag_parity * tp + me) * kFlagPad + blockIdx.x);
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(p.epoch) : "memory");
+        stamp(p, 26);
         const unsigned* src = p.peer_flags[me] + ((size_t)(p.flag_parity * tp + tid) * kFlagPad + blockIdx.x);
         const long long t0 = clock64();
         unsigned v = 0, spins = 0;
@@ -922,6 +924,7 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
         }
     }
     __syncthreads();
+    stamp(p, 25);
     for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
     __syncthreads();
     for (int s = 0; s < sh.nseg; ++s) {
@@ -929,14 +932,22 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
         const size_t off = (size_t)sh.plan.off[sg.b];
         float* out = p.votes_final + off;
         for (int t = sg.t0 + 4 * tid; t < sg.t1; t += 4 * kFusedThreads) {
+            // all ranks' pieces are requested before the first is used (one NVLink round trip), then
+            // added in rank order
+            float4 x[kMaxTp];
+#pragma unroll
+            for (int r = 0; r < kMaxTp; ++r) {
+                if (r < tp) {
+                    const float* src = p.peer_votes[r] + off + t;
+                    asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(x[r].x), "=f"(x[r].y), "=f"(x[r].z), "=f"(x[r].w)
+                                 : "l"(src));
+                }
+            }
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < tp; ++r) {
-                const float* src = p.peer_votes[r] + off + t;
-                float4 x;
-                asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w)
-                             : "l"(src));
-                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+#pragma unroll
+            for (int r = 0; r < kMaxTp; ++r) {
+                if (r < tp) { acc.x += x[r].x; acc.y += x[r].y; acc.z += x[r].z; acc.w += x[r].w; }
             }
             *reinterpret_cast<float4*>(out + t) = acc;
             if (with_hist) {
