@@ -74,6 +74,11 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     int ch = (n_sel + num_sms - 1) / num_sms;
     ch = ch < 16 ? 16 : (ch + 3) / 4 * 4;
     while (ch > 4 && (size_t)ch * 2 * c->hkv * c->head_dim * elem > 160 * 1024) ch -= 4;
+    // bf16 at head_dim 128 runs the tensor-core split kernel: partials per 16 listed rows
+    const bool attn_tc = c->dtype == TS_DTYPE_BF16 && c->head_dim == 128 && c->hq / c->hkv <= 8 &&
+                         (c->hkv == 1 || c->hkv == 2 || c->hkv == 4 || c->hkv == 8);
+    if (attn_tc) ch = 16;
+    const int cs_tiles = (n_sel + 1 + 15) / 16 * 2;
     const int chunks = (n_sel + ch - 1) / ch;
     Carve cv;
     size_t o_err = cv.take(16);
@@ -101,6 +106,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_scs = cv.take((size_t)(c->head_dim / 2) * 8);
     size_t o_acs = cv.take((size_t)(n_sel + 1) * (c->head_dim / 2) * 8);
     size_t o_acsl = cv.take((size_t)(n_sel + 1) * (c->head_dim / 2) * 8);
+    size_t o_acst = cv.take(attn_tc ? (size_t)cs_tiles * 4096 : 16);
     size_t o_fp = cv.take((size_t)c->max_reqs * c->n_layers * hd * elem);
     size_t o_pc = cv.take((size_t)c->max_reqs * c->n_layers * c->top_k * 4);
     size_t o_valid = cv.take((size_t)c->max_reqs * c->n_layers * 4);
@@ -145,6 +151,8 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.score_cs = reinterpret_cast<const float2*>(a + o_scs);
         p.attn_cs = reinterpret_cast<const float2*>(a + o_acs);
         p.attn_cs_lane = reinterpret_cast<const float2*>(a + o_acsl);
+        p.attn_cs_tile = reinterpret_cast<const float4*>(a + o_acst);
+        p.attn_tc = attn_tc ? 1 : 0;
         p.cand_capacity = cap;
         p.fp_cache = a + o_fp;
         p.pos_cache = reinterpret_cast<int*>(a + o_pc);
@@ -307,6 +315,9 @@ int ts_create(const ts_config* cfg, ts_handle** out) {
                        cudaMemcpyHostToDevice);
     if (e == cudaSuccess)
         e = launch_lane_order_table(p.attn_cs, const_cast<float2*>(p.attn_cs_lane), cfg->head_dim, h->n_sel + 1, 0);
+    if (e == cudaSuccess && p.attn_tc)
+        e = launch_tile_order_table(p.attn_cs, const_cast<float4*>(p.attn_cs_tile), h->n_sel + 1,
+                                    (h->n_sel + 1 + 15) / 16 * 2, 0);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { cudaFree(h->arena); delete h; return TS_ERR_CUDA; }
     *out = h;

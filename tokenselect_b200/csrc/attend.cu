@@ -364,6 +364,205 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
     ATT_STAMP(38);
 }
 
+// ------------------------------------------------------------------------------------------
+// Tensor-core split kernel (bf16, head_dim 128).  grid = (ceil(blocks / BPC), batch), 8 warps; a warp
+// owns one KV head and one block of 16 listed rows.
+//   S^T[heads x rows] = Q_rot . K_rot^T : A = the KV head's (<= 8) query heads, rotated, from registers;
+//                        B = key rows read with ldmatrix, rotated in registers (both members of a
+//                        rotation pair sit in the same lane: k-steps s and s+4);
+//   O^T[d x heads]    = V^T . P^T      : A = ldmatrix.trans of the value rows, B = the softmax numerators
+//                        straight from the S^T accumulators (same lane layout).
+// fp32 operands (rotated Q and K, P) are split into bf16 high and low parts and multiplied in three
+// (two) mma.sync so that products keep ~16 mantissa bits; V is bf16 already.  Rows, rotation tiles and
+// values arrive by bulk asynchronous copies; key/value rows are padded by 16 bytes in shared memory so
+// that ldmatrix phases hit distinct banks.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    hi = pack_bf16x2(a, b);
+    lo = pack_bf16x2(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
+}
+
+template <int HKV>
+__global__ void __launch_bounds__(256, 2) attend_split_tc_kernel(const LayerParams p) {
+    constexpr int BPC = 8 / HKV;                        // 16-row blocks per CTA
+    constexpr int ROWB = HKV * 256, ROWS = ROWB + 16;   // key/value row bytes in the pool / in shared memory
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    unsigned char* sm_k = smem_raw;
+    unsigned char* sm_v = sm_k + BPC * 16 * ROWS;
+    const float4* sm_cs = reinterpret_cast<const float4*>(sm_v + BPC * 16 * ROWS);   // [BPC*2 tiles][256]
+    const uint32_t bar = smem_u32(sm_v + BPC * 16 * ROWS + BPC * 2 * 4096);
+
+    const int b = blockIdx.y, blk0 = blockIdx.x * BPC;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int kv = warp % HKV, wb = warp / HKV;
+    const int G = p.group, hq = p.hq;
+    const int count = min(p.seq_lens[b], p.n_sel);      // inputs only: known before the selection kernel ends
+
+    ATT_STAMP(32);
+    // ---- query fragments (inputs only) ----
+    uint32_t qh[8][2], ql[8][2];
+    {
+        const __nv_bfloat16* q = reinterpret_cast<const __nv_bfloat16*>(p.q) + ((size_t)b * hq + kv * G + min(g, G - 1)) * 128;
+        const float2* csq = p.attn_cs + (size_t)max(count - 1, 0) * 64;
+        uint32_t w[8][2];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) w[ks][u] = *reinterpret_cast<const uint32_t*>(q + 16 * ks + 8 * u + 2 * t);
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float4 cs = *reinterpret_cast<const float4*>(csq + 16 * s + 8 * u + 2 * t);
+                const float x1a = __uint_as_float(w[s][u] << 16), x1b = __uint_as_float(w[s][u] & 0xFFFF0000u);
+                const float x2a = __uint_as_float(w[s + 4][u] << 16), x2b = __uint_as_float(w[s + 4][u] & 0xFFFF0000u);
+                const bool on = g < G;
+                split_bf16x2(on ? x1a * cs.x - x2a * cs.y : 0.f, on ? x1b * cs.z - x2b * cs.w : 0.f, qh[s][u], ql[s][u]);
+                split_bf16x2(on ? x2a * cs.x + x1a * cs.y : 0.f, on ? x2b * cs.z + x1b * cs.w : 0.f, qh[s + 4][u], ql[s + 4][u]);
+            }
+    }
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    ATT_STAMP(33);
+    // nothing above depends on the selection kernel; everything below does
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    ATT_STAMP(34);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __syncthreads();
+
+    const int err = *(volatile int*)p.err;
+    const int base = blk0 * 16;
+    if (err != 0 || base >= count) return;
+    const int cnt = min(BPC * 16, count - base);
+    if (warp == 0) {
+        const int tiles = (cnt + 7) / 8;
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)cnt * 2u * ROWB + (uint32_t)tiles * 4096u);
+        __syncwarp();
+        const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
+        const unsigned char* vpool = reinterpret_cast<const unsigned char*>(p.v_pool);
+        for (int i = lane; i < cnt; i += 32) {
+            int slot = __ldcg(p.sel_slots + (size_t)b * p.n_sel + base + i);
+            if ((unsigned long long)(long long)slot >= (unsigned long long)p.pool_rows) {
+                set_error(p.err, TS_ERR_BAD_SLOT, slot);
+                slot = 0;
+            }
+            bulk_g2s(smem_u32(sm_k) + i * ROWS, kpool + (size_t)slot * ROWB, ROWB, bar);
+            bulk_g2s(smem_u32(sm_v) + i * ROWS, vpool + (size_t)slot * ROWB, ROWB, bar);
+        }
+        if (lane == 0)
+            bulk_g2s(smem_u32(sm_cs), p.attn_cs_tile + (size_t)(base / 8) * 256, (uint32_t)tiles * 4096u, bar);
+    }
+    // rows past the end of the list: zeros, so that 0-weight products stay finite
+    for (int i = cnt * (ROWB / 16) + tid; i < BPC * 16 * (ROWB / 16); i += 256) {
+        const int r = i / (ROWB / 16), c = i - r * (ROWB / 16);
+        *reinterpret_cast<uint4*>(sm_k + r * ROWS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(sm_v + r * ROWS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    {
+        bool dead = false;
+        mbar_wait(bar, 0u, p.err, dead, 21);
+    }
+    ATT_STAMP(35);
+    const int cntb = min(16, cnt - wb * 16);             // rows of this warp's block
+    if (cntb <= 0) return;
+
+    // ---- S^T = Q_rot . K_rot^T ----
+    float sc[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[j][i] = 0.f;
+    const int lrow = lane & 7, lsel = lane >> 3;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const float4* cst = sm_cs + (size_t)((wb * 16 + 8 * j) / 8 ) * 256;
+        // when a tile of eight lies wholly past the copied rotation tiles its scores are masked below
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            uint32_t r[4];
+            const int doff = 16 * s + (lsel & 1) * 8 + (lsel >> 1) * 64;
+            ldmatrix_x4(r, smem_u32(sm_k) + (wb * 16 + 8 * j + lrow) * ROWS + kv * 256 + doff * 2);
+            uint32_t bh[2][2], bl[2][2];               // [k-step s | s+4][b0 | b1]
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const float4 cs = cst[((s * 2 + u) * 8 + g) * 4 + t];
+                const float x1a = __uint_as_float(r[u] << 16), x1b = __uint_as_float(r[u] & 0xFFFF0000u);
+                const float x2a = __uint_as_float(r[2 + u] << 16), x2b = __uint_as_float(r[2 + u] & 0xFFFF0000u);
+                split_bf16x2(x1a * cs.x - x2a * cs.y, x1b * cs.z - x2b * cs.w, bh[0][u], bl[0][u]);
+                split_bf16x2(x2a * cs.x + x1a * cs.y, x2b * cs.z + x1b * cs.w, bh[1][u], bl[1][u]);
+            }
+#pragma unroll
+            for (int k2 = 0; k2 < 2; ++k2) {
+                const int ks = s + 4 * k2;
+                const uint32_t ah[4] = {qh[ks][0], 0u, qh[ks][1], 0u};
+                const uint32_t al[4] = {ql[ks][0], 0u, ql[ks][1], 0u};
+                mma_bf16_16816(sc[j], ah, bh[k2][0], bh[k2][1]);
+                mma_bf16_16816(sc[j], ah, bl[k2][0], bl[k2][1]);
+                mma_bf16_16816(sc[j], al, bh[k2][0], bh[k2][1]);
+            }
+        }
+    }
+    ATT_STAMP(36);
+    // ---- softmax over the block's rows (head = accumulator row g; a quad shares it) ----
+    float x[2][2], mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            float v = sc[j][u] * p.sm_scale;
+            if (p.logit_cap > 0.f) v = p.logit_cap * tanhf(v / p.logit_cap);
+            v = (8 * j + 2 * t + u < cntb) ? v * kLog2eA : -INFINITY;
+            x[j][u] = v;
+            mx = fmaxf(mx, v);
+        }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    float pe[2][2], lsum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            pe[j][u] = (x[j][u] == -INFINITY) ? 0.f : exp2f(x[j][u] - mx);
+            lsum += pe[j][u];
+        }
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
+    lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
+    uint32_t ph[2], pl[2];
+    split_bf16x2(pe[0][0], pe[0][1], ph[0], pl[0]);
+    split_bf16x2(pe[1][0], pe[1][1], ph[1], pl[1]);
+
+    // ---- O^T = V^T . P^T ----
+    const int chunk = blk0 + wb;
+    float* out_base = p.attn_o + (((size_t)b * p.attn_chunks + chunk) * hq + (size_t)kv * G) * 128;
+#pragma unroll
+    for (int db = 0; db < 8; ++db) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(a, smem_u32(sm_v) + (wb * 16 + ((lane >> 4) & 1) * 8 + lrow) * ROWS + kv * 256 +
+                                 (16 * db + ((lane >> 3) & 1) * 8) * 2);
+        float o[4] = {0.f, 0.f, 0.f, 0.f};
+        mma_bf16_16816(o, a, ph[0], ph[1]);
+        mma_bf16_16816(o, a, pl[0], pl[1]);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int hh = 2 * t + u;
+            if (hh < G) {
+                out_base[(size_t)hh * 128 + 16 * db + g] = o[u];
+                out_base[(size_t)hh * 128 + 16 * db + g + 8] = o[2 + u];
+            }
+        }
+    }
+    if (t == 0 && g < G) p.attn_ml[((size_t)b * p.attn_chunks + chunk) * hq + kv * G + g] = make_float2(mx, lsum);
+    ATT_STAMP(37);
+}
+
 // grid = (hq, batch), block = 512: warp w takes chunks w, w+16, ...; lane i takes elements
 // [VEC*i, VEC*i + VEC).  The partial outputs are requested before the weights are known.
 constexpr int kMergeThreads = 512;
@@ -503,7 +702,37 @@ static cudaError_t launch_attend_t(const LayerParams& p, const Launch& l) {
     return e;
 }
 
+template <int HKV>
+static cudaError_t launch_attend_tc(const LayerParams& p, const Launch& l) {
+    constexpr int BPC = 8 / HKV;
+    const size_t smem = (size_t)2 * BPC * 16 * (HKV * 256 + 16) + (size_t)BPC * 2 * 4096 + 16;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attend_split_tc_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    stage_begin(l, kStageAttendSplit);
+    cudaError_t e = launch_pdl(attend_split_tc_kernel<HKV>, dim3((p.attn_chunks + BPC - 1) / BPC, p.batch), dim3(256),
+                               smem, l.stream, p);
+    stage_end(l);
+    if (e != cudaSuccess) return e;
+    stage_begin(l, kStageAttendMerge);
+    e = launch_pdl(attend_merge_kernel<__nv_bfloat16, 4>, dim3(p.hq, p.batch), dim3(kMergeThreads), 0, l.stream, p);
+    stage_end(l);
+    return e;
+}
+
 cudaError_t launch_attend(const LayerParams& p, const Launch& l) {
+    if (p.attn_tc) {
+        switch (p.hkv) {
+            case 1: return launch_attend_tc<1>(p, l);
+            case 2: return launch_attend_tc<2>(p, l);
+            case 4: return launch_attend_tc<4>(p, l);
+            default: return launch_attend_tc<8>(p, l);
+        }
+    }
     if (l.dtype == TS_DTYPE_BF16) {
         if (p.d == 128) return launch_attend_t<__nv_bfloat16, 8>(p, l);
         return launch_attend_t<__nv_bfloat16, 4>(p, l);

@@ -80,6 +80,8 @@ struct LayerParams {
     const float2* score_cs;    // [d/2] (cos, sin) of the scoring position
     const float2* attn_cs;     // [n_sel+1, d/2]
     const float2* attn_cs_lane; // same rows, entries in the order the attention kernel's lanes read them
+    const float4* attn_cs_tile; // same rows in 8-position tiles ordered for the tensor-core attention kernel
+    int attn_tc;               // 1: tensor-core split kernel (bf16, head_dim 128), chunks of 16 rows
     long long cand_capacity;
     // per-request selection cache
     void* fp_cache;            // [max_reqs, n_layers, hq*d] dtype
@@ -211,6 +213,7 @@ inline void stage_end(const Launch& l) {
 
 cudaError_t launch_rope_tables(float2* score_cs, float2* attn_cs, int d, int n_rows, double base,
                                double rope_scale, int n_local, cudaStream_t stream);
+cudaError_t launch_tile_order_table(const float2* attn_cs, float4* attn_cs_tile, int n_rows, int n_tiles, cudaStream_t stream);
 cudaError_t launch_lane_order_table(const float2* attn_cs, float2* attn_cs_lane, int d, int n_rows, cudaStream_t stream);
 
 // Position of rotation entry i (0 <= i < d/2) inside a lane-ordered table row: lane j = i / E of an

@@ -44,6 +44,26 @@ cudaError_t launch_lane_order_table(const float2* attn_cs, float2* attn_cs_lane,
     return cudaGetLastError();
 }
 
+// Tile order for the tensor-core attention kernel (head_dim 128): positions in tiles of eight; inside a
+// tile the (cos, sin) of frequency i = 16s + 8u + 2t + w of position g sits in float4 ((s*2+u)*8 + g)*4 + t,
+// halves w = 0, 1 -- the order in which a warp's lanes (g = lane/4, t = lane%4) need them, so that one
+// 16-byte load per lane is conflict-free.
+__global__ void tile_order_kernel(const float2* src, float2* dst, int n_rows, int n_tiles) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_tiles * 8 * 64) return;
+    const int pos = idx / 64, i = idx - pos * 64;
+    const int tile = pos >> 3, g = pos & 7;
+    const int s = i >> 4, u = (i >> 3) & 1, t = (i >> 1) & 3, w = i & 1;
+    const float2 v = pos < n_rows ? src[(size_t)pos * 64 + i] : make_float2(1.f, 0.f);
+    dst[((size_t)tile * 256 + ((s * 2 + u) * 8 + g) * 4 + t) * 2 + w] = v;
+}
+
+cudaError_t launch_tile_order_table(const float2* attn_cs, float4* attn_cs_tile, int n_rows, int n_tiles, cudaStream_t stream) {
+    const int total = n_tiles * 8 * 64;
+    tile_order_kernel<<<(total + 255) / 256, 256, 0, stream>>>(attn_cs, reinterpret_cast<float2*>(attn_cs_tile), n_rows, n_tiles);
+    return cudaGetLastError();
+}
+
 // grid = batch, block = 256.
 template <typename T>
 __global__ void __launch_bounds__(256) prep_kernel(const LayerParams p) {
