@@ -577,6 +577,7 @@ __global__ void __launch_bounds__(kMergeThreads) attend_merge_kernel(const Layer
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hq = p.hq;
+    ATT_STAMP(48 + 2 * (p.layer & 1));
     const int err = *(volatile int*)p.err;
     const int count = min(p.seq_lens[b], p.n_sel);
     if (err != 0 || count < 1) return;
@@ -660,6 +661,7 @@ __global__ void __launch_bounds__(kMergeThreads) attend_merge_kernel(const Layer
         for (int w = 0; w < NW; ++w) r += s_acc[w][e];
         reinterpret_cast<T*>(p.out)[((size_t)b * hq + h) * D + e] = from_f32<T>(r / ll_run);
     }
+    ATT_STAMP(49 + 2 * (p.layer & 1));
 }
 
 // Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor

@@ -1258,10 +1258,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     // ---- phase 0 ----
     stamp(p, 0);
+    stamp(p, 52 + (p.layer & 1));
     if (threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        if (blockIdx.x == 0) { p.phase_ts[9] = t; p.phase_ts[10] = t; }
+        if (blockIdx.x == 0) { p.phase_ts[9] = t; p.phase_ts[10] = t; p.phase_ts[13] = ~0ull; p.phase_ts[14] = 0ull; }
         else atomicMin(p.phase_ts + 11, t);
     }
     bool ok = *(volatile int*)p.err == 0;
@@ -1337,6 +1338,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         }
         if (ok) vote_prefetch(p, sh, ring);
         stamp(p, 2);
+        if (threadIdx.x == 0) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            atomicMin(p.phase_ts + 13, t);
+            atomicMax(p.phase_ts + 14, t);
+        }
         grid_barrier(p, dead);
         stamp(p, 3);
         // ---- phase 2: votes ----
