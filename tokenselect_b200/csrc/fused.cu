@@ -1076,8 +1076,9 @@ __device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& 
 __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& sh) {
     const int tid = threadIdx.x;
     const int k = p.top_k;
-    // windows, dense requests and cached index sets: request b is handled by CTA b % grid
-    for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    // windows, dense requests and cached index sets: request b is handled by CTA grid-1 - b % grid (the
+    // low-numbered CTAs prepare requests at the same time)
+    for (int b = (int)(gridDim.x - 1 - blockIdx.x); b < p.batch; b += gridDim.x) {
         const int n = sh.plan.n[b];
         const int flag = sh.plan.flag[b];
         const int req = p.req_pool_indices[b];
@@ -1265,20 +1266,23 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         if (blockIdx.x == 0) { p.phase_ts[9] = t; p.phase_ts[10] = t; p.phase_ts[13] = ~0ull; p.phase_ts[14] = 0ull; }
         else atomicMin(p.phase_ts + 11, t);
     }
-    bool ok = *(volatile int*)p.err == 0;
+    // The sticky error word is requested here and looked at only after the plan's own loads have been
+    // issued, so that the two round trips overlap (CTAs that prepare a request need it at once).
+    const int err0 = *(volatile int*)p.err;
     const bool need_flags_barrier = p.query_cache != 0;
     if (mode != kModeTpB) {
-        if (ok) {
-            for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
-                if (mode == kModeAll || mode == kModeTpFused) prepare_request<T, true>(p, b, sh.prep);
-                else if (p.query_cache) decide_request<T>(p, b, sh.prep);
-            }
+        for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+            if (err0 != 0) break;
+            if (mode == kModeAll || mode == kModeTpFused) prepare_request<T, true>(p, b, sh.prep);
+            else if (p.query_cache) decide_request<T>(p, b, sh.prep);
         }
         if (need_flags_barrier) grid_barrier(p, dead);
     }
     // Flags: from the length guard alone when the selection cache is off (nothing to wait for).
-    if (need_flags_barrier || mode == kModeTpB) ok = build_plan<false>(p, sh.plan) && ok;
-    else ok = build_plan<true>(p, sh.plan) && ok;
+    bool ok;
+    if (need_flags_barrier || mode == kModeTpB) ok = build_plan<false>(p, sh.plan);
+    else ok = build_plan<true>(p, sh.plan);
+    ok = ok && err0 == 0;
 
     // ---- ownership: contiguous tile range per CTA ----
     if (tid == 0) {
@@ -1316,8 +1320,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // Nothing recomputes (every request reuses its cached set or attends to everything): every CTA sees
     // the same empty plan, so all of them skip the scoring phases and their barriers together.  In the
     // fused tensor-parallel form the ranks decide alike for the same reason.
+    // The parts of the index sets that do not depend on votes are written now, off the kernel's tail.
+    if (ok && mode != kModeTpA) emit_windows(p, sh);
     if (sh.tile_off[p.batch] == 0) {
-        if (ok && mode != kModeTpA) emit_windows(p, sh);
         stamp(p, 8);
         return;
     }
@@ -1367,10 +1372,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     grid_barrier(p, dead);
     stamp(p, 7);
     // ---- phase 4 ----
-    if (ok) {
-        emit_windows(p, sh);
-        emit_phase(p, sh, ring);
-    }
+    if (ok) emit_phase(p, sh, ring);
     stamp(p, 8);
     if (threadIdx.x == 0) {
         unsigned long long t;
