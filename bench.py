@@ -12,8 +12,9 @@ layers through the C ABI.  The model's dense projections lie outside the patched
 and are not part of the step.
 
 With N > 1 (launched by torch.distributed.run) the same request is sharded by KV head over N ranks
-(tensor parallel): every rank scores its heads, the fp32 vote vector is all-reduced with NCCL, every
-rank runs the same top-k.  Total work is fixed ("strong" scaling).
+(tensor parallel): every rank scores its heads, the fp32 vote vectors are summed inside the selection
+kernel over NVLink peer memory (--tp-split: by an NCCL all-reduce between two kernels), every rank runs
+the same top-k.  Total work is fixed ("strong" scaling).
 
 Prints one JSON line on rank 0 (see the keys below).  ``--impl reference`` times the reference's
 selection + attention arithmetic restated in torch on the host CPU cores (the CPU oracle), one layer
@@ -395,9 +396,9 @@ def main():
                          "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                          "peak_source": peak_kind, "bytes_per_launch": ab["select"],
                          "us_per_launch": score_us,
-                         # dram read+write of one launch from the ncu capture in profiles/ (277.77 MB at
-                         # 267.68 MB algorithmic), scaled with the algorithmic bytes; single-GPU shape only
-                         "traffic": (ab["select"] * 277.77 / 267.68) if tp == 1 else None},
+                         # dram read+write of one launch from the ncu capture in profiles/ (278.51 MB at
+                         # 267.70 MB algorithmic), scaled with the algorithmic bytes; single-GPU shape only
+                         "traffic": (ab["select"] * 278.51 / 267.70) if tp == 1 else None},
             "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
