@@ -82,7 +82,8 @@ def retrieval_indices(q: torch.Tensor, k_pool: torch.Tensor, slot_row: torch.Ten
                       rope_base: float, rope_scale: float = 1, kernel_size: int = -1,
                       root: str = DEFAULT_REFERENCE_ROOT) -> Optional[torch.Tensor]:
     """Reference ``TokenRetriever.retrieval_indices`` (token_retrieval.py:375-449) for one decode
-    query ``q [Hq*D]`` (fp32) of a request whose ``n_tokens`` positions map to ``slot_row``.
+    query ``q [Hq*D]`` or one prefill chunk ``q [Lq, Hq*D]`` (fp32) of a request whose ``n_tokens``
+    positions map to ``slot_row``.
     The module globals are set as ``patch()`` sets them (token_retrieval.py:907-918).
     Returns the int32 slot list, or None when the reference falls back to dense attention."""
     ref = load(root)
@@ -98,4 +99,4 @@ def retrieval_indices(q: torch.Tensor, k_pool: torch.Tensor, slot_row: torch.Ten
         token_to_kv_pool=_FakePool(k_pool), rotary_embedding=rope)
     retriever.add_k_cache(slot_row[:n_tokens].to(torch.int32), 0)
     with torch.no_grad():
-        return retriever.retrieval_indices(q.view(1, -1), 0, n_init, n_local, top_k)
+        return retriever.retrieval_indices(q.reshape(-1, hq * head_dim), 0, n_init, n_local, top_k)

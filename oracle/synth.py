@@ -104,3 +104,10 @@ def make_layer_case(seed: int, n_tokens: int, hq: int, hkv: int, d: int, n_init:
     rtt[req_pool_idx, :n_tokens] = rows.to(torch.int32)
     return LayerCase(q=q.reshape(-1), k_pool=k_pool, v_pool=v_pool, req_to_token=rtt,
                      req_pool_idx=req_pool_idx, n_tokens=n_tokens, planted=planted)
+
+
+def make_chunk_queries(seed: int, case: LayerCase, lq: int, hq: int, d: int, spread: float = 0.5) -> torch.Tensor:
+    """Queries of a prefill chunk ``[lq, hq*d]``: the case's query plus ``spread`` x N(0,1) per token, so
+    that the chunk's mean fingerprint keeps a direction (the mean of independent queries would be ~0)."""
+    noise = normal(seed, 11, (lq, hq * d))
+    return (case.q.float().view(1, -1) + spread * noise).to(case.q.dtype)

@@ -63,6 +63,32 @@ def rotate_scoring_query(q: torch.Tensor, n_local: int, rope_base: float, rope_s
     return ((q.float() * cos) + (rotate_half(q).float() * sin)).to(q.dtype)
 
 
+def rotate_chunk_queries(q: torch.Tensor, n_local: int, rope_base: float, rope_scale: float) -> torch.Tensor:
+    """Prefill chunk ``q [Lq, Hq, D]``: query i is rotated at position ``(n_local + i) * rope_scale`` and
+    rounded to ``q.dtype`` (token_retrieval.py:380-388: ``position_ids = arange(n_local, n_local + Lq)``)."""
+    lq = q.shape[0]
+    inv_freq = rope_inv_freq(q.shape[-1], rope_base)
+    pos = torch.arange(n_local, n_local + lq, dtype=torch.float32) * rope_scale
+    cos, sin = rope_cos_sin(pos, inv_freq)                               # [Lq, D]
+    return ((q.float() * cos[:, None, :]) + (rotate_half(q).float() * sin[:, None, :])).to(q.dtype)
+
+
+def chunk_fingerprint(q: torch.Tensor, n_local: int, rope_base: float, rope_scale: float,
+                      fixed_order: bool = True) -> torch.Tensor:
+    """Scoring query of a prefill chunk: the mean over the chunk of the rotated, rounded queries
+    (token_retrieval.py:392, ``torch.mean(query, dim=0)``), ``[Hq, D]`` in ``q.dtype``.  ``fixed_order``
+    fixes what torch leaves open: fp32 running sum in ascending query order, one fp32 division by the
+    chunk length, one rounding to the dtype; otherwise ``torch.mean`` itself is called."""
+    rot = rotate_chunk_queries(q, n_local, rope_base, rope_scale)
+    if not fixed_order:
+        return torch.mean(rot.view(rot.shape[0], -1), dim=0).view(rot.shape[1:])
+    acc = np.zeros(rot.shape[1:], dtype=np.float32)
+    rot32 = rot.float().numpy()
+    for i in range(rot.shape[0]):
+        acc = acc + rot32[i]
+    return torch.from_numpy(acc / np.float32(rot.shape[0])).to(q.dtype)
+
+
 # --------------------------------------------------------------------------------------
 # scoring, soft vote, top-k                                 token_retrieval.py:166-261, 338-373
 # --------------------------------------------------------------------------------------
@@ -219,6 +245,54 @@ def sparse_attention(
     return out
 
 
+def sparse_prefill_attention(
+    q: torch.Tensor,          # [Lq, Hq, D] un-rotated queries of the chunk (the last Lq tokens of the list)
+    k_pool: torch.Tensor,     # [rows, Hkv, D]
+    v_pool: torch.Tensor,
+    slots: torch.Tensor,      # [n] pool rows in list order; the chunk's own rows are the last Lq
+    sm_scale: float,
+    rope_base: float,
+    rope_scale: float = 1.0,
+    logit_cap: float = 0.0,
+    compute_dtype: torch.dtype = torch.float32,
+) -> torch.Tensor:
+    """Causal attention of a prefill chunk over ``slots`` as the reference's third-party paged prefill
+    wrapper computes it in its Llama-RoPE mode with ``causal=True`` (call site
+    token_retrieval.py:746-772): with ``n`` listed keys and ``Lq`` queries, query i sits at position
+    ``n - Lq + i`` and sees the listed keys ``j <= n - Lq + i``; key j is rotated at position j; the
+    rest as in :func:`sparse_attention`.  Returns ``[Lq, Hq, D]``."""
+    lq, hq, d = q.shape
+    hkv = k_pool.shape[1]
+    group = hq // hkv
+    n = slots.numel()
+    inv_freq = rope_inv_freq(d, rope_base) / rope_scale
+    kpos = torch.arange(n, dtype=torch.float32)
+    qpos = torch.arange(n - lq, n, dtype=torch.float32)
+    if compute_dtype == torch.float64:
+        inv64 = inv_freq.double()
+        fk, fq = torch.outer(kpos.double(), inv64), torch.outer(qpos.double(), inv64)
+        cos_k, sin_k = torch.cat((fk, fk), -1).cos(), torch.cat((fk, fk), -1).sin()
+        cos_q, sin_q = torch.cat((fq, fq), -1).cos(), torch.cat((fq, fq), -1).sin()
+    else:
+        cos_k, sin_k = rope_cos_sin(kpos, inv_freq)
+        cos_q, sin_q = rope_cos_sin(qpos, inv_freq)
+    qf = q.to(compute_dtype)
+    q_rot = qf * cos_q.to(compute_dtype)[:, None, :] + rotate_half(qf) * sin_q.to(compute_dtype)[:, None, :]
+    ks = k_pool[slots.long()].to(compute_dtype)
+    vs = v_pool[slots.long()].to(compute_dtype)
+    k_rot = ks * cos_k.to(compute_dtype)[:, None, :] + rotate_half(ks) * sin_k.to(compute_dtype)[:, None, :]
+    visible = torch.arange(n)[None, :] <= (n - lq + torch.arange(lq))[:, None]       # [Lq, n]
+    out = torch.empty((lq, hq, d), dtype=compute_dtype)
+    for h in range(hq):
+        kv = h // group
+        s = (q_rot[:, h, :] @ k_rot[:, kv, :].T) * sm_scale                           # [Lq, n]
+        if logit_cap > 0:
+            s = logit_cap * torch.tanh(s / logit_cap)
+        s = s.masked_fill(~visible, float("-inf"))
+        out[:, h, :] = torch.softmax(s, dim=1) @ vs[:, kv, :]
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # whole decode layer for a ragged batch, with per-request state
 # --------------------------------------------------------------------------------------
@@ -292,14 +366,19 @@ class DecodeOracle:
 
     # -- selection for one request -----------------------------------------------------------
     def select(self, layer: int, req_slot: int, q: torch.Tensor, k_pool: torch.Tensor,
-               slot_row: torch.Tensor, n_tokens: int) -> Tuple[int, torch.Tensor, dict]:
+               slot_row: torch.Tensor, n_tokens: int,
+               scoring_query: Optional[torch.Tensor] = None) -> Tuple[int, torch.Tensor, dict]:
         """Returns ``(flag, logical positions, info)`` for one request (token_retrieval.py:375-449).
-        ``q [Hq, D]`` un-rotated; ``slot_row`` is the request's row of the position->slot map."""
+        ``q [Hq, D]`` un-rotated; ``slot_row`` is the request's row of the position->slot map.  A prefill
+        chunk passes its fingerprint as ``scoring_query`` (already rotated and averaged, :380-392)."""
         cfg = self.cfg
         info: dict = {}
         if cfg.n_sel >= n_tokens:                                   # :376-378
             return FLAG_DENSE, torch.arange(n_tokens), info
-        q_rot = rotate_scoring_query(q, cfg.n_local, cfg.rope_base, cfg.rope_scale)   # :380-388
+        if scoring_query is not None:
+            q_rot = scoring_query
+        else:
+            q_rot = rotate_scoring_query(q, cfg.n_local, cfg.rope_base, cfg.rope_scale)   # :380-388
         info["q_rot"] = q_rot
         recompute = True
         entry = self.cache.setdefault((req_slot, layer), _CacheEntry())
@@ -370,6 +449,38 @@ class DecodeOracle:
             infos.append(info)
         return {"out": torch.stack(outs), "flags": flags, "positions": positions,
                 "slots": slots_out, "info": infos}
+
+
+    # -- one prefill chunk of one request ------------------------------------------------------------
+    def extend_chunk(self, layer: int, req_slot: int, q: torch.Tensor, k_new: Optional[torch.Tensor],
+                     v_new: Optional[torch.Tensor], out_cache_loc: Optional[torch.Tensor],
+                     k_pool: torch.Tensor, v_pool: torch.Tensor, slot_row: torch.Tensor, n_tokens: int,
+                     attn_dtype: torch.dtype = torch.float32,
+                     scoring_query: Optional[torch.Tensor] = None) -> dict:
+        """One chunk (at most 512 tokens, token_retrieval.py:716-724, :917) of a prefill, one layer
+        (:726-775).  ``q [Lq, Hq*D]``; the chunk's K/V rows are stored first (:726-734) and
+        ``n_tokens`` counts them; selection uses the chunk's fingerprint (:736-738, :392); a request
+        with ``n_sel >= n_tokens`` attends to all its tokens (:741-744); causal attention over the
+        list (:760-772)."""
+        cfg = self.cfg
+        lq = q.shape[0]
+        if k_new is not None:
+            k_pool[out_cache_loc.long()] = k_new.view(lq, cfg.hkv, cfg.head_dim).to(k_pool.dtype)
+            v_pool[out_cache_loc.long()] = v_new.view(lq, cfg.hkv, cfg.head_dim).to(v_pool.dtype)
+        qh = q.view(lq, cfg.hq, cfg.head_dim)
+        fp = scoring_query if scoring_query is not None else \
+            chunk_fingerprint(qh, cfg.n_local, cfg.rope_base, cfg.rope_scale)
+        flag, pos, info = self.select(layer, req_slot, None, k_pool, slot_row, n_tokens, scoring_query=fp)
+        info["fingerprint"] = fp
+        sl = slot_row[pos.long()]
+        sm_scale = cfg.sm_scale if cfg.sm_scale is not None else cfg.head_dim ** -0.5
+        hq_r, hkv_r = cfg.hq // self.tp, cfg.hkv // self.tp
+        o = torch.cat([
+            sparse_prefill_attention(qh[:, r * hq_r:(r + 1) * hq_r], k_pool[:, r * hkv_r:(r + 1) * hkv_r],
+                                     v_pool[:, r * hkv_r:(r + 1) * hkv_r], sl, sm_scale, cfg.rope_base,
+                                     cfg.rope_scale, cfg.logit_cap, attn_dtype)
+            for r in range(self.tp)], dim=1)
+        return {"out": o.reshape(lq, -1), "flag": flag, "positions": pos, "slots": sl, "info": info}
 
 
 # --------------------------------------------------------------------------------------

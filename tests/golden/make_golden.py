@@ -31,6 +31,14 @@ CASES = [
     ("pool_even6", 8, 2048, 8, 2, 128, 16, 64, 256, 5e5, 6),
 ]
 
+# prefill chunks: name, seed, N (tokens incl. the chunk), chunk length, Hq, Hkv, D, n_init, n_local, top_k, rope_base
+CHUNK_CASES = [
+    ("chunk_gqa4", 21, 2048, 64, 8, 2, 128, 16, 64, 256, 5e5),
+    ("chunk_partial37", 22, 1500, 37, 8, 2, 128, 16, 64, 256, 5e5),
+    ("chunk_llama_512", 23, 8192, 512, 32, 8, 128, 128, 512, 1024, 5e5),
+    ("chunk_dense", 24, 300, 64, 8, 2, 128, 16, 64, 256, 5e5),
+]
+
 
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -47,6 +55,17 @@ def main() -> None:
         records.append({
             "name": name, "seed": seed, "n_tokens": n, "hq": hq, "hkv": hkv, "head_dim": d,
             "n_init": n_init, "n_local": n_local, "top_k": top_k, "rope_base": base, "kernel_size": ks,
+            "slots": None if out is None else [int(x) for x in out.tolist()],
+        })
+        print(name, "dense" if out is None else len(out))
+    for name, seed, n, lq, hq, hkv, d, n_init, n_local, top_k, base in CHUNK_CASES:
+        case = synth.make_layer_case(seed, n, hq, hkv, d, n_init, n_local, base)
+        qc = synth.make_chunk_queries(seed, case, lq, hq, d)
+        out = rv.retrieval_indices(qc, case.k_pool, case.req_to_token[case.req_pool_idx], n, hq, hkv, d,
+                                   n_init, n_local, top_k, base, 1, -1, root=args.reference_root)
+        records.append({
+            "name": name, "seed": seed, "n_tokens": n, "chunk": lq, "hq": hq, "hkv": hkv, "head_dim": d,
+            "n_init": n_init, "n_local": n_local, "top_k": top_k, "rope_base": base, "kernel_size": -1,
             "slots": None if out is None else [int(x) for x in out.tolist()],
         })
         print(name, "dense" if out is None else len(out))

@@ -24,8 +24,13 @@ def _run(case, **over):
     cfg = orc.OracleConfig(1, case["hq"], case["hkv"], case["head_dim"], case["n_init"], case["n_local"],
                            case["top_k"], case["rope_base"], kernel_size=case["kernel_size"], **over)
     o = orc.DecodeOracle(cfg)
+    fp = None
+    if "chunk" in case:                # a prefill chunk: the scoring query is the chunk's fingerprint
+        qc = synth.make_chunk_queries(case["seed"], c, case["chunk"], case["hq"], case["head_dim"])
+        fp = orc.chunk_fingerprint(qc.view(case["chunk"], case["hq"], case["head_dim"]), case["n_local"],
+                                   case["rope_base"], 1.0, fixed_order=over.get("deterministic_topk", True))
     flag, pos, info = o.select(0, c.req_pool_idx, c.q.view(case["hq"], case["head_dim"]), c.k_pool,
-                               c.req_to_token[c.req_pool_idx], case["n_tokens"])
+                               c.req_to_token[c.req_pool_idx], case["n_tokens"], scoring_query=fp)
     return c, flag, pos, info
 
 

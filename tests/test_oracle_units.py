@@ -65,3 +65,28 @@ def test_selection_cache_rule():
     o.reset_request(1)
     f4, _, _ = o.select(0, 1, q, c.k_pool, c.req_to_token[1], 200)
     assert f4 == orc.FLAG_RECOMPUTE and o.retrieval_count[1] == 1
+
+
+def test_prefill_attention_rows_equal_decode_attention_on_prefixes():
+    """Query i of a chunk sees the listed keys up to its own position, rotated as a decode query at that
+    position would be: row i of the causal chunk attention equals decode attention over the list prefix."""
+    torch.manual_seed(3)
+    hq, hkv, d, n, lq = 4, 2, 64, 40, 7
+    kp, vp = torch.randn(64, hkv, d), torch.randn(64, hkv, d)
+    slots = torch.randperm(64)[:n].to(torch.int32)
+    q = torch.randn(lq, hq, d)
+    out = orc.sparse_prefill_attention(q, kp, vp, slots, d ** -0.5, 1e4, 1.0, 0.0, torch.float64)
+    for i in (0, 3, lq - 1):
+        want = orc.sparse_attention(q[i], kp, vp, slots[: n - lq + i + 1], d ** -0.5, 1e4, 1.0, 0.0, torch.float64)
+        assert (out[i] - want).abs().max().item() < 1e-12
+
+
+def test_chunk_fingerprint_fixed_order_matches_torch_mean():
+    torch.manual_seed(4)
+    q = torch.randn(100, 4, 64).bfloat16()
+    a = orc.chunk_fingerprint(q, 16, 1e4, 1.0, True).float()
+    b = orc.chunk_fingerprint(q, 16, 1e4, 1.0, False).float()
+    # identical up to the last bf16 bit where the fp32 sums round differently
+    assert (a - b).abs().max().item() <= 2 ** -8 * b.abs().max().item()
+    one = orc.chunk_fingerprint(q[:1], 16, 1e4, 1.0, True)
+    assert torch.equal(one, orc.rotate_scoring_query(q[0], 16, 1e4, 1.0))
