@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define TS_ABI_VERSION 1
+#define TS_ABI_VERSION 2
 
 /* status codes */
 #define TS_OK 0
@@ -91,7 +91,8 @@ typedef struct ts_config {
     int32_t tp_rank;
     int32_t tp_size;
     uint32_t flags;                /* TS_CFG_* */
-    uint32_t reserved;
+    int32_t prefill_chunk;         /* longest prefill chunk ts_extend_chunk() accepts (the reference uses
+                                    * 512, :917); 0: no prefill workspace is allocated */
     /* Optional host tables built the way RotaryEmbedding builds them (:73-96).  NULL: computed
      * by the library from rope_base / rope_scale.
      *   score_cos_sin: [head_dim/2][2] cos,sin at position n_local*rope_scale (:380-388)
@@ -160,6 +161,50 @@ int ts_reset_request(ts_handle* h, int32_t req_slot, void* stream);
  * and retrieval_indices (:375-449). */
 int ts_decode_layer(ts_handle* h, const ts_decode_args* args);
 
+/*
+ * One chunk of a prefill of ONE request, one layer.  Replaces one iteration of the chunk loop of
+ * patched_radix_attention_extend_forward_flashinfer (:716-775): store the chunk's K/V rows (:726-734),
+ * select with the chunk's fingerprint -- the mean over the chunk of the queries rotated at positions
+ * n_local, n_local+1, ... and rounded to the model dtype (:380-392, :736-738) -- fall back to all tokens
+ * when n_init+top_k+n_local >= seq_len (:741-744), and run causal attention of the chunk's queries over
+ * the list, the chunk being the list's tail: query t sees list entries j <= count - chunk_len + t and sits
+ * at that position; entry j is rotated at position j (:746-772).  The caller loops over chunks of at most
+ * ts_config.prefill_chunk tokens exactly as :716-724 does.
+ *
+ * Needs prefill_chunk > 0 in the configuration, tp_size == 1 and n_init+top_k+n_local >= chunk_len.
+ * The selection cache, when on, is consulted and updated with the fingerprint as in the reference.
+ */
+typedef struct ts_extend_args {
+    uint32_t struct_size;          /* sizeof(ts_extend_args), checked */
+    int32_t layer;
+    int32_t chunk_len;             /* 1 .. prefill_chunk */
+    int32_t req_pool_index;        /* row of req_to_token / request slot (host value) */
+    int32_t seq_len;               /* tokens of the request INCLUDING this chunk (host value) */
+    int32_t reserved;
+    const void* q;                 /* [chunk_len, hq*head_dim], un-rotated */
+    const void* k_new;             /* [chunk_len, hkv*head_dim] or NULL (rows already in the pools) */
+    const void* v_new;
+    const int32_t* out_cache_loc;  /* [chunk_len] pool rows of the chunk's tokens              (:852) */
+    void* k_pool;
+    void* v_pool;
+    int64_t pool_rows;
+    const int32_t* req_to_token;
+    int64_t req_to_token_stride;
+    /* optional device table [chunk_len][head_dim/2][2]: cos, sin of position (n_local + t) * rope_scale
+     * built as RotaryEmbedding builds it (:73-96); NULL: computed in the kernel */
+    const float* chunk_cos_sin;
+    void* out;                     /* [chunk_len, hq*head_dim] */
+    /* optional device outputs for inspection, NULL to skip */
+    int32_t* dbg_sel_slots;        /* [n_sel] */
+    int32_t* dbg_sel_pos;          /* [n_sel] */
+    int32_t* dbg_sel_count;        /* [1] */
+    int32_t* dbg_flags;            /* [1] */
+    void* dbg_fingerprint;         /* [hq*head_dim] model dtype */
+    void* stream;
+} ts_extend_args;
+
+int ts_extend_chunk(ts_handle* h, const ts_extend_args* args);
+
 /* The same step split at the tensor-parallel exchange points (:363-364):
  *   ts_tp_prepare       K/V append, scoring-query rotation, cosine terms -> args->tp_cos
  *   [caller: all_reduce(tp_cos, SUM) when the selection cache is on]
@@ -208,7 +253,8 @@ int ts_launch_count(ts_handle* h, uint64_t* launches);
  * on; ts_timing_end() synchronises, switches it off and returns, per stage, the summed device
  * milliseconds and the number of launches.  Stages: 0 prepare (tensor-parallel form only), 1 the
  * selection kernel (prepare, score, vote, top-k, emit; or its first part under tensor parallelism),
- * 2 its second part under tensor parallelism, 3 attend-split, 4 attend-merge, 5-7 unused.  The
+ * 2 its second part under tensor parallelism, 3 attend-split, 4 attend-merge; prefill chunks: 5 append +
+ * fingerprint, 6 gather + rotate, 7 causal attention.  The
  * reference's counterpart is the
  * cuda_timer context manager (token_retrieval.py:41-53).  Recording adds an event pair per kernel,
  * so throughput numbers are taken with it off. */

@@ -74,15 +74,18 @@ def test_struct_layout_matches_header():
     import subprocess
     import tempfile
     src = ('#include "tokenselect_b200.h"\n#include <stdio.h>\n#include <stddef.h>\n'
-           'int main(){printf("%zu %zu %zu %zu\\n", sizeof(ts_config), sizeof(ts_decode_args),'
-           ' offsetof(ts_config, rope_base), offsetof(ts_decode_args, stream));return 0;}\n')
+           'int main(){printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(ts_config), sizeof(ts_decode_args),'
+           ' offsetof(ts_config, rope_base), offsetof(ts_decode_args, stream), sizeof(ts_extend_args),'
+           ' offsetof(ts_extend_args, chunk_cos_sin), offsetof(ts_config, prefill_chunk));return 0;}\n')
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "s.c"), "w").write(src)
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), os.path.join(d, "s.c"), "-o",
                                os.path.join(d, "s")])
-        a, b, c, e = map(int, subprocess.check_output([os.path.join(d, "s")]).split())
+        a, b, c, e, x, y, z = map(int, subprocess.check_output([os.path.join(d, "s")]).split())
     assert a == C.sizeof(_lib.TsConfig) and b == C.sizeof(_lib.TsDecodeArgs)
     assert c == _lib.TsConfig.rope_base.offset and e == _lib.TsDecodeArgs.stream.offset
+    assert x == C.sizeof(_lib.TsExtendArgs) and y == _lib.TsExtendArgs.chunk_cos_sin.offset
+    assert z == _lib.TsConfig.prefill_chunk.offset
 
 
 def test_rotation_tables_match_oracle_bitwise():
@@ -94,6 +97,11 @@ def test_rotation_tables_match_oracle_bitwise():
     cos, sin = orc.rope_cos_sin(torch.arange(cfg.n_sel + 1, dtype=torch.float32), inv)
     assert torch.equal(attn[..., 0], cos[:, :64]) and torch.equal(attn[..., 1], sin[:, :64])
     assert attn.shape == (cfg.n_sel + 1, 64, 2)
+    # prefill chunk: positions n_local, n_local + 1, ... (token_retrieval.py:380-388)
+    from tokenselect_b200.engine import chunk_rotary_table
+    table = chunk_rotary_table(cfg)
+    cos, sin = orc.rope_cos_sin(torch.arange(64, 64 + cfg.prefill_chunk, dtype=torch.float32), inv)
+    assert torch.equal(table[..., 0], cos[:, :64]) and torch.equal(table[..., 1], sin[:, :64])
 
 
 def test_config_from_reference_style_yaml(tmp_path):

@@ -16,7 +16,7 @@ TS_DTYPE_BF16, TS_DTYPE_F32 = 0, 1
 TS_GQA_MOD, TS_GQA_DIV = 0, 1
 TS_FLAG_DENSE, TS_FLAG_RECOMPUTE, TS_FLAG_REUSE = 0, 1, 2
 TS_CFG_PLAIN_SCORE = 1
-TS_ABI_VERSION = 1
+TS_ABI_VERSION = 2
 
 # every symbol include/tokenselect_b200.h declares
 EXPORTS = [
@@ -24,6 +24,7 @@ EXPORTS = [
     "ts_destroy", "ts_reset_request", "ts_decode_layer", "ts_tp_prepare", "ts_tp_score_vote",
     "ts_tp_select_attend", "ts_get_counters", "ts_last_error", "ts_last_cuda_error", "ts_debug_read",
     "ts_launch_count", "ts_timing_begin", "ts_timing_end", "ts_attend_rows_static", "ts_tp_symmetric_bytes", "ts_tp_attach_peers",
+    "ts_extend_chunk",
 ]
 
 
@@ -35,7 +36,7 @@ class TsConfig(C.Structure):
         ("similarity_threshold", C.c_float), ("gqa_map", C.c_int32), ("rope_base", C.c_double),
         ("rope_scale", C.c_double), ("sm_scale", C.c_float), ("logit_cap", C.c_float), ("max_reqs", C.c_int32),
         ("max_batch", C.c_int32), ("max_ctx", C.c_int32), ("max_total_tokens", C.c_int64),
-        ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("flags", C.c_uint32), ("prefill_chunk", C.c_int32),
         ("score_cos_sin", C.c_void_p), ("attn_cos_sin", C.c_void_p),
     ]
 
@@ -49,6 +50,19 @@ class TsDecodeArgs(C.Structure):
         ("seq_lens", C.c_void_p), ("out", C.c_void_p), ("tp_votes", C.c_void_p), ("tp_cos", C.c_void_p),
         ("dbg_sel_slots", C.c_void_p), ("dbg_sel_pos", C.c_void_p), ("dbg_sel_count", C.c_void_p),
         ("dbg_flags", C.c_void_p), ("stream", C.c_void_p),
+    ]
+
+
+class TsExtendArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("layer", C.c_int32), ("chunk_len", C.c_int32), ("req_pool_index", C.c_int32),
+        ("seq_len", C.c_int32), ("reserved", C.c_int32),
+        ("q", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("out_cache_loc", C.c_void_p),
+        ("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("pool_rows", C.c_int64),
+        ("req_to_token", C.c_void_p), ("req_to_token_stride", C.c_int64), ("chunk_cos_sin", C.c_void_p),
+        ("out", C.c_void_p), ("dbg_sel_slots", C.c_void_p), ("dbg_sel_pos", C.c_void_p),
+        ("dbg_sel_count", C.c_void_p), ("dbg_flags", C.c_void_p), ("dbg_fingerprint", C.c_void_p),
+        ("stream", C.c_void_p),
     ]
 
 
@@ -98,6 +112,7 @@ def load() -> C.CDLL:
     lib.ts_attend_rows_static.argtypes = [C.POINTER(TsAttendStaticArgs)]
     lib.ts_tp_symmetric_bytes.argtypes = [C.POINTER(TsConfig), C.POINTER(C.c_size_t)]
     lib.ts_tp_attach_peers.argtypes = [H, C.POINTER(C.c_uint64), C.c_int32]
+    lib.ts_extend_chunk.argtypes = [H, C.POINTER(TsExtendArgs)]
     if lib.ts_abi_version() != TS_ABI_VERSION:
         raise RuntimeError("libtokenselect_b200.so was built from a different header; rebuild it")
     _lib = lib

@@ -29,6 +29,9 @@ struct ts_handle {
     float** dev_peer_votes;                 // [2][kMaxTp] device array of pointers
     unsigned** dev_peer_flags;              // [kMaxTp]
     int last_batch;
+    // prefill chunks
+    void* ext_fp; int* ext_meta; void* ext_k; void* ext_v; void* ext_q;
+    int ext_rows_k, ext_rows_q;
     char cuda_msg[256];
 };
 
@@ -49,6 +52,7 @@ int validate(const ts_config* c) {
     if (c->gqa_map != TS_GQA_MOD && c->gqa_map != TS_GQA_DIV) return TS_ERR_INVALID_ARG;
     if (c->tp_size < 1 || c->tp_rank < 0 || c->tp_rank >= c->tp_size) return TS_ERR_INVALID_ARG;
     if (!(c->rope_base > 0.0) || !(c->rope_scale > 0.0)) return TS_ERR_INVALID_ARG;
+    if (c->prefill_chunk < 0 || c->prefill_chunk > 4096) return TS_ERR_INVALID_ARG;
     return TS_OK;
 }
 
@@ -111,6 +115,14 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_pc = cv.take((size_t)c->max_reqs * c->n_layers * c->top_k * 4);
     size_t o_valid = cv.take((size_t)c->max_reqs * c->n_layers * 4);
     size_t o_cnt = cv.take((size_t)c->max_reqs * 16);
+    // prefill chunks: fingerprint, (length, slot) pair, compact rotated K / V / Q arrays
+    const int ext = c->prefill_chunk;
+    const int rows_k = (n_sel + 63) / 64 * 64, rows_q = (ext + 63) / 64 * 64;
+    size_t o_xfp = cv.take(ext > 0 ? hd * elem : 16);
+    size_t o_xmeta = cv.take(16);
+    size_t o_xk = cv.take(ext > 0 ? (size_t)c->hkv * rows_k * c->head_dim * elem : 16);
+    size_t o_xv = cv.take(ext > 0 ? (size_t)c->hkv * rows_k * c->head_dim * elem : 16);
+    size_t o_xq = cv.take(ext > 0 ? (size_t)c->hq * rows_q * c->head_dim * elem : 16);
     if (h) {
         unsigned char* a = h->arena;
         LayerParams& p = h->base;
@@ -158,6 +170,9 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.pos_cache = reinterpret_cast<int*>(a + o_pc);
         p.valid = reinterpret_cast<int*>(a + o_valid);
         p.counters = reinterpret_cast<unsigned long long*>(a + o_cnt);
+        h->ext_fp = a + o_xfp; h->ext_meta = reinterpret_cast<int*>(a + o_xmeta);
+        h->ext_k = a + o_xk; h->ext_v = a + o_xv; h->ext_q = a + o_xq;
+        h->ext_rows_k = rows_k; h->ext_rows_q = rows_q;
         h->elem = elem; h->n_sel = n_sel; h->cand_capacity = cap; h->grid = grid;
         h->attn_chunk_tokens = ch; h->attn_chunks = chunks;
     }
@@ -414,6 +429,64 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
     TS_TRY(launch_fused(p, l, fused_tp ? kModeTpFused : kModeAll), "select");
     TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);
+}
+
+int ts_extend_chunk(ts_handle* h, const ts_extend_args* a) {
+    if (!h || !a || a->struct_size != sizeof(ts_extend_args)) return TS_ERR_INVALID_ARG;
+    const ts_config& c = h->cfg;
+    if (c.prefill_chunk < 1 || c.tp_size != 1) return TS_ERR_UNSUPPORTED;
+    if (a->layer < 0 || a->layer >= c.n_layers) return TS_ERR_INVALID_ARG;
+    if (a->chunk_len < 1) return TS_ERR_INVALID_ARG;
+    if (a->chunk_len > c.prefill_chunk) return TS_ERR_CAPACITY;
+    if (a->req_pool_index < 0 || a->req_pool_index >= c.max_reqs) return TS_ERR_INVALID_ARG;
+    if (a->seq_len < a->chunk_len) return TS_ERR_INVALID_ARG;
+    if (a->seq_len > c.max_ctx || a->seq_len > c.max_total_tokens) return TS_ERR_CAPACITY;
+    if (!a->q || !a->k_pool || !a->v_pool || !a->req_to_token || !a->out) return TS_ERR_INVALID_ARG;
+    if ((a->k_new != nullptr) != (a->v_new != nullptr)) return TS_ERR_INVALID_ARG;
+    if (a->k_new && !a->out_cache_loc) return TS_ERR_INVALID_ARG;
+    if (a->pool_rows < 1 || a->req_to_token_stride < 1) return TS_ERR_INVALID_ARG;
+    // the chunk must fit inside the list it closes (otherwise its first queries would see no key at all)
+    if (h->n_sel < a->chunk_len) return TS_ERR_UNSUPPORTED;
+
+    ExtendParams e;
+    memset(&e, 0, sizeof(e));
+    e.hq = c.hq; e.hkv = c.hkv; e.d = c.head_dim; e.group = c.hq / c.hkv;
+    e.n_init = c.n_init; e.n_local = c.n_local; e.n_sel = h->n_sel;
+    e.chunk_len = a->chunk_len; e.seq_len = a->seq_len; e.req = a->req_pool_index; e.layer = a->layer;
+    e.sm_scale = c.sm_scale; e.logit_cap = c.logit_cap; e.rope_base = c.rope_base; e.rope_scale = c.rope_scale;
+    e.q = a->q; e.k_new = a->k_new; e.v_new = a->v_new; e.out_cache_loc = a->out_cache_loc;
+    e.k_pool = a->k_pool; e.v_pool = a->v_pool; e.pool_rows = a->pool_rows;
+    e.chunk_cs = reinterpret_cast<const float2*>(a->chunk_cos_sin);
+    e.out = a->out;
+    e.fp = h->ext_fp; e.meta = h->ext_meta; e.kc = h->ext_k; e.vc = h->ext_v; e.qc = h->ext_q;
+    e.rows_k = h->ext_rows_k; e.rows_q = (a->chunk_len + 63) / 64 * 64;
+    e.sel_slots = h->base.sel_slots; e.sel_count = h->base.sel_count; e.attn_cs = h->base.attn_cs;
+    e.err = h->base.err;
+
+    // the selection kernel sees a batch of one request whose query is the fingerprint
+    ts_decode_args d;
+    memset(&d, 0, sizeof(d));
+    d.struct_size = sizeof(d);
+    d.layer = a->layer; d.batch = 1;
+    d.q = h->ext_fp;
+    d.k_pool = a->k_pool; d.v_pool = a->v_pool; d.pool_rows = a->pool_rows;
+    d.req_to_token = a->req_to_token; d.req_to_token_stride = a->req_to_token_stride;
+    d.req_pool_indices = h->ext_meta + 1; d.seq_lens = h->ext_meta;
+    d.out = a->out;
+    d.dbg_sel_slots = a->dbg_sel_slots; d.dbg_sel_pos = a->dbg_sel_pos;
+    d.dbg_sel_count = a->dbg_sel_count; d.dbg_flags = a->dbg_flags;
+    d.stream = a->stream;
+    LayerParams p; Launch l;
+    int s = fill(h, &d, p, l);
+    if (s != TS_OK) return s;
+    p.q_prerot = 1;
+    TS_TRY(launch_extend_prep(e, l), "extend prepare");
+    TS_TRY(launch_fused(p, l, kModeAll), "select");
+    TS_TRY(launch_extend_attend(e, l), "extend attend");
+    if (a->dbg_fingerprint)
+        TS_TRY(cudaMemcpyAsync(a->dbg_fingerprint, h->ext_fp, (size_t)c.hq * c.head_dim * h->elem,
+                               cudaMemcpyDeviceToDevice, l.stream), "debug copy");
+    return copy_debug(h, &d, p, l.stream);
 }
 
 int ts_get_counters(ts_handle* h, int32_t req_slot, uint64_t* retrievals, uint64_t* reuses, void* stream) {

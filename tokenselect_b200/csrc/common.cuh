@@ -34,6 +34,7 @@ struct LayerParams {
     int tp_size;
     // call
     int layer, batch;
+    int q_prerot;              // 1: `q` already is the rotated, rounded scoring query (a prefill chunk's fingerprint)
     const void* q;
     const void* k_new;
     const void* v_new;
@@ -191,7 +192,8 @@ struct Launch {
     StageTimer* timer;
 };
 
-enum Stage { kStagePrep = 0, kStageSelect = 1, kStageSelectTpB = 2, kStageAttendSplit = 3, kStageAttendMerge = 4 };
+enum Stage { kStagePrep = 0, kStageSelect = 1, kStageSelectTpB = 2, kStageAttendSplit = 3, kStageAttendMerge = 4,
+             kStageExtendPrep = 5, kStageExtendGather = 6, kStageExtendAttend = 7 };
 
 // Bracket every kernel launch with these two: counts the launch and, when timing is on, records an
 // event pair on the launching stream.
@@ -231,6 +233,38 @@ enum FusedMode {
     kModeTpFused = 3,  // like kModeAll, with the vote sum over ranks done in the kernel through peer memory
 };
 
+// One prefill chunk of one request (extend.cu).  Shapes and knobs are copied from the handle; the call
+// fields come from ts_extend_args; the workspace pointers from the arena.
+struct ExtendParams {
+    int hq, hkv, d, group;
+    int n_init, n_local, n_sel;
+    int chunk_len, seq_len, req, layer;
+    float sm_scale, logit_cap;
+    double rope_base, rope_scale;
+    const void* q;              // [chunk_len, hq*d] un-rotated
+    const void* k_new;          // [chunk_len, hkv*d] or null
+    const void* v_new;
+    const int* out_cache_loc;   // [chunk_len]
+    void* k_pool;
+    void* v_pool;
+    long long pool_rows;
+    const float2* chunk_cs;     // [chunk_len, d/2] (cos, sin) of positions (n_local + t) * rope_scale, or null
+    void* out;                  // [chunk_len, hq*d]
+    void* fp;                   // [hq*d] the chunk's scoring query
+    int* meta;                  // [2] sequence length, request slot: what the selection kernel reads as its batch
+    void* kc;                   // [hkv, rows_k, d] listed keys rotated at their list position
+    void* vc;                   // [hkv, rows_k, d] listed values
+    void* qc;                   // [hq, rows_q, d] the chunk's queries rotated at their list position
+    int rows_k, rows_q;         // multiples of 64
+    const int* sel_slots;
+    const int* sel_count;
+    const float2* attn_cs;
+    int* err;
+};
+
+cudaError_t launch_extend_prep(const ExtendParams& e, const Launch& l);
+cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l);
+bool extend_uses_tensor_cores(int dtype, int d, int group);
 cudaError_t launch_prep(const LayerParams& p, const Launch& l);
 cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode);
 cudaError_t launch_attend(const LayerParams& p, const Launch& l);

@@ -190,6 +190,7 @@ __device__ __forceinline__ int checked_slot(const LayerParams& p, const int* row
 // Element e of the rotated, dtype-rounded scoring query of head h (same arithmetic as prep.cuh).
 template <typename T>
 __device__ __forceinline__ T rotated_q(const LayerParams& p, const T* q, int h, int e) {
+    if (p.q_prerot) return q[h * p.d + e];
     const int half = p.d / 2;
     const int i = e < half ? e : e - half;
     const float x1 = to_f32<T>(q[h * p.d + i]);

@@ -86,6 +86,11 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     const int half = p.d / 2;
     for (int e = tid; e < p.hq * half; e += blockDim.x) {
         int h = e / half, i = e % half;
+        if (p.q_prerot) {                                  // a prefill chunk's fingerprint: copy
+            qr[h * p.d + i] = q[h * p.d + i];
+            qr[h * p.d + i + half] = q[h * p.d + i + half];
+            continue;
+        }
         float x1 = to_f32<T>(q[h * p.d + i]);
         float x2 = to_f32<T>(q[h * p.d + i + half]);
         float2 cs = p.score_cs[i];

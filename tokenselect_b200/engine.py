@@ -15,7 +15,7 @@ from typing import Dict, Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import TsConfig, TsDecodeArgs, check
+from ._lib import TsExtendArgs, TsConfig, TsDecodeArgs, check
 
 
 @dataclasses.dataclass
@@ -51,6 +51,7 @@ class TokenSelectConfig:
     plain_score: bool = False              # diagnostic: plain-load scoring kernel for bf16 too
     score_path: str = "auto"               # "auto" | "direct" (keys to registers) | "staged" (bulk copies to smem)
     tp_fused: bool = True                  # tp_size > 1: sum the votes inside the kernel through peer memory
+    prefill_chunk: int = 512               # PREFILL_CHUNK_SIZE (:917); 0: no prefill workspace
 
     @property
     def n_sel(self) -> int:
@@ -81,6 +82,18 @@ def rotary_tables(cfg: TokenSelectConfig):
     ang_a = torch.outer(torch.arange(cfg.n_sel + 1, dtype=torch.float32), inv_freq / cfg.rope_scale)
     attn = torch.stack((ang_a.cos(), ang_a.sin()), dim=-1).contiguous()
     return score, attn
+
+
+def chunk_rotary_table(cfg: TokenSelectConfig) -> torch.Tensor:
+    """cos/sin of the positions a prefill chunk's queries are rotated at before they are averaged into
+    the chunk's fingerprint: ``position_ids = arange(n_local, n_local + Lq)`` times ``rope_scale``
+    (token_retrieval.py:380-388 with :92-96).  ``[prefill_chunk, D/2, 2]`` fp32, built with the same torch
+    expressions as :func:`rotary_tables`."""
+    d = cfg.head_dim
+    inv_freq = 1.0 / (cfg.rope_base ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
+    pos = torch.arange(cfg.n_local, cfg.n_local + cfg.prefill_chunk, dtype=torch.float32) * cfg.rope_scale
+    ang = torch.outer(pos, inv_freq)
+    return torch.stack((ang.cos(), ang.sin()), dim=-1).contiguous()
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -119,6 +132,7 @@ class TokenSelectEngine:
         c.max_total_tokens = max_total
         c.tp_rank, c.tp_size = cfg.tp_rank, cfg.tp_size
         c.flags = (_lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0) | {"auto": 0, "direct": 2, "staged": 4}[cfg.score_path]
+        c.prefill_chunk = int(cfg.prefill_chunk) if cfg.tp_size == 1 else 0
         c.score_cos_sin = score_cs.data_ptr()
         c.attn_cos_sin = attn_cs.data_ptr()
         self._c = c
@@ -133,6 +147,7 @@ class TokenSelectEngine:
             check(self.lib.ts_create(C.byref(c), C.byref(self._h)), "ts_create")
         self.tp_votes = self.tp_cos = None
         self.fused_tp = False
+        self.chunk_cs = chunk_rotary_table(cfg).to(self.device) if c.prefill_chunk > 0 else None
         if cfg.tp_size > 1:
             self.tp_votes = torch.zeros(self.vote_elems, dtype=torch.float32, device=self.device)
             self.tp_cos = torch.zeros(cfg.max_batch * 4, dtype=torch.float32, device=self.device)
@@ -213,7 +228,8 @@ class TokenSelectEngine:
         check(self.lib.ts_launch_count(self._h, C.byref(n)), "ts_launch_count")
         return n.value
 
-    STAGES = ("prepare", "select", "select_tp_b", "attend_split", "attend_merge", "-", "-", "-")
+    STAGES = ("prepare", "select", "select_tp_b", "attend_split", "attend_merge", "extend_prep", "extend_gather",
+              "extend_attend")
 
     def timing_begin(self, max_launches: int = 65536) -> None:
         """Record a CUDA-event pair around every kernel of this handle until ``timing_end``."""
@@ -312,6 +328,60 @@ class TokenSelectEngine:
         n = self.vote_elems if vote_elems is None else min(int(vote_elems), self.vote_elems)
         dist.all_reduce(self.tp_votes[:n], op=dist.ReduceOp.SUM, group=self.group)
         check(self.lib.ts_tp_select_attend(self._h, C.byref(a)), "ts_tp_select_attend", self._h)
+        return out
+
+    def extend_chunk(self, layer: int, q: torch.Tensor, k_new: Optional[torch.Tensor],
+                     v_new: Optional[torch.Tensor], out_cache_loc: Optional[torch.Tensor],
+                     k_pool: torch.Tensor, v_pool: torch.Tensor, req_to_token: torch.Tensor,
+                     req_pool_index: int, seq_len: int, out: Optional[torch.Tensor] = None,
+                     debug: Optional[dict] = None) -> torch.Tensor:
+        """One chunk (at most ``prefill_chunk`` tokens) of one request's prefill, one layer: one iteration of
+        the chunk loop at token_retrieval.py:716-775.  ``q [Lq, Hq*D]``, ``k_new, v_new [Lq, Hkv*D]`` are
+        stored at ``out_cache_loc [Lq]`` first; ``seq_len`` counts the request's tokens including this
+        chunk.  Returns ``[Lq, Hq*D]``.  ``debug`` may hold int32 tensors ``slots, positions [n_sel]``,
+        ``count, flags [1]`` and ``fingerprint [Hq*D]`` (model dtype)."""
+        cfg = self.cfg
+        if self.chunk_cs is None:
+            raise ValueError("prefill needs prefill_chunk > 0 and tp_size == 1")
+        lq = q.shape[0]
+        hd, kd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        if out is None:
+            out = torch.empty_like(q)
+        for name, t, dt in (("q", q, cfg.dtype), ("k_pool", k_pool, cfg.dtype), ("v_pool", v_pool, cfg.dtype),
+                            ("req_to_token", req_to_token, torch.int32), ("out", out, cfg.dtype)):
+            if not t.is_cuda or t.dtype != dt:
+                raise ValueError(f"{name}: expected a CUDA tensor of {dt}, got {t.device} {t.dtype}")
+        if q.numel() != lq * hd or not q.is_contiguous() or not out.is_contiguous() or out.numel() != lq * hd:
+            raise ValueError("q/out must be contiguous [chunk, num_q_heads*head_dim]")
+        if not k_pool.is_contiguous() or not v_pool.is_contiguous() or k_pool.shape != v_pool.shape:
+            raise ValueError("pools must be contiguous [rows, num_kv_heads, head_dim] of equal shape")
+        if req_to_token.dim() != 2 or req_to_token.stride(1) != 1:
+            raise ValueError("req_to_token must be [max_reqs, max_ctx] with unit inner stride")
+        a = TsExtendArgs()
+        a.struct_size = C.sizeof(TsExtendArgs)
+        a.layer, a.chunk_len, a.req_pool_index, a.seq_len = int(layer), int(lq), int(req_pool_index), int(seq_len)
+        a.q = q.data_ptr()
+        if k_new is not None:
+            for name, t in (("k", k_new), ("v", v_new)):
+                if not t.is_cuda or t.dtype != cfg.dtype or not t.is_contiguous() or t.numel() != lq * kd:
+                    raise ValueError(f"{name}: expected contiguous CUDA [chunk, num_kv_heads*head_dim] {cfg.dtype}")
+            if out_cache_loc is None or out_cache_loc.dtype != torch.int32 or not out_cache_loc.is_cuda \
+                    or out_cache_loc.numel() != lq or not out_cache_loc.is_contiguous():
+                raise ValueError("out_cache_loc must be a contiguous CUDA int32 tensor [chunk]")
+            a.k_new, a.v_new, a.out_cache_loc = k_new.data_ptr(), v_new.data_ptr(), out_cache_loc.data_ptr()
+        a.k_pool, a.v_pool, a.pool_rows = k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0]
+        a.req_to_token, a.req_to_token_stride = req_to_token.data_ptr(), req_to_token.stride(0)
+        a.chunk_cos_sin = self.chunk_cs.data_ptr()
+        a.out = out.data_ptr()
+        if debug is not None:
+            a.dbg_sel_slots = debug["slots"].data_ptr()
+            a.dbg_sel_pos = debug["positions"].data_ptr()
+            a.dbg_sel_count = debug["count"].data_ptr()
+            a.dbg_flags = debug["flags"].data_ptr()
+            if "fingerprint" in debug:
+                a.dbg_fingerprint = debug["fingerprint"].data_ptr()
+        a.stream = self._stream()
+        check(self.lib.ts_extend_chunk(self._h, C.byref(a)), "ts_extend_chunk", self._h)
         return out
 
     # The three tensor-parallel stages one by one, for callers that run the exchange themselves

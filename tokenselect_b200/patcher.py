@@ -10,7 +10,8 @@ names, argument meaning and error behaviour of the pieces the decode path touche
   is a pool row, K and V buffers of ``[rows, kv_heads, head_dim]`` per layer (:170, :599-601, :847-848).
 * ``ReqToTokenRetriever``             -- per-request state keyed by request id (:117-163).
 * ``RadixAttention.forward(q, k, v, input_metadata)`` -- the patched forward (:827-842): stores the
-  new K/V, selects, attends, returns ``[batch, heads*head_dim]``.
+  new K/V, selects, attends, returns ``[batch, heads*head_dim]``; in EXTEND mode it runs the chunked
+  prefill of one request (:703-775).
 
 A serving stack integrates by constructing one ``ReqToTokenRetriever`` per model runner (as
 PatchedModelRunner does at :458-469) and assigning ``RadixAttention.forward`` /
@@ -128,6 +129,10 @@ class InputMetadata:
     out_cache_loc: torch.Tensor           # [batch] int32
     token_retriever: TokenSelectEngine = None
     seq_lens_cpu: Optional[List[int]] = None   # optional host copy; bounds the tensor-parallel message
+    # EXTEND only (host values, so that the chunk loop needs no device sync): the request's slot and the
+    # number of its tokens already in the cache before this forward (prefix_lens of the serving stack)
+    req_pool_indices_cpu: Optional[List[int]] = None
+    extend_prefix_lens_cpu: Optional[List[int]] = None
 
 
 def patched_radix_attention_forward(self, q, k, v, input_metadata: InputMetadata):
@@ -150,8 +155,37 @@ def patched_radix_attention_forward(self, q, k, v, input_metadata: InputMetadata
             input_metadata.out_cache_loc, k_pool, v_pool, input_metadata.req_to_token_pool.req_to_token,
             input_metadata.req_pool_indices, input_metadata.seq_lens, vote_elems=ve)
         return o.view(-1, self.tp_q_head_num * self.head_dim)
-    raise NotImplementedError(
-        "only ForwardMode.DECODE runs through tokenselect_b200; prefill stays with the serving stack")
+    if input_metadata.forward_mode == ForwardMode.EXTEND:
+        return patched_radix_attention_extend_forward(self, q, k, v, input_metadata)
+    raise NotImplementedError("ForwardMode.PREFILL is not a mode of the patched stack (:834-841)")
+
+
+def patched_radix_attention_extend_forward(self, q, k, v, input_metadata: InputMetadata):
+    """Replacement for ``patched_radix_attention_extend_forward_flashinfer`` (:703-775): the new tokens of
+    ONE request (the reference asserts a single request, :130, :526-528) go through the layer in chunks of
+    ``PREFILL_CHUNK_SIZE`` (:716-724); every chunk stores its K/V, selects with its fingerprint and runs
+    causal attention over the selected list."""
+    if input_metadata.batch_size != 1:
+        raise NotImplementedError("prefill handles one request per forward, as the reference does")
+    if input_metadata.req_pool_indices_cpu is None or input_metadata.extend_prefix_lens_cpu is None:
+        raise ValueError("EXTEND needs req_pool_indices_cpu and extend_prefix_lens_cpu (host values)")
+    eng = input_metadata.token_retriever
+    chunk = PREFILL_CHUNK_SIZE if PREFILL_CHUNK_SIZE > 0 else eng.cfg.prefill_chunk
+    hd = self.tp_q_head_num * self.head_dim
+    q = q.contiguous().view(-1, hd)
+    total = q.shape[0]
+    req = int(input_metadata.req_pool_indices_cpu[0])
+    prefix = int(input_metadata.extend_prefix_lens_cpu[0])
+    k_pool, v_pool = input_metadata.token_to_kv_pool.get_kv_buffer(self.layer_id)
+    outputs = torch.empty_like(q)
+    for start in range(0, total, chunk):
+        end = min(start + chunk, total)
+        eng.extend_chunk(
+            self.layer_id, q[start:end], None if k is None else k[start:end].contiguous(),
+            None if v is None else v[start:end].contiguous(),
+            None if k is None else input_metadata.out_cache_loc[start:end].contiguous(), k_pool, v_pool,
+            input_metadata.req_to_token_pool.req_to_token, req, prefix + end, out=outputs[start:end])
+    return outputs
 
 
 class RadixAttention:
