@@ -77,16 +77,20 @@ def chunk_fingerprint(q: torch.Tensor, n_local: int, rope_base: float, rope_scal
                       fixed_order: bool = True) -> torch.Tensor:
     """Scoring query of a prefill chunk: the mean over the chunk of the rotated, rounded queries
     (token_retrieval.py:392, ``torch.mean(query, dim=0)``), ``[Hq, D]`` in ``q.dtype``.  ``fixed_order``
-    fixes what torch leaves open: fp32 running sum in ascending query order, one fp32 division by the
-    chunk length, one rounding to the dtype; otherwise ``torch.mean`` itself is called."""
+    fixes what torch leaves open: 32 fp32 partial sums (partial j takes queries j, j+32, ... in ascending
+    order), joined by an XOR butterfly (16, 8, 4, 2, 1), one fp32 division by the chunk length, one
+    rounding to the dtype; otherwise ``torch.mean`` itself is called."""
     rot = rotate_chunk_queries(q, n_local, rope_base, rope_scale)
     if not fixed_order:
         return torch.mean(rot.view(rot.shape[0], -1), dim=0).view(rot.shape[1:])
-    acc = np.zeros(rot.shape[1:], dtype=np.float32)
     rot32 = rot.float().numpy()
+    part = np.zeros((32,) + tuple(rot.shape[1:]), dtype=np.float32)
     for i in range(rot.shape[0]):
-        acc = acc + rot32[i]
-    return torch.from_numpy(acc / np.float32(rot.shape[0])).to(q.dtype)
+        part[i % 32] = part[i % 32] + rot32[i]
+    lanes = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        part = part + part[lanes ^ o]
+    return torch.from_numpy(part[0] / np.float32(rot.shape[0])).to(q.dtype)
 
 
 # --------------------------------------------------------------------------------------

@@ -255,7 +255,7 @@ struct ExtendParams {
     void* kc;                   // [hkv, rows_k, d] listed keys rotated at their list position
     void* vc;                   // [hkv, rows_k, d] listed values
     void* qc;                   // [hq, rows_q, d] the chunk's queries rotated at their list position
-    int rows_k, rows_q;         // multiples of 64
+    int rows_k, rows_q;         // padded row counts: multiples of 64 and of 128
     const int* sel_slots;
     const int* sel_count;
     const float2* attn_cs;

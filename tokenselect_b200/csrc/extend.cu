@@ -25,55 +25,92 @@ namespace ts {
 namespace {
 
 constexpr int kExtThreads = 256;
-constexpr int kTile = 64;                 // queries per CTA and keys per block of the tensor-core kernel
+constexpr int kTile = 64;                 // keys per block of the tensor-core kernel
 constexpr float kLog2eX = 1.4426950408889634f;
-
-template <typename T>
-__device__ __forceinline__ size_t swz(size_t row_base_elems, int row, int e, bool swizzle) {
-    if (!swizzle) return row_base_elems + e;
-    constexpr int per = 16 / (int)sizeof(T);               // elements per 16-byte piece
-    const int piece = e / per, within = e - piece * per;
-    return row_base_elems + (size_t)((piece ^ (row & 7)) * per + within);
-}
 
 // ------------------------------------------------------------------------------------------------
 // 1. K/V rows of the chunk into the pools; fingerprint; the (length, request) pair the selection kernel reads
 // ------------------------------------------------------------------------------------------------
+// Fingerprint: a warp owns eight adjacent rotation pairs (h, i0..i0+7).  Lane j rotates the queries
+// t = j, j+32, ... at position (n_local + t) * rope_scale, rounds each to the model dtype (:98-107) and
+// sums them in fp32 in ascending t; an XOR butterfly (16, 8, 4, 2, 1) joins the 32 partial sums; one fp32
+// division by the chunk length, one rounding.  (torch.mean leaves the order open; this one is fixed.)
 template <typename T>
 __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendParams e) {
     if (*(volatile int*)e.err != 0) return;
     const int half = e.d / 2, hd = e.hq * e.d;
-    const int fp_blocks = (e.hq * half + kExtThreads - 1) / kExtThreads;
+    const int groups = e.hq * half / 8;                                   // pair groups == warps needed
+    const int fp_blocks = (groups + kExtThreads / 32 - 1) / (kExtThreads / 32);
     const int lq = e.chunk_len;
     if (blockIdx.x == 0 && threadIdx.x == 0) { e.meta[0] = e.seq_len; e.meta[1] = e.req; }
     if ((int)blockIdx.x < fp_blocks) {
-        // Pair (h, i): every query of the chunk rotated at position (n_local + t) * rope_scale and rounded
-        // to the model dtype (:98-107), summed in fp32 in ascending t, divided once, rounded once.
-        const int pidx = blockIdx.x * kExtThreads + threadIdx.x;
-        if (pidx >= e.hq * half) return;
-        const int h = pidx / half, i = pidx - h * half;
-        const T* q = reinterpret_cast<const T*>(e.q) + (size_t)h * e.d + i;
-        const float inv = (float)(1.0 / pow(e.rope_base, (double)(2 * i) / (double)e.d));
-        float acc1 = 0.f, acc2 = 0.f;
-#pragma unroll 4
-        for (int t = 0; t < lq; ++t) {
-            const float x1 = to_f32<T>(q[(size_t)t * hd]);
-            const float x2 = to_f32<T>(q[(size_t)t * hd + half]);
-            float2 cs;
-            if (e.chunk_cs != nullptr) {
-                cs = e.chunk_cs[(size_t)t * half + i];
-            } else {
-                const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv);
-                cs = make_float2(cosf(ang), sinf(ang));
-            }
-            const float r1 = __fadd_rn(__fmul_rn(x1, cs.x), __fmul_rn(-x2, cs.y));
-            const float r2 = __fadd_rn(__fmul_rn(x2, cs.x), __fmul_rn(x1, cs.y));
-            acc1 = __fadd_rn(acc1, to_f32<T>(from_f32<T>(r1)));
-            acc2 = __fadd_rn(acc2, to_f32<T>(from_f32<T>(r2)));
+        const int lane = threadIdx.x & 31;
+        const int grp = blockIdx.x * (kExtThreads / 32) + (threadIdx.x >> 5);
+        if (grp >= groups) return;
+        const int h = grp / (half / 8), i0 = (grp - h * (half / 8)) * 8;
+        const T* q = reinterpret_cast<const T*>(e.q) + (size_t)h * e.d + i0;
+        float inv[8];
+        if (e.chunk_cs == nullptr) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) inv[u] = (float)(1.0 / pow(e.rope_base, (double)(2 * (i0 + u)) / (double)e.d));
         }
-        T* fp = reinterpret_cast<T*>(e.fp) + (size_t)h * e.d + i;
-        fp[0] = from_f32<T>(__fdiv_rn(acc1, (float)lq));
-        fp[half] = from_f32<T>(__fdiv_rn(acc2, (float)lq));
+        float acc1[8], acc2[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { acc1[u] = 0.f; acc2[u] = 0.f; }
+#pragma unroll 4
+        for (int t = lane; t < lq; t += 32) {
+            T x1[8], x2[8];
+            if constexpr (sizeof(T) == 2) {
+                *reinterpret_cast<uint4*>(x1) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
+                *reinterpret_cast<uint4*>(x2) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; u += 4) {
+                    *reinterpret_cast<float4*>(x1 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
+                    *reinterpret_cast<float4*>(x2 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
+                }
+            }
+            float2 cs[8];
+            if (e.chunk_cs != nullptr) {
+                const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float4 v = src[u];
+                    cs[2 * u] = make_float2(v.x, v.y);
+                    cs[2 * u + 1] = make_float2(v.z, v.w);
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
+                    cs[u] = make_float2(cosf(ang), sinf(ang));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float a = to_f32<T>(x1[u]), b = to_f32<T>(x2[u]);
+                const float r1 = __fadd_rn(__fmul_rn(a, cs[u].x), __fmul_rn(-b, cs[u].y));
+                const float r2 = __fadd_rn(__fmul_rn(b, cs[u].x), __fmul_rn(a, cs[u].y));
+                acc1[u] = __fadd_rn(acc1[u], to_f32<T>(from_f32<T>(r1)));
+                acc2[u] = __fadd_rn(acc2[u], to_f32<T>(from_f32<T>(r2)));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                acc1[u] = __fadd_rn(acc1[u], __shfl_xor_sync(0xffffffffu, acc1[u], o));
+                acc2[u] = __fadd_rn(acc2[u], __shfl_xor_sync(0xffffffffu, acc2[u], o));
+            }
+        }
+        if (lane == 0) {
+            T* fp = reinterpret_cast<T*>(e.fp) + (size_t)h * e.d + i0;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                fp[u] = from_f32<T>(__fdiv_rn(acc1[u], (float)lq));
+                fp[half + u] = from_f32<T>(__fdiv_rn(acc2[u], (float)lq));
+            }
+        }
         return;
     }
     if (e.k_new == nullptr) return;
@@ -92,69 +129,115 @@ __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendPa
 // ------------------------------------------------------------------------------------------------
 // 3. compact arrays: kc, vc [hkv][rows_k][d], qc [hq][rows_q][d]; rows beyond the list / the chunk are zero
 // ------------------------------------------------------------------------------------------------
+// A thread owns eight adjacent rotation pairs of one (row, head): elements i0..i0+7 of both halves, i.e.
+// one 16-byte piece per half in bf16.
+template <typename T>
+__device__ __forceinline__ void load8(const T* src, float (&x)[8]) {
+    if constexpr (sizeof(T) == 2) {
+        T raw[8];
+        *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) x[u] = to_f32<T>(raw[u]);
+    } else {
+#pragma unroll
+        for (int u = 0; u < 8; u += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(src + u);
+            x[u] = v.x; x[u + 1] = v.y; x[u + 2] = v.z; x[u + 3] = v.w;
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* row_base, int row, int e0, const float (&x)[8], bool swizzle) {
+    if constexpr (sizeof(T) == 2) {
+        T raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) raw[u] = from_f32<T>(x[u]);
+        const int piece = e0 >> 3;
+        *reinterpret_cast<uint4*>(row_base + ((swizzle ? (piece ^ (row & 7)) : piece) << 3)) = *reinterpret_cast<uint4*>(raw);
+    } else {
+#pragma unroll
+        for (int u = 0; u < 8; u += 4)
+            *reinterpret_cast<float4*>(row_base + e0 + u) = make_float4(x[u], x[u + 1], x[u + 2], x[u + 3]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const ExtendParams e, const int swizzle) {
     if (*(volatile int*)e.err != 0) return;
     const int half = e.d / 2;
-    const int per_block = kExtThreads / half;
-    const int item = blockIdx.x * per_block + threadIdx.x / half;
-    const int i = threadIdx.x % half;
+    const int tpi = half / 8;                                             // threads per (row, head) item
+    const int per_block = kExtThreads / tpi;
+    const int item = blockIdx.x * per_block + threadIdx.x / tpi;
+    const int i0 = (threadIdx.x % tpi) * 8;
     const int count = min(*e.sel_count, e.n_sel);
     const int lq = e.chunk_len;
     const int k_items = e.rows_k * e.hkv;
+    float z[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) z[u] = 0.f;
     if (item < k_items) {
         const int j = item / e.hkv, kv = item - j * e.hkv;
-        float r1 = 0.f, r2 = 0.f, v1 = 0.f, v2 = 0.f;
-        if (j < count) {
-            int slot = e.sel_slots[j];
-            if ((unsigned long long)(long long)slot >= (unsigned long long)e.pool_rows) {
-                set_error(e.err, TS_ERR_BAD_SLOT, slot);
-                slot = 0;
-            }
-            const T* kr = reinterpret_cast<const T*>(e.k_pool) + ((size_t)slot * e.hkv + kv) * e.d;
-            const T* vr = reinterpret_cast<const T*>(e.v_pool) + ((size_t)slot * e.hkv + kv) * e.d;
-            const float x1 = to_f32<T>(kr[i]), x2 = to_f32<T>(kr[i + half]);
-            const float2 cs = e.attn_cs[(size_t)j * half + i];          // list position j (:820-822)
-            r1 = x1 * cs.x - x2 * cs.y;
-            r2 = x2 * cs.x + x1 * cs.y;
-            v1 = to_f32<T>(vr[i]);
-            v2 = to_f32<T>(vr[i + half]);
+        T* kc = reinterpret_cast<T*>(e.kc) + ((size_t)kv * e.rows_k + j) * e.d;
+        T* vc = reinterpret_cast<T*>(e.vc) + ((size_t)kv * e.rows_k + j) * e.d;
+        if (j >= count) {
+            store8<T>(kc, j, i0, z, swizzle); store8<T>(kc, j, i0 + half, z, swizzle);
+            store8<T>(vc, j, i0, z, swizzle); store8<T>(vc, j, i0 + half, z, swizzle);
+            return;
         }
-        const size_t base = ((size_t)kv * e.rows_k + j) * e.d;
-        T* kc = reinterpret_cast<T*>(e.kc);
-        T* vc = reinterpret_cast<T*>(e.vc);
-        kc[swz<T>(base, j, i, swizzle)] = from_f32<T>(r1);
-        kc[swz<T>(base, j, i + half, swizzle)] = from_f32<T>(r2);
-        vc[swz<T>(base, j, i, swizzle)] = from_f32<T>(v1);
-        vc[swz<T>(base, j, i + half, swizzle)] = from_f32<T>(v2);
+        int slot = e.sel_slots[j];
+        if ((unsigned long long)(long long)slot >= (unsigned long long)e.pool_rows) {
+            set_error(e.err, TS_ERR_BAD_SLOT, slot);
+            slot = 0;
+        }
+        const T* kr = reinterpret_cast<const T*>(e.k_pool) + ((size_t)slot * e.hkv + kv) * e.d;
+        const T* vr = reinterpret_cast<const T*>(e.v_pool) + ((size_t)slot * e.hkv + kv) * e.d;
+        float x1[8], x2[8], v1[8], v2[8], r1[8], r2[8];
+        load8<T>(kr + i0, x1); load8<T>(kr + i0 + half, x2);
+        load8<T>(vr + i0, v1); load8<T>(vr + i0 + half, v2);
+        const float2* cs = e.attn_cs + (size_t)j * half + i0;            // list position j (:820-822)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float2 c = cs[u];
+            r1[u] = x1[u] * c.x - x2[u] * c.y;
+            r2[u] = x2[u] * c.x + x1[u] * c.y;
+        }
+        store8<T>(kc, j, i0, r1, swizzle); store8<T>(kc, j, i0 + half, r2, swizzle);
+        store8<T>(vc, j, i0, v1, swizzle); store8<T>(vc, j, i0 + half, v2, swizzle);
         return;
     }
     const int qitem = item - k_items;
     if (qitem >= e.rows_q * e.hq) return;
     const int t = qitem / e.hq, h = qitem - t * e.hq;
-    float r1 = 0.f, r2 = 0.f;
-    if (t < lq) {
-        const int pos = count - lq + t;                                   // the chunk closes the list
-        const T* qr = reinterpret_cast<const T*>(e.q) + ((size_t)t * e.hq + h) * e.d;
-        const float x1 = to_f32<T>(qr[i]), x2 = to_f32<T>(qr[i + half]);
-        const float2 cs = e.attn_cs[(size_t)max(pos, 0) * half + i];
-        r1 = x1 * cs.x - x2 * cs.y;
-        r2 = x2 * cs.x + x1 * cs.y;
+    T* qc = reinterpret_cast<T*>(e.qc) + ((size_t)h * e.rows_q + t) * e.d;
+    if (t >= lq) {
+        store8<T>(qc, t, i0, z, swizzle); store8<T>(qc, t, i0 + half, z, swizzle);
+        return;
     }
-    const size_t base = ((size_t)h * e.rows_q + t) * e.d;
-    T* qc = reinterpret_cast<T*>(e.qc);
-    qc[swz<T>(base, t, i, swizzle)] = from_f32<T>(r1);
-    qc[swz<T>(base, t, i + half, swizzle)] = from_f32<T>(r2);
+    const int pos = max(count - lq + t, 0);                               // the chunk closes the list
+    const T* qr = reinterpret_cast<const T*>(e.q) + ((size_t)t * e.hq + h) * e.d;
+    float x1[8], x2[8], r1[8], r2[8];
+    load8<T>(qr + i0, x1); load8<T>(qr + i0 + half, x2);
+    const float2* cs = e.attn_cs + (size_t)pos * half + i0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const float2 c = cs[u];
+        r1[u] = x1[u] * c.x - x2[u] * c.y;
+        r2[u] = x2[u] * c.x + x1[u] * c.y;
+    }
+    store8<T>(qc, t, i0, r1, swizzle); store8<T>(qc, t, i0 + half, r2, swizzle);
 }
 
 // ------------------------------------------------------------------------------------------------
 // 4a. causal attention on the compact arrays, tensor cores (bf16, head_dim 128)
 // ------------------------------------------------------------------------------------------------
-// grid (rows_q / 64, hq), 128 threads.  Warp w owns query rows 16w..16w+15 of the tile; keys in blocks of 64,
-// two stages, each block's K and V tile (16 KB each, contiguous in the compact arrays) fetched by one bulk
-// copy.  S = Q K^T and O += P V with mma.sync m16n8k16 (bf16 in, fp32 accumulate), softmax in base 2.
+// grid (rows_q / 128, hq), 128 threads.  Warp w owns query rows 32w..32w+31 of the tile (two 16-row mma
+// tiles, so every K / V fragment read from shared memory feeds two mma); keys in blocks of 64, two stages,
+// each block's K and V tile (16 KB each, contiguous in the compact arrays) fetched by one bulk copy.
+// S = Q K^T and O += P V with mma.sync m16n8k16 (bf16 in, fp32 accumulate), softmax in base 2.  The
+// query fragments are re-read from shared memory in every block (registers hold the 32 x 128 output).
+constexpr int kQTile = 128;
 struct ExtSmem {
-    unsigned char q[kTile * 256];
+    unsigned char q[kQTile * 256];
     unsigned char k[2][kTile * 256];
     unsigned char v[2][kTile * 256];
     uint64_t qbar, full[2];
@@ -165,20 +248,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(128, 2) extend_attend_tc_kernel(const ExtendParams e) {
+__global__ void __launch_bounds__(128, 1) extend_attend_tc_kernel(const ExtendParams e) {
     extern __shared__ __align__(128) unsigned char ext_dyn[];
     ExtSmem& sm = *reinterpret_cast<ExtSmem*>(ext_dyn);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int qt = blockIdx.x, h = blockIdx.y, kv = h / e.group;
     const int lq = e.chunk_len;
-    if (*(volatile int*)e.err != 0 || qt * kTile >= lq) return;
+    if (*(volatile int*)e.err != 0 || qt * kQTile >= lq) return;
     const int count = min(*e.sel_count, e.n_sel);
     const int base_vis = count - lq;                         // query row r sees list entries j <= base_vis + r
-    const int kmax = min(count - 1, base_vis + qt * kTile + kTile - 1);
+    const int kmax = min(count - 1, base_vis + qt * kQTile + kQTile - 1);
     const int nblk = kmax / kTile + 1;
     bool dead = false;
 
-    const __nv_bfloat16* qsrc = reinterpret_cast<const __nv_bfloat16*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * kTile) * 128;
+    const __nv_bfloat16* qsrc = reinterpret_cast<const __nv_bfloat16*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * kQTile) * 128;
     const __nv_bfloat16* ksrc = reinterpret_cast<const __nv_bfloat16*>(e.kc) + (size_t)kv * e.rows_k * 128;
     const __nv_bfloat16* vsrc = reinterpret_cast<const __nv_bfloat16*>(e.vc) + (size_t)kv * e.rows_k * 128;
     if (tid == 0) {
@@ -186,8 +269,8 @@ __global__ void __launch_bounds__(128, 2) extend_attend_tc_kernel(const ExtendPa
         mbar_init(smem_u32(&sm.full[0]), 1);
         mbar_init(smem_u32(&sm.full[1]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        mbar_expect_tx(smem_u32(&sm.qbar), kTile * 256);
-        bulk_g2s(smem_u32(sm.q), qsrc, kTile * 256, smem_u32(&sm.qbar));
+        mbar_expect_tx(smem_u32(&sm.qbar), kQTile * 256);
+        bulk_g2s(smem_u32(sm.q), qsrc, kQTile * 256, smem_u32(&sm.qbar));
         for (int s = 0; s < 2 && s < nblk; ++s) {
             mbar_expect_tx(smem_u32(&sm.full[s]), 2 * kTile * 256);
             bulk_g2s(smem_u32(sm.k[s]), ksrc + (size_t)s * kTile * 128, kTile * 256, smem_u32(&sm.full[s]));
@@ -195,103 +278,117 @@ __global__ void __launch_bounds__(128, 2) extend_attend_tc_kernel(const ExtendPa
         }
     }
     __syncthreads();
-
-    // query fragments: 8 k-steps of 16
-    uint32_t qa[8][4];
     mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40);
-    {
-        const int row = warp * 16 + (lane & 15);
-        const uint32_t rbase = smem_u32(sm.q) + row * 256;
+
+    float o[2][16][4];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            const int piece = 2 * ks + (lane >> 4);
-            ldmatrix_x4(qa[ks], rbase + ((piece ^ (row & 7)) << 4));
-        }
-    }
-    float o[16][4];
+    for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-    for (int n = 0; n < 16; ++n) { o[n][0] = 0.f; o[n][1] = 0.f; o[n][2] = 0.f; o[n][3] = 0.f; }
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    const int row0 = qt * kTile + warp * 16 + g;
-    const int lim0 = base_vis + row0, lim1 = lim0 + 8;
+        for (int n = 0; n < 16; ++n) { o[mt][n][0] = 0.f; o[mt][n][1] = 0.f; o[mt][n][2] = 0.f; o[mt][n][3] = 0.f; }
+    float m_run[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l_run[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+    const int row_base = qt * kQTile + warp * 32;            // first query row of this warp
     const float scale = e.sm_scale;
     const float cap = e.logit_cap;
+    // ldmatrix source of the query fragments: row of the 128-row tile, 16-byte piece selector
+    const int qrow0 = warp * 32 + (lane & 15);
+    const uint32_t qb0 = smem_u32(sm.q) + qrow0 * 256, qb1 = qb0 + 16 * 256;
+    const int qsw = qrow0 & 7, qhi = lane >> 4;              // (row + 16) & 7 == row & 7
 
     for (int blk = 0; blk < nblk; ++blk) {
         const int s = blk & 1;
         mbar_wait(smem_u32(&sm.full[s]), (uint32_t)((blk >> 1) & 1), e.err, dead, 41);
-        float sc[8][4];
+        float sc[2][8][4];
 #pragma unroll
-        for (int n = 0; n < 8; ++n) { sc[n][0] = 0.f; sc[n][1] = 0.f; sc[n][2] = 0.f; sc[n][3] = 0.f; }
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int n = 0; n < 8; ++n) { sc[mt][n][0] = 0.f; sc[mt][n][1] = 0.f; sc[mt][n][2] = 0.f; sc[mt][n][3] = 0.f; }
         const uint32_t kb = smem_u32(sm.k[s]);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
+            uint32_t qa0[4], qa1[4];
+            const int qpiece = ((2 * ks + qhi) ^ qsw) << 4;
+            ldmatrix_x4(qa0, qb0 + qpiece);
+            ldmatrix_x4(qa1, qb1 + qpiece);
 #pragma unroll
             for (int np = 0; np < 4; ++np) {
                 const int row = np * 16 + (lane & 7) + ((lane >> 4) << 3);
                 const int piece = 2 * ks + ((lane >> 3) & 1);
                 uint32_t b[4];
                 ldmatrix_x4(b, kb + row * 256 + ((piece ^ (row & 7)) << 4));
-                mma_bf16_16816(sc[2 * np], qa[ks], b[0], b[1]);
-                mma_bf16_16816(sc[2 * np + 1], qa[ks], b[2], b[3]);
+                mma_bf16_16816(sc[0][2 * np], qa0, b[0], b[1]);
+                mma_bf16_16816(sc[0][2 * np + 1], qa0, b[2], b[3]);
+                mma_bf16_16816(sc[1][2 * np], qa1, b[0], b[1]);
+                mma_bf16_16816(sc[1][2 * np + 1], qa1, b[2], b[3]);
             }
         }
-        // scale, soft cap, causal mask, base-2 units
+        // scale, soft cap, causal mask, base-2 units; online softmax per row
         const int key0 = blk * kTile + 2 * t4;
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        const bool need_mask = blk * kTile + kTile - 1 > base_vis + row_base;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int mt = 0; mt < 2; ++mt) {
+            const int lim0 = base_vis + row_base + mt * 16 + g, lim1 = lim0 + 8;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float x = sc[n][c] * scale;
-                if (cap > 0.f) x = cap * tanhf(x / cap);
-                x *= kLog2eX;
-                const int key = key0 + n * 8 + (c & 1);
-                const int lim = (c < 2) ? lim0 : lim1;
-                if (key > lim) x = -INFINITY;
-                sc[n][c] = x;
+            for (int n = 0; n < 8; ++n) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float x = sc[mt][n][c] * scale;
+                    if (cap > 0.f) x = cap * tanhf(x / cap);
+                    x *= kLog2eX;
+                    if (need_mask) {
+                        const int key = key0 + n * 8 + (c & 1);
+                        if (key > ((c < 2) ? lim0 : lim1)) x = -INFINITY;
+                    }
+                    sc[mt][n][c] = x;
+                }
+                mx0 = fmaxf(mx0, fmaxf(sc[mt][n][0], sc[mt][n][1]));
+                mx1 = fmaxf(mx1, fmaxf(sc[mt][n][2], sc[mt][n][3]));
             }
-            mx0 = fmaxf(mx0, fmaxf(sc[n][0], sc[n][1]));
-            mx1 = fmaxf(mx1, fmaxf(sc[n][2], sc[n][3]));
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-        // a row whose every entry so far is masked keeps (max, sum) = (-inf, 0) and contributes nothing
-        const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float corr0 = exp2f(m_run[0] - ref0), corr1 = exp2f(m_run[1] - ref1);
-        m_run[0] = mn0; m_run[1] = mn1;
-        float sum0 = 0.f, sum1 = 0.f;
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m_run[mt][0], mx0), mn1 = fmaxf(m_run[mt][1], mx1);
+            // a row whose every entry so far is masked keeps (max, sum) = (-inf, 0) and contributes nothing
+            const float ref0 = mn0 == -INFINITY ? 0.f : mn0, ref1 = mn1 == -INFINITY ? 0.f : mn1;
+            const float corr0 = exp2f(m_run[mt][0] - ref0), corr1 = exp2f(m_run[mt][1] - ref1);
+            m_run[mt][0] = mn0; m_run[mt][1] = mn1;
+            float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-            sc[n][0] = exp2f(sc[n][0] - ref0); sc[n][1] = exp2f(sc[n][1] - ref0);
-            sc[n][2] = exp2f(sc[n][2] - ref1); sc[n][3] = exp2f(sc[n][3] - ref1);
-            sum0 += sc[n][0] + sc[n][1];
-            sum1 += sc[n][2] + sc[n][3];
-        }
-        l_run[0] = l_run[0] * corr0 + sum0;
-        l_run[1] = l_run[1] * corr1 + sum1;
+            for (int n = 0; n < 8; ++n) {
+                sc[mt][n][0] = exp2f(sc[mt][n][0] - ref0); sc[mt][n][1] = exp2f(sc[mt][n][1] - ref0);
+                sc[mt][n][2] = exp2f(sc[mt][n][2] - ref1); sc[mt][n][3] = exp2f(sc[mt][n][3] - ref1);
+                sum0 += sc[mt][n][0] + sc[mt][n][1];
+                sum1 += sc[mt][n][2] + sc[mt][n][3];
+            }
+            l_run[mt][0] = l_run[mt][0] * corr0 + sum0;
+            l_run[mt][1] = l_run[mt][1] * corr1 + sum1;
 #pragma unroll
-        for (int n = 0; n < 16; ++n) { o[n][0] *= corr0; o[n][1] *= corr0; o[n][2] *= corr1; o[n][3] *= corr1; }
+            for (int n = 0; n < 16; ++n) { o[mt][n][0] *= corr0; o[mt][n][1] *= corr0; o[mt][n][2] *= corr1; o[mt][n][3] *= corr1; }
+        }
         // O += P V
         const uint32_t vb = smem_u32(sm.v[s]);
 #pragma unroll
         for (int kb16 = 0; kb16 < 4; ++kb16) {
-            uint32_t a[4];
-            a[0] = pack_bf16(sc[2 * kb16][0], sc[2 * kb16][1]);
-            a[1] = pack_bf16(sc[2 * kb16][2], sc[2 * kb16][3]);
-            a[2] = pack_bf16(sc[2 * kb16 + 1][0], sc[2 * kb16 + 1][1]);
-            a[3] = pack_bf16(sc[2 * kb16 + 1][2], sc[2 * kb16 + 1][3]);
+            uint32_t a0[4], a1[4];
+            a0[0] = pack_bf16(sc[0][2 * kb16][0], sc[0][2 * kb16][1]);
+            a0[1] = pack_bf16(sc[0][2 * kb16][2], sc[0][2 * kb16][3]);
+            a0[2] = pack_bf16(sc[0][2 * kb16 + 1][0], sc[0][2 * kb16 + 1][1]);
+            a0[3] = pack_bf16(sc[0][2 * kb16 + 1][2], sc[0][2 * kb16 + 1][3]);
+            a1[0] = pack_bf16(sc[1][2 * kb16][0], sc[1][2 * kb16][1]);
+            a1[1] = pack_bf16(sc[1][2 * kb16][2], sc[1][2 * kb16][3]);
+            a1[2] = pack_bf16(sc[1][2 * kb16 + 1][0], sc[1][2 * kb16 + 1][1]);
+            a1[3] = pack_bf16(sc[1][2 * kb16 + 1][2], sc[1][2 * kb16 + 1][3]);
 #pragma unroll
             for (int dp = 0; dp < 8; ++dp) {
                 const int row = kb16 * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
                 const int piece = 2 * dp + (lane >> 4);
                 uint32_t b[4];
                 ldmatrix_x4_trans(b, vb + row * 256 + ((piece ^ (row & 7)) << 4));
-                mma_bf16_16816(o[2 * dp], a, b[0], b[1]);
-                mma_bf16_16816(o[2 * dp + 1], a, b[2], b[3]);
+                mma_bf16_16816(o[0][2 * dp], a0, b[0], b[1]);
+                mma_bf16_16816(o[0][2 * dp + 1], a0, b[2], b[3]);
+                mma_bf16_16816(o[1][2 * dp], a1, b[0], b[1]);
+                mma_bf16_16816(o[1][2 * dp + 1], a1, b[2], b[3]);
             }
         }
         __syncthreads();                                    // every warp is done with stage s
@@ -302,22 +399,29 @@ __global__ void __launch_bounds__(128, 2) extend_attend_tc_kernel(const ExtendPa
             bulk_g2s(smem_u32(sm.v[s]), vsrc + (size_t)(blk + 2) * kTile * 128, kTile * 256, smem_u32(&sm.full[s]));
         }
     }
-    // the row sums were kept per thread: join the four threads of a row
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-    }
-    const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out);
     const size_t hd = (size_t)e.hq * 128;
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
-        const int col = h * 128 + n * 8 + 2 * t4;
-        if (row0 < lq)
-            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row0 * hd + col) = __floats2bfloat162_rn(o[n][0] * inv0, o[n][1] * inv0);
-        if (row0 + 8 < lq)
-            *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(row0 + 8) * hd + col) = __floats2bfloat162_rn(o[n][2] * inv1, o[n][3] * inv1);
+    for (int mt = 0; mt < 2; ++mt) {
+        // the row sums were kept per thread: join the four threads of a row
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l_run[mt][r] += __shfl_xor_sync(0xffffffffu, l_run[mt][r], 1);
+            l_run[mt][r] += __shfl_xor_sync(0xffffffffu, l_run[mt][r], 2);
+        }
+        const float inv0 = l_run[mt][0] > 0.f ? 1.f / l_run[mt][0] : 0.f;
+        const float inv1 = l_run[mt][1] > 0.f ? 1.f / l_run[mt][1] : 0.f;
+        const int row0 = row_base + mt * 16 + g;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            const int col = h * 128 + n * 8 + 2 * t4;
+            if (row0 < lq)
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row0 * hd + col) =
+                    __floats2bfloat162_rn(o[mt][n][0] * inv0, o[mt][n][1] * inv0);
+            if (row0 + 8 < lq)
+                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(row0 + 8) * hd + col) =
+                    __floats2bfloat162_rn(o[mt][n][2] * inv1, o[mt][n][3] * inv1);
+        }
     }
 }
 
@@ -365,8 +469,8 @@ __global__ void __launch_bounds__(kExtThreads) extend_attend_plain_kernel(const 
 
 template <typename T>
 cudaError_t launch_extend_prep_t(const ExtendParams& e, const Launch& l) {
-    const int half = e.d / 2;
-    const int fp_blocks = (e.hq * half + kExtThreads - 1) / kExtThreads;
+    const int groups = e.hq * (e.d / 2) / 8;
+    const int fp_blocks = (groups + kExtThreads / 32 - 1) / (kExtThreads / 32);
     const int row_vec = e.hkv * e.d * (int)sizeof(T) / 16;
     int app = e.k_new ? (e.chunk_len * row_vec + kExtThreads - 1) / kExtThreads : 0;
     if (app > 4 * l.num_sms) app = 4 * l.num_sms;
@@ -390,7 +494,7 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     const bool tc = extend_uses_tensor_cores(l.dtype, e.d, e.group);
     const int half = e.d / 2;
     const int items = e.rows_k * e.hkv + e.rows_q * e.hq;
-    const int per_block = kExtThreads / half;
+    const int per_block = kExtThreads / (half / 8);
     stage_begin(l, kStageExtendGather);
     if (l.dtype == TS_DTYPE_BF16)
         extend_gather_kernel<__nv_bfloat16><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, tc ? 1 : 0);
@@ -407,7 +511,7 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
             if (err != cudaSuccess) return err;
             configured = true;
         }
-        extend_attend_tc_kernel<<<dim3(e.rows_q / kTile, e.hq), 128, sizeof(ExtSmem), l.stream>>>(e);
+        extend_attend_tc_kernel<<<dim3(e.rows_q / kQTile, e.hq), 128, sizeof(ExtSmem), l.stream>>>(e);
     } else {
         const int warps = e.chunk_len * e.hq;
         const int blocks = (warps + kExtThreads / 32 - 1) / (kExtThreads / 32);

@@ -1113,7 +1113,7 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
     }
 }
 
-constexpr int kCandSmem = 8192;       // threshold-bin members staged in shared memory (64 KB)
+constexpr int kCandSmem = kFusedDynSmem / 8;   // threshold-bin members staged in shared memory (the idle ring)
 
 __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn) {
     const int tid = threadIdx.x;
