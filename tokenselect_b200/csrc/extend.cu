@@ -146,23 +146,40 @@ __device__ __forceinline__ void load8(const T* src, float (&x)[8]) {
         }
     }
 }
+// Layouts of the compact arrays (per head: `rows` rows of d elements):
+//   kLayoutPlain   row-major;
+//   kLayoutXor16   row-major, the sixteen 16-byte pieces of a 256-byte row XOR-ed with row & 7 (mma.sync kernel);
+//   kLayoutImage   tiles of `tile_rows` rows stored as the shared-memory image tcgen05 reads: per tile the
+//                  two 64-element halves one after the other, each [row][128 B] with the eight 16-byte
+//                  pieces of a row XOR-ed with row & 7 (the 128-byte swizzle of the K-major / MN-major
+//                  canonical layouts), so that one linear bulk copy brings a whole operand tile.
+enum { kLayoutPlain = 0, kLayoutXor16 = 1, kLayoutImage = 2 };
+
 template <typename T>
-__device__ __forceinline__ void store8(T* row_base, int row, int e0, const float (&x)[8], bool swizzle) {
+__device__ __forceinline__ void store8(T* head_base, int d, int row, int e0, const float (&x)[8], int layout, int tile_rows) {
     if constexpr (sizeof(T) == 2) {
         T raw[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) raw[u] = from_f32<T>(x[u]);
-        const int piece = e0 >> 3;
-        *reinterpret_cast<uint4*>(row_base + ((swizzle ? (piece ^ (row & 7)) : piece) << 3)) = *reinterpret_cast<uint4*>(raw);
+        size_t off;                                                        // in elements
+        if (layout == kLayoutImage) {
+            const int tile = row / tile_rows, r = row - tile * tile_rows;
+            const int hlf = e0 >> 6, piece = (e0 & 63) >> 3;
+            off = (size_t)tile * tile_rows * 128 + (size_t)hlf * tile_rows * 64 + (size_t)r * 64 + ((piece ^ (r & 7)) << 3);
+        } else {
+            const int piece = e0 >> 3;
+            off = (size_t)row * d + ((layout == kLayoutXor16 ? (piece ^ (row & 7)) : piece) << 3);
+        }
+        *reinterpret_cast<uint4*>(head_base + off) = *reinterpret_cast<uint4*>(raw);
     } else {
 #pragma unroll
         for (int u = 0; u < 8; u += 4)
-            *reinterpret_cast<float4*>(row_base + e0 + u) = make_float4(x[u], x[u + 1], x[u + 2], x[u + 3]);
+            *reinterpret_cast<float4*>(head_base + (size_t)row * d + e0 + u) = make_float4(x[u], x[u + 1], x[u + 2], x[u + 3]);
     }
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const ExtendParams e, const int swizzle) {
+__global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const ExtendParams e, const int layout) {
     if (*(volatile int*)e.err != 0) return;
     const int half = e.d / 2;
     const int tpi = half / 8;                                             // threads per (row, head) item
@@ -177,11 +194,11 @@ __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const Extend
     for (int u = 0; u < 8; ++u) z[u] = 0.f;
     if (item < k_items) {
         const int j = item / e.hkv, kv = item - j * e.hkv;
-        T* kc = reinterpret_cast<T*>(e.kc) + ((size_t)kv * e.rows_k + j) * e.d;
-        T* vc = reinterpret_cast<T*>(e.vc) + ((size_t)kv * e.rows_k + j) * e.d;
+        T* kc = reinterpret_cast<T*>(e.kc) + (size_t)kv * e.rows_k * e.d;
+        T* vc = reinterpret_cast<T*>(e.vc) + (size_t)kv * e.rows_k * e.d;
         if (j >= count) {
-            store8<T>(kc, j, i0, z, swizzle); store8<T>(kc, j, i0 + half, z, swizzle);
-            store8<T>(vc, j, i0, z, swizzle); store8<T>(vc, j, i0 + half, z, swizzle);
+            store8<T>(kc, e.d, j, i0, z, layout, 64); store8<T>(kc, e.d, j, i0 + half, z, layout, 64);
+            store8<T>(vc, e.d, j, i0, z, layout, 64); store8<T>(vc, e.d, j, i0 + half, z, layout, 64);
             return;
         }
         int slot = e.sel_slots[j];
@@ -201,16 +218,16 @@ __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const Extend
             r1[u] = x1[u] * c.x - x2[u] * c.y;
             r2[u] = x2[u] * c.x + x1[u] * c.y;
         }
-        store8<T>(kc, j, i0, r1, swizzle); store8<T>(kc, j, i0 + half, r2, swizzle);
-        store8<T>(vc, j, i0, v1, swizzle); store8<T>(vc, j, i0 + half, v2, swizzle);
+        store8<T>(kc, e.d, j, i0, r1, layout, 64); store8<T>(kc, e.d, j, i0 + half, r2, layout, 64);
+        store8<T>(vc, e.d, j, i0, v1, layout, 64); store8<T>(vc, e.d, j, i0 + half, v2, layout, 64);
         return;
     }
     const int qitem = item - k_items;
     if (qitem >= e.rows_q * e.hq) return;
     const int t = qitem / e.hq, h = qitem - t * e.hq;
-    T* qc = reinterpret_cast<T*>(e.qc) + ((size_t)h * e.rows_q + t) * e.d;
+    T* qc = reinterpret_cast<T*>(e.qc) + (size_t)h * e.rows_q * e.d;
     if (t >= lq) {
-        store8<T>(qc, t, i0, z, swizzle); store8<T>(qc, t, i0 + half, z, swizzle);
+        store8<T>(qc, e.d, t, i0, z, layout, 128); store8<T>(qc, e.d, t, i0 + half, z, layout, 128);
         return;
     }
     const int pos = max(count - lq + t, 0);                               // the chunk closes the list
@@ -224,7 +241,7 @@ __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const Extend
         r1[u] = x1[u] * c.x - x2[u] * c.y;
         r2[u] = x2[u] * c.x + x1[u] * c.y;
     }
-    store8<T>(qc, t, i0, r1, swizzle); store8<T>(qc, t, i0 + half, r2, swizzle);
+    store8<T>(qc, e.d, t, i0, r1, layout, 128); store8<T>(qc, e.d, t, i0 + half, r2, layout, 128);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -426,6 +443,290 @@ __global__ void __launch_bounds__(128, 1) extend_attend_tc_kernel(const ExtendPa
 }
 
 // ------------------------------------------------------------------------------------------------
+// 4a'. the same with the 5th-generation tensor cores: tcgen05.mma, accumulators in tensor memory
+// ------------------------------------------------------------------------------------------------
+// grid (rows_q / 128, hq), 512 threads, one CTA per SM.  M = 128 query rows per CTA; keys in blocks of 64.
+//   S[b&1] (128 x 64 fp32, TMEM columns 64*(b&1)..)  = Q (smem, K-major SW128) . K_b^T (smem, K-major SW128)
+//   O      (128 x 128 fp32, TMEM columns 128..255)  += P_b (smem, K-major SW128) . V_b (smem, MN-major SW128)
+// Four threads share TMEM lane r == query row r (a quarter of the columns each): they read S with
+// tcgen05.ld, keep the row's reference maximum and partial sums, write P = 2^(S - ref) as bf16 into the swizzled P tile.  O stays in
+// tensor memory across blocks; it is rescaled (tcgen05.ld / st) only when a row's maximum has grown by more
+// than 2^8 since the reference was taken, so P never exceeds 256.  Thread 0 issues the MMAs: Q.K^T of block
+// b+1 is issued before the softmax of block b starts, so the tensor pipe works under the softmax.
+// K/V tiles: four stages, one bulk copy each per tile (the gather kernel stores them as smem images).
+constexpr int kKvStages = 4;
+struct Tc5Smem {
+    unsigned char q[128 * 256];                 // 2 halves x [128 rows][128 B]
+    unsigned char k[kKvStages][kTile * 256];    // 2 halves x [64 keys][128 B]
+    unsigned char v[kKvStages][kTile * 256];
+    unsigned char p[128 * 128];                 // [128 rows][64 keys] bf16
+    float rowmax[4][128];                       // per column quarter: row maxima of a block, row sums at the end
+    uint64_t qbar, full[kKvStages], s_done[2], o_done;
+    uint32_t tmem_base;
+};
+
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    // start address, leading / stride byte offsets in 16-byte units; descriptor version 1; 128-byte swizzle
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// 512 threads: thread (quarter c = warp / 4, lane quarter w = warp % 4, lane l) owns query row 32w + l and the
+// columns [16c, 16c+16) of S, [32c, 32c+32) of O.  Four threads share a row; they exchange the row maximum
+// through shared memory and keep separate partial sums.
+constexpr int kTc5Threads = 512;
+__global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const ExtendParams e) {
+    extern __shared__ unsigned char tc5_dyn[];
+    // the swizzled operand tiles need 1024-byte alignment
+    Tc5Smem& sm = *reinterpret_cast<Tc5Smem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cq = warp >> 2, rq = warp & 3;                 // column quarter, row (lane) quarter
+    const int r_in = rq * 32 + lane;                         // row inside the 128-row tile
+    const int qt = blockIdx.x, h = blockIdx.y, kv = h / e.group;
+    const int lq = e.chunk_len;
+    if (*(volatile int*)e.err != 0 || qt * 128 >= lq) return;
+    const int count = min(*e.sel_count, e.n_sel);
+    const int base_vis = count - lq;                         // query row r sees list entries j <= base_vis + r
+    const int kmax = min(count - 1, base_vis + qt * 128 + 127);
+    const int nblk = kmax / kTile + 1;
+    bool dead = false;
+
+    const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
+    const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(e.kc) + (size_t)kv * e.rows_k * 256;
+    const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(e.vc) + (size_t)kv * e.rows_k * 256;
+    constexpr uint32_t kTileBytes = kTile * 256;             // one K or V tile image
+
+    if (tid == 0) {
+        mbar_init(smem_u32(&sm.qbar), 1);
+        for (int s = 0; s < kKvStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
+        mbar_init(smem_u32(&sm.s_done[0]), 1);
+        mbar_init(smem_u32(&sm.s_done[1]), 1);
+        mbar_init(smem_u32(&sm.o_done), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *(volatile uint32_t*)&sm.tmem_base;
+    const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
+    const uint32_t t_s[2] = {tmem + lane_base + 16u * cq, tmem + lane_base + 64u + 16u * cq};
+    const uint32_t t_o = tmem + lane_base + 128u + 32u * cq;
+
+    auto load_tile = [&](int b) {                            // thread 0
+        const int st = b % kKvStages;
+        mbar_expect_tx(smem_u32(&sm.full[st]), 2 * kTileBytes);
+        bulk_g2s(smem_u32(sm.k[st]), ksrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
+        bulk_g2s(smem_u32(sm.v[st]), vsrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
+    };
+    // instruction descriptors: fp32 accumulate, bf16 A and B, M = 128; N = 64 with K-major B, N = 128 with MN-major B
+    constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+    constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+    auto issue_qk = [&](int b) {                             // thread 0: S[b&1] = Q . K_b^T
+        const int st = b % kKvStages;
+        mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42);
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sm.q), ka = smem_u32(sm.k[st]);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t off_q = (ks >> 2) * (128u * 128u) + (ks & 3) * 32u;
+            const uint32_t off_k = (ks >> 2) * (kTile * 128u) + (ks & 3) * 32u;
+            umma_bf16(tmem + 64u * (b & 1), umma_desc_sw128(qa + off_q, 16, 1024), umma_desc_sw128(ka + off_k, 16, 1024),
+                      kIdescQK, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sm.s_done[b & 1]));
+    };
+
+    if (tid == 0) {
+        mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
+        bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
+        for (int b = 0; b < kKvStages && b < nblk; ++b) load_tile(b);
+        mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40);
+        issue_qk(0);
+    }
+
+    const int row = qt * 128 + r_in;
+    const int lim = base_vis + row;
+    const float cap = e.logit_cap;
+    const float scale2 = e.sm_scale * kLog2eX;
+    float m_ref = 0.f, l_run = 0.f;
+    const uint32_t p_row = smem_u32(sm.p) + r_in * 128;
+
+    for (int blk = 0; blk < nblk; ++blk) {
+        if (tid == 0 && blk + 1 < nblk) issue_qk(blk + 1);
+        mbar_wait(smem_u32(&sm.s_done[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 43);
+        tc_fence_after();
+        __syncwarp();                                        // thread 0 rejoins its warp after issuing MMAs
+        float x[16];
+        {
+            uint32_t r0[16];
+            tmem_ld16(t_s[blk & 1], r0);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) x[c] = __uint_as_float(r0[c]);
+        }
+        float mx = -INFINITY;
+        const int key0 = blk * kTile + 16 * cq;
+        if (cap > 0.f) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
+        } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) x[c] *= scale2;
+        }
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            if (key0 + c > lim) x[c] = -INFINITY;
+            mx = fmaxf(mx, x[c]);
+        }
+        sm.rowmax[cq][r_in] = mx;
+        __syncthreads();
+        mx = fmaxf(fmaxf(sm.rowmax[0][r_in], sm.rowmax[1][r_in]), fmaxf(sm.rowmax[2][r_in], sm.rowmax[3][r_in]));
+        if (blk > 0) {
+            // P.V of the previous block is complete: O may be read, the P tile and that block's stage are free
+            mbar_wait(smem_u32(&sm.o_done), (uint32_t)((blk - 1) & 1), e.err, dead, 44);
+            tc_fence_after();
+            if (tid == 0 && blk - 1 + kKvStages < nblk) {
+                asm volatile("fence.proxy.async;" ::: "memory");
+                load_tile(blk - 1 + kKvStages);
+            }
+            __syncwarp();
+            const bool grow = mx > m_ref + 8.f;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
+                uint32_t r[32];
+                tmem_ld32(t_o, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                tmem_st32(t_o, r);
+                tmem_wait_st();
+                l_run *= corr;
+                if (grow) m_ref = mx;
+            }
+        } else {
+            m_ref = mx == -INFINITY ? 0.f : mx;
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int c8 = 0; c8 < 2; ++c8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float p0 = ex2_fast(x[c8 * 8 + 2 * u] - m_ref), p1 = ex2_fast(x[c8 * 8 + 2 * u + 1] - m_ref);
+                sum += p0 + p1;
+                w[u] = pack_bf16(p0, p1);
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((2 * cq + c8) ^ (r_in & 7)) << 4)), "r"(w[0]),
+                         "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+        }
+        l_run += sum;
+        asm volatile("fence.proxy.async;" ::: "memory");       // P (generic stores) -> visible to the tensor core's reads
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const int st = blk % kKvStages;
+            const uint32_t pa = smem_u32(sm.p), va = smem_u32(sm.v[st]);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)                   // 16 keys per step
+                umma_bf16(tmem + 128u, umma_desc_sw128(pa + ks * 32u, 16, 1024),
+                          umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024), kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(smem_u32(&sm.o_done));
+        }
+    }
+    // row sums: the four partial sums of a row share the reference maximum
+    sm.rowmax[cq][r_in] = l_run;
+    mbar_wait(smem_u32(&sm.o_done), (uint32_t)((nblk - 1) & 1), e.err, dead, 45);
+    tc_fence_after();
+    __syncthreads();
+    const float l_tot = (sm.rowmax[0][r_in] + sm.rowmax[1][r_in]) + (sm.rowmax[2][r_in] + sm.rowmax[3][r_in]);
+    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + 32 * cq;
+    {
+        uint32_t r[32];
+        tmem_ld32(t_o, r);
+        tmem_wait_ld();
+        if (row < lq) {
+#pragma unroll
+            for (int c8 = 0; c8 < 4; ++c8) {
+                uint4 w;
+                w.x = pack_bf16(__uint_as_float(r[c8 * 8 + 0]) * inv, __uint_as_float(r[c8 * 8 + 1]) * inv);
+                w.y = pack_bf16(__uint_as_float(r[c8 * 8 + 2]) * inv, __uint_as_float(r[c8 * 8 + 3]) * inv);
+                w.z = pack_bf16(__uint_as_float(r[c8 * 8 + 4]) * inv, __uint_as_float(r[c8 * 8 + 5]) * inv);
+                w.w = pack_bf16(__uint_as_float(r[c8 * 8 + 6]) * inv, __uint_as_float(r[c8 * 8 + 7]) * inv);
+                *reinterpret_cast<uint4*>(out + c8 * 8) = w;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // 4b. the same on CUDA cores in fp32 (fp32 check mode, head_dim 64): one warp per (query, head)
 // ------------------------------------------------------------------------------------------------
 template <typename T, int E>
@@ -495,16 +796,27 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     const int half = e.d / 2;
     const int items = e.rows_k * e.hkv + e.rows_q * e.hq;
     const int per_block = kExtThreads / (half / 8);
+    const bool tc5 = tc && !(l.flags & TS_CFG_EXTEND_MMA_SYNC);
+    const int layout = tc5 ? kLayoutImage : tc ? kLayoutXor16 : kLayoutPlain;
     stage_begin(l, kStageExtendGather);
     if (l.dtype == TS_DTYPE_BF16)
-        extend_gather_kernel<__nv_bfloat16><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, tc ? 1 : 0);
+        extend_gather_kernel<__nv_bfloat16><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, layout);
     else
-        extend_gather_kernel<float><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, 0);
+        extend_gather_kernel<float><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, layout);
     stage_end(l);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     stage_begin(l, kStageExtendAttend);
-    if (tc) {
+    if (tc5) {
+        static bool configured5 = false;
+        const size_t smem5 = sizeof(Tc5Smem) + 1024;
+        if (!configured5) {
+            err = cudaFuncSetAttribute(extend_attend_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem5);
+            if (err != cudaSuccess) return err;
+            configured5 = true;
+        }
+        extend_attend_tc5_kernel<<<dim3(e.rows_q / 128, e.hq), kTc5Threads, smem5, l.stream>>>(e);
+    } else if (tc) {
         static bool configured = false;
         if (!configured) {
             err = cudaFuncSetAttribute(extend_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ExtSmem));
