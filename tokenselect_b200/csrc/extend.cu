@@ -445,23 +445,23 @@ __global__ void __launch_bounds__(128, 1) extend_attend_tc_kernel(const ExtendPa
 // ------------------------------------------------------------------------------------------------
 // 4a'. the same with the 5th-generation tensor cores: tcgen05.mma, accumulators in tensor memory
 // ------------------------------------------------------------------------------------------------
-// grid (rows_q / 128, hq), 512 threads, one CTA per SM.  M = 128 query rows per CTA; keys in blocks of 64.
+// grid (rows_q / 128, hq), 544 threads, one CTA per SM.  M = 128 query rows per CTA; keys in blocks of 64.
 //   S[b&1] (128 x 64 fp32, TMEM columns 64*(b&1)..)  = Q (smem, K-major SW128) . K_b^T (smem, K-major SW128)
-//   O      (128 x 128 fp32, TMEM columns 128..255)  += P_b (smem, K-major SW128) . V_b (smem, MN-major SW128)
+//   O      (128 x 128 fp32, TMEM columns 128..255)  += P_b (TMEM columns 256..287, packed bf16) . V_b (smem, MN-major SW128)
 // Four threads share TMEM lane r == query row r (a quarter of the columns each): they read S with
-// tcgen05.ld, keep the row's reference maximum and partial sums, write P = 2^(S - ref) as bf16 into the swizzled P tile.  O stays in
-// tensor memory across blocks; it is rescaled (tcgen05.ld / st) only when a row's maximum has grown by more
-// than 2^8 since the reference was taken, so P never exceeds 256.  Thread 0 issues the MMAs: Q.K^T of block
-// b+1 is issued before the softmax of block b starts, so the tensor pipe works under the softmax.
+// tcgen05.ld, keep the row's reference maximum and partial sums and write P = 2^(S - ref) back to tensor
+// memory as bf16.  O stays in tensor memory across blocks; it is rescaled (tcgen05.ld / st) only when a
+// row's maximum has grown by more than 2^8 since the reference was taken, so P never exceeds 256.  One
+// thread of a separate warp issues the MMAs: Q.K^T of block b+1 is issued before the softmax of block b
+// starts, so the tensor pipe works under the softmax.
 // K/V tiles: four stages, one bulk copy each per tile (the gather kernel stores them as smem images).
 constexpr int kKvStages = 4;
 struct Tc5Smem {
     unsigned char q[128 * 256];                 // 2 halves x [128 rows][128 B]
     unsigned char k[kKvStages][kTile * 256];    // 2 halves x [64 keys][128 B]
     unsigned char v[kKvStages][kTile * 256];
-    unsigned char p[128 * 128];                 // [128 rows][64 keys] bf16
-    float rowmax[4][128];                       // per column quarter: row maxima of a block, row sums at the end
-    uint64_t qbar, full[kKvStages], s_done[2], o_done;
+    float rowmax[2][4][128];                    // [block parity][column quarter][row]: row maxima; row sums at the end
+    uint64_t qbar, full[kKvStages], s_done[2], o_done, p_ready;
     uint32_t tmem_base;
 };
 
@@ -525,17 +525,38 @@ __device__ __forceinline__ float ex2_fast(float x) {
     return y;
 }
 
-// 512 threads: thread (quarter c = warp / 4, lane quarter w = warp % 4, lane l) owns query row 32w + l and the
-// columns [16c, 16c+16) of S, [32c, 32c+32) of O.  Four threads share a row; they exchange the row maximum
-// through shared memory and keep separate partial sums.
-constexpr int kTc5Threads = 512;
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+// A operand in tensor memory (rows = lanes, two bf16 per 32-bit column), B through a shared-memory descriptor
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// 16 softmax warps + 1 issuer warp.  Softmax thread (column quarter c = warp / 4, lane quarter w = warp % 4,
+// lane l) owns query row 32w + l and the columns [16c, 16c+16) of S, [32c, 32c+32) of O; the four threads of a
+// row exchange the row maximum through shared memory (a 128-thread named barrier per lane quarter) and
+// keep separate partial sums.  P goes back to tensor memory as packed bf16 and is the A operand of P.V.
+// Lane 0 of the issuer warp requests tiles and issues every MMA.
+constexpr int kTc5Softmax = 512;
+constexpr int kTc5Threads = kTc5Softmax + 32;
+constexpr uint32_t kTmemCols = 512, kTmemO = 128, kTmemP = 256;
 __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const ExtendParams e) {
     extern __shared__ unsigned char tc5_dyn[];
     // the swizzled operand tiles need 1024-byte alignment
     Tc5Smem& sm = *reinterpret_cast<Tc5Smem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cq = warp >> 2, rq = warp & 3;                 // column quarter, row (lane) quarter
-    const int r_in = rq * 32 + lane;                         // row inside the 128-row tile
     const int qt = blockIdx.x, h = blockIdx.y, kv = h / e.group;
     const int lq = e.chunk_len;
     if (*(volatile int*)e.err != 0 || qt * 128 >= lq) return;
@@ -545,21 +566,17 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
     const int nblk = kmax / kTile + 1;
     bool dead = false;
 
-    const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
-    const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(e.kc) + (size_t)kv * e.rows_k * 256;
-    const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(e.vc) + (size_t)kv * e.rows_k * 256;
-    constexpr uint32_t kTileBytes = kTile * 256;             // one K or V tile image
-
     if (tid == 0) {
         mbar_init(smem_u32(&sm.qbar), 1);
         for (int s = 0; s < kKvStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
         mbar_init(smem_u32(&sm.s_done[0]), 1);
         mbar_init(smem_u32(&sm.s_done[1]), 1);
         mbar_init(smem_u32(&sm.o_done), 1);
+        mbar_init(smem_u32(&sm.p_ready), kTc5Softmax / 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(256u)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -567,142 +584,145 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *(volatile uint32_t*)&sm.tmem_base;
-    const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
-    const uint32_t t_s[2] = {tmem + lane_base + 16u * cq, tmem + lane_base + 64u + 16u * cq};
-    const uint32_t t_o = tmem + lane_base + 128u + 32u * cq;
 
-    auto load_tile = [&](int b) {                            // thread 0
-        const int st = b % kKvStages;
-        mbar_expect_tx(smem_u32(&sm.full[st]), 2 * kTileBytes);
-        bulk_g2s(smem_u32(sm.k[st]), ksrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
-        bulk_g2s(smem_u32(sm.v[st]), vsrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
-    };
-    // instruction descriptors: fp32 accumulate, bf16 A and B, M = 128; N = 64 with K-major B, N = 128 with MN-major B
-    constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
-    constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-    auto issue_qk = [&](int b) {                             // thread 0: S[b&1] = Q . K_b^T
-        const int st = b % kKvStages;
-        mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42);
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sm.q), ka = smem_u32(sm.k[st]);
+    if (warp == kTc5Softmax / 32) {
+        // ---------------- issuer ----------------
+        if (lane == 0) {
+            const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
+            const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(e.kc) + (size_t)kv * e.rows_k * 256;
+            const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(e.vc) + (size_t)kv * e.rows_k * 256;
+            constexpr uint32_t kTileBytes = kTile * 256;     // one K or V tile image
+            auto load_tile = [&](int b) {
+                const int st = b % kKvStages;
+                mbar_expect_tx(smem_u32(&sm.full[st]), 2 * kTileBytes);
+                bulk_g2s(smem_u32(sm.k[st]), ksrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
+                bulk_g2s(smem_u32(sm.v[st]), vsrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
+            };
+            // instruction descriptors: fp32 accumulate, bf16 A and B, M = 128; N = 64 with K-major B, N = 128 with MN-major B
+            constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+            constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            auto issue_qk = [&](int b) {                     // S[b&1] = Q . K_b^T
+                const int st = b % kKvStages;
+                mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42);
+                tc_fence_after();
+                const uint32_t qa = smem_u32(sm.q), ka = smem_u32(sm.k[st]);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t off_q = (ks >> 2) * (128u * 128u) + (ks & 3) * 32u;
-            const uint32_t off_k = (ks >> 2) * (kTile * 128u) + (ks & 3) * 32u;
-            umma_bf16(tmem + 64u * (b & 1), umma_desc_sw128(qa + off_q, 16, 1024), umma_desc_sw128(ka + off_k, 16, 1024),
-                      kIdescQK, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&sm.s_done[b & 1]));
-    };
-
-    if (tid == 0) {
-        mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
-        bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
-        for (int b = 0; b < kKvStages && b < nblk; ++b) load_tile(b);
-        mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40);
-        issue_qk(0);
-    }
-
-    const int row = qt * 128 + r_in;
-    const int lim = base_vis + row;
-    const float cap = e.logit_cap;
-    const float scale2 = e.sm_scale * kLog2eX;
-    float m_ref = 0.f, l_run = 0.f;
-    const uint32_t p_row = smem_u32(sm.p) + r_in * 128;
-
-    for (int blk = 0; blk < nblk; ++blk) {
-        if (tid == 0 && blk + 1 < nblk) issue_qk(blk + 1);
-        mbar_wait(smem_u32(&sm.s_done[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 43);
-        tc_fence_after();
-        __syncwarp();                                        // thread 0 rejoins its warp after issuing MMAs
-        float x[16];
-        {
-            uint32_t r0[16];
-            tmem_ld16(t_s[blk & 1], r0);
-            tmem_wait_ld();
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off_q = (ks >> 2) * (128u * 128u) + (ks & 3) * 32u;
+                    const uint32_t off_k = (ks >> 2) * (kTile * 128u) + (ks & 3) * 32u;
+                    umma_bf16(tmem + 64u * (b & 1), umma_desc_sw128(qa + off_q, 16, 1024),
+                              umma_desc_sw128(ka + off_k, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&sm.s_done[b & 1]));
+            };
+            mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
+            bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
+            for (int b = 0; b < kKvStages && b < nblk; ++b) load_tile(b);
+            mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40);
+            issue_qk(0);
+            for (int blk = 0; blk < nblk; ++blk) {
+                if (blk + 1 < nblk) issue_qk(blk + 1);
+                if (blk > 0 && blk - 1 + kKvStages < nblk) {
+                    // P.V of the previous block is complete: its stage can take the tile four blocks ahead
+                    mbar_wait(smem_u32(&sm.o_done), (uint32_t)((blk - 1) & 1), e.err, dead, 46);
+                    load_tile(blk - 1 + kKvStages);
+                }
+                mbar_wait(smem_u32(&sm.p_ready), (uint32_t)(blk & 1), e.err, dead, 47);
+                tc_fence_after();
+                const uint32_t va = smem_u32(sm.v[blk % kKvStages]);
 #pragma unroll
-            for (int c = 0; c < 16; ++c) x[c] = __uint_as_float(r0[c]);
-        }
-        float mx = -INFINITY;
-        const int key0 = blk * kTile + 16 * cq;
-        if (cap > 0.f) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
-        } else {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) x[c] *= scale2;
-        }
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-            if (key0 + c > lim) x[c] = -INFINITY;
-            mx = fmaxf(mx, x[c]);
-        }
-        sm.rowmax[cq][r_in] = mx;
-        __syncthreads();
-        mx = fmaxf(fmaxf(sm.rowmax[0][r_in], sm.rowmax[1][r_in]), fmaxf(sm.rowmax[2][r_in], sm.rowmax[3][r_in]));
-        if (blk > 0) {
-            // P.V of the previous block is complete: O may be read, the P tile and that block's stage are free
-            mbar_wait(smem_u32(&sm.o_done), (uint32_t)((blk - 1) & 1), e.err, dead, 44);
-            tc_fence_after();
-            if (tid == 0 && blk - 1 + kKvStages < nblk) {
-                asm volatile("fence.proxy.async;" ::: "memory");
-                load_tile(blk - 1 + kKvStages);
+                for (int ks = 0; ks < 4; ++ks)               // 16 keys per step: 8 packed columns of P
+                    umma_bf16_ts(tmem + kTmemO, tmem + kTmemP + 8u * ks, umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024),
+                                 kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&sm.o_done));
             }
-            __syncwarp();
-            const bool grow = mx > m_ref + 8.f;
-            if (__any_sync(0xffffffffu, grow)) {
-                const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
-                uint32_t r[32];
-                tmem_ld32(t_o, r);
+        }
+    } else {
+        // ---------------- softmax ----------------
+        const int cq = warp >> 2, rq = warp & 3;             // column quarter, row (lane) quarter
+        const int r_in = rq * 32 + lane;                     // row inside the 128-row tile
+        const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
+        const uint32_t t_s[2] = {tmem + lane_base + 16u * cq, tmem + lane_base + 64u + 16u * cq};
+        const uint32_t t_o = tmem + lane_base + kTmemO + 32u * cq;
+        const uint32_t t_p = tmem + lane_base + kTmemP + 8u * cq;
+        const int row = qt * 128 + r_in;
+        const int lim = base_vis + row;
+        const float cap = e.logit_cap;
+        const float scale2 = e.sm_scale * kLog2eX;
+        float m_ref = 0.f, l_run = 0.f;
+
+        for (int blk = 0; blk < nblk; ++blk) {
+            mbar_wait(smem_u32(&sm.s_done[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 43);
+            tc_fence_after();
+            float x[16];
+            {
+                uint32_t r0[16];
+                tmem_ld16(t_s[blk & 1], r0);
                 tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-                tmem_st32(t_o, r);
-                tmem_wait_st();
-                l_run *= corr;
-                if (grow) m_ref = mx;
+                for (int c = 0; c < 16; ++c) x[c] = __uint_as_float(r0[c]);
             }
-        } else {
-            m_ref = mx == -INFINITY ? 0.f : mx;
-        }
-        float sum = 0.f;
+            float mx = -INFINITY;
+            const int key0 = blk * kTile + 16 * cq;
+            if (cap > 0.f) {
 #pragma unroll
-        for (int c8 = 0; c8 < 2; ++c8) {
-            uint32_t w[4];
+                for (int c = 0; c < 16; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
+            } else {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float p0 = ex2_fast(x[c8 * 8 + 2 * u] - m_ref), p1 = ex2_fast(x[c8 * 8 + 2 * u + 1] - m_ref);
+                for (int c = 0; c < 16; ++c) x[c] *= scale2;
+            }
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                if (key0 + c > lim) x[c] = -INFINITY;
+                mx = fmaxf(mx, x[c]);
+            }
+            float* rm = &sm.rowmax[blk & 1][0][r_in];
+            rm[cq * 128] = mx;
+            named_bar_sync(1 + rq, 128);                     // the four warps that share these rows
+            mx = fmaxf(fmaxf(rm[0], rm[128]), fmaxf(rm[256], rm[384]));
+            if (blk > 0) {
+                // P.V of the previous block is complete: O may be rescaled, P may be overwritten
+                mbar_wait(smem_u32(&sm.o_done), (uint32_t)((blk - 1) & 1), e.err, dead, 44);
+                tc_fence_after();
+                const bool grow = mx > m_ref + 8.f;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
+                    uint32_t r[32];
+                    tmem_ld32(t_o, r);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                    tmem_st32(t_o, r);
+                    l_run *= corr;
+                    if (grow) m_ref = mx;
+                }
+            } else {
+                m_ref = mx == -INFINITY ? 0.f : mx;
+            }
+            float sum = 0.f;
+            uint32_t w[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float p0 = ex2_fast(x[2 * u] - m_ref), p1 = ex2_fast(x[2 * u + 1] - m_ref);
                 sum += p0 + p1;
                 w[u] = pack_bf16(p0, p1);
             }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + (((2 * cq + c8) ^ (r_in & 7)) << 4)), "r"(w[0]),
-                         "r"(w[1]), "r"(w[2]), "r"(w[3])
-                         : "memory");
+            tmem_st8(t_p, w);
+            tmem_wait_st();
+            l_run += sum;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready));
         }
-        l_run += sum;
-        asm volatile("fence.proxy.async;" ::: "memory");       // P (generic stores) -> visible to the tensor core's reads
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-            const int st = blk % kKvStages;
-            const uint32_t pa = smem_u32(sm.p), va = smem_u32(sm.v[st]);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks)                   // 16 keys per step
-                umma_bf16(tmem + 128u, umma_desc_sw128(pa + ks * 32u, 16, 1024),
-                          umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024), kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
-            umma_commit(smem_u32(&sm.o_done));
-        }
-    }
-    // row sums: the four partial sums of a row share the reference maximum
-    sm.rowmax[cq][r_in] = l_run;
-    mbar_wait(smem_u32(&sm.o_done), (uint32_t)((nblk - 1) & 1), e.err, dead, 45);
-    tc_fence_after();
-    __syncthreads();
-    const float l_tot = (sm.rowmax[0][r_in] + sm.rowmax[1][r_in]) + (sm.rowmax[2][r_in] + sm.rowmax[3][r_in]);
-    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + 32 * cq;
-    {
+        // row sums: the four partial sums of a row share the reference maximum
+        float* rs = &sm.rowmax[nblk & 1][0][r_in];
+        rs[cq * 128] = l_run;
+        named_bar_sync(1 + rq, 128);
+        const float l_tot = (rs[0] + rs[128]) + (rs[256] + rs[384]);
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+        mbar_wait(smem_u32(&sm.o_done), (uint32_t)((nblk - 1) & 1), e.err, dead, 45);
+        tc_fence_after();
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + 32 * cq;
         uint32_t r[32];
         tmem_ld32(t_o, r);
         tmem_wait_ld();
@@ -722,7 +742,7 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
     }
 }
 
