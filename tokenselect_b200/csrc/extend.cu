@@ -648,7 +648,7 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
         const int row = qt * 128 + r_in;
         const int lim = base_vis + row;
         const float cap = e.logit_cap;
-        const float scale2 = e.sm_scale * kLog2eX;
+        const float mul = cap > 0.f ? 1.f : e.sm_scale * kLog2eX;     // x * mul is the logit in base-2 units
         float m_ref = 0.f, l_run = 0.f;
 
         for (int blk = 0; blk < nblk; ++blk) {
@@ -662,20 +662,21 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
 #pragma unroll
                 for (int c = 0; c < 16; ++c) x[c] = __uint_as_float(r0[c]);
             }
+            // x keeps S in raw units unless the soft cap is on; the scale goes into the exponent's FMA
             float mx = -INFINITY;
             const int key0 = blk * kTile + 16 * cq;
             if (cap > 0.f) {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
-            } else {
+            }
+            if (blk * kTile + kTile - 1 > base_vis + qt * 128) {      // only blocks that reach the diagonal are masked
 #pragma unroll
-                for (int c = 0; c < 16; ++c) x[c] *= scale2;
+                for (int c = 0; c < 16; ++c)
+                    if (key0 + c > lim) x[c] = -INFINITY;
             }
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                if (key0 + c > lim) x[c] = -INFINITY;
-                mx = fmaxf(mx, x[c]);
-            }
+            for (int c = 0; c < 16; ++c) mx = fmaxf(mx, x[c]);
+            mx *= mul;                                               // base-2 units (mul > 0)
             float* rm = &sm.rowmax[blk & 1][0][r_in];
             rm[cq * 128] = mx;
             named_bar_sync(1 + rq, 128);                     // the four warps that share these rows
@@ -703,7 +704,7 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
             uint32_t w[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
-                const float p0 = ex2_fast(x[2 * u] - m_ref), p1 = ex2_fast(x[2 * u + 1] - m_ref);
+                const float p0 = ex2_fast(fmaf(x[2 * u], mul, -m_ref)), p1 = ex2_fast(fmaf(x[2 * u + 1], mul, -m_ref));
                 sum += p0 + p1;
                 w[u] = pack_bf16(p0, p1);
             }
