@@ -147,7 +147,17 @@ def test_cuda_path_against_reference_golden(case):
     eng = gu.make_engine(case["hq"], case["hkv"], case["head_dim"], case["n_init"], case["n_local"], case["top_k"],
                          case["rope_base"], F32, max_ctx=case["n_tokens"] + 8, kernel_size=case["kernel_size"])
     q, kp, vp, rtt, ridx, lens = gu.case_tensors(c)
-    _, res = gu.run_gpu(eng, 0, q, kp, vp, rtt, ridx, lens)
+    if "chunk" in case:            # a prefill chunk: selection with the chunk's fingerprint (ts_extend_chunk)
+        qc = synth.make_chunk_queries(case["seed"], c, case["chunk"], case["hq"], case["head_dim"])
+        dev = eng.device
+        dbg = eng.new_debug_buffers(1)
+        eng.extend_chunk(0, qc.to(dev), None, None, None, kp.to(dev), vp.to(dev), rtt.to(dev), c.req_pool_idx,
+                         case["n_tokens"], debug=dbg)
+        torch.cuda.synchronize()
+        eng.raise_on_device_error()
+        res = {k_: v.cpu() for k_, v in dbg.items()}
+    else:
+        _, res = gu.run_gpu(eng, 0, q, kp, vp, rtt, ridx, lens)
     if case["slots"] is None:
         assert int(res["flags"][0]) == orc.FLAG_DENSE and int(res["count"][0]) == case["n_tokens"]
         return
