@@ -63,6 +63,9 @@ def parse_args():
                     help="diagnostic: run ONE rank's share of an N-way KV-head split on a single GPU, no exchange")
     ap.add_argument("--phase-times", action="store_true",
                     help="print the selection kernel's phase split (CTA 0 timestamps of the last launch) to stderr")
+    ap.add_argument("--prefill", action="store_true",
+                    help="secondary measurement: chunked prefill of one request of --ctx tokens (512-token chunks) "
+                         "through ts_extend_chunk instead of the decode step")
     ap.add_argument("--seed", type=int, default=2024)
     return ap.parse_args()
 
@@ -207,8 +210,99 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def tensor_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["bf16_tflops_sustained"]), "measured (sustained)"
+        except Exception:
+            pass
+    return 1400.0, "fallback"
+
+
+def run_prefill(args):
+    """Chunked prefill of one request (Llama-3-8B attention shape) through ``ts_extend_chunk``: per
+    512-token chunk and layer the chunk's K/V rows are appended, the chunk's fingerprint selects, and the
+    chunk's queries attend causally over the selected list.  One step = the whole prefill of ``--ctx``
+    tokens over ``--layers`` layers; tok/s = ctx / seconds.  Not the headline metric."""
+    from tokenselect_b200 import TokenSelectConfig, TokenSelectEngine
+    from tokenselect_b200 import build as _build
+    _build.build_library()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    ctx, layers, chunk = args.ctx, args.layers, 512
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    rows = ctx + 64
+    rtt = torch.zeros(2, ctx + 8, dtype=torch.int32, device=dev)
+    rtt[1, :ctx] = torch.randperm(rows, generator=g, device=dev)[:ctx].to(torch.int32)
+    k_pools = [torch.zeros(rows, HKV, D, dtype=torch.bfloat16, device=dev) for _ in range(layers)]
+    v_pools = [torch.zeros(rows, HKV, D, dtype=torch.bfloat16, device=dev) for _ in range(layers)]
+    # the tokens' K/V (shared by the layers: what matters is the traffic, not the values) and eight
+    # chunk-query buffers with a common direction, so that the averaged query keeps a direction
+    k_tok = torch.randn(ctx, HKV * D, generator=g, device=dev).to(torch.bfloat16)
+    v_tok = torch.randn(ctx, HKV * D, generator=g, device=dev).to(torch.bfloat16)
+    base_q = torch.randn(1, HQ * D, generator=g, device=dev)
+    qs = [(base_q + 0.5 * torch.randn(chunk, HQ * D, generator=g, device=dev)).to(torch.bfloat16) for _ in range(8)]
+    out = torch.empty(chunk, HQ * D, dtype=torch.bfloat16, device=dev)
+    cfg = TokenSelectConfig(rope_base=ROPE_BASE, max_n_tokens=ctx + 8, top_k=TOP_K, n_init=N_INIT, n_local=N_LOCAL,
+                            n_layers=layers, num_q_heads=HQ, num_kv_heads=HKV, head_dim=D, max_reqs=2, max_batch=1,
+                            max_total_tokens=ctx + 8, prefill_chunk=chunk)
+    eng = TokenSelectEngine(cfg, device=dev)
+    n_chunks = (ctx + chunk - 1) // chunk
+
+    def prefill(first_chunk, last_chunk):
+        for c in range(first_chunk, last_chunk):
+            s0, s1 = c * chunk, min((c + 1) * chunk, ctx)
+            loc = rtt[1, s0:s1]
+            for li in range(layers):
+                eng.extend_chunk(li, qs[c % 8][: s1 - s0], k_tok[s0:s1], v_tok[s0:s1], loc, k_pools[li], v_pools[li],
+                                 rtt, 1, s1, out=out[: s1 - s0])
+
+    prefill(0, min(8, n_chunks))                     # warm-up
+    torch.cuda.synchronize()
+    eng.raise_on_device_error()
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = eng.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    prefill(0, n_chunks)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    launches = eng.launch_count - launches0
+    eng.raise_on_device_error()
+    # per-kernel split and the attention kernel's rate on the last 8 chunks (full-length list)
+    eng.timing_begin(8 * layers * 4 + 16)
+    prefill(max(0, n_chunks - 8), n_chunks)
+    stages = {k: v for k, v in eng.timing_end().items() if v[1]}
+    n_sel = N_INIT + TOP_K + N_LOCAL
+    count = min(ctx, n_sel)
+    flops = 4.0 * HQ * D * sum(count - chunk + t + 1 for t in range(chunk))
+    att_us = 1e3 * stages["extend_attend"][0] / stages["extend_attend"][1]
+    peak, src = tensor_peak()
+    line = {
+        "metric": "prefill tok/s at 128K ctx, hot path per 512-token chunk (KV append + selection + sparse causal attention)",
+        "value": ctx / (ms * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": 1, "warmup": 1, "ms_per_step": ms,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"llama3-8b-shape chunked prefill, one request, ctx={ctx}, {layers} layers, chunk=512, "
+                               f"top_k={TOP_K}, n_init={N_INIT}, n_local={N_LOCAL}, page size 1, permuted pool rows"},
+        "us_per_chunk_layer": 1e3 * ms / (n_chunks * layers),
+        "kernel_us_last_chunks": {k: round(1e3 * v[0] / v[1], 2) for k, v in stages.items()},
+        "roofline": {"bound": "tensor", "kernel": "extend_attend_tc5_kernel", "achieved": flops / (att_us * 1e-6) / 1e12,
+                     "peak": peak, "unit": "TFLOP/s", "frac": flops / (att_us * 1e-6) / 1e12 / peak, "peak_source": src,
+                     "flops_per_launch": flops, "us_per_launch": att_us, "traffic": None},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.prefill:
+        run_prefill(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
