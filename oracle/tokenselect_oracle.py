@@ -77,16 +77,18 @@ def chunk_fingerprint(q: torch.Tensor, n_local: int, rope_base: float, rope_scal
                       fixed_order: bool = True) -> torch.Tensor:
     """Scoring query of a prefill chunk: the mean over the chunk of the rotated, rounded queries
     (token_retrieval.py:392, ``torch.mean(query, dim=0)``), ``[Hq, D]`` in ``q.dtype``.  ``fixed_order``
-    fixes what torch leaves open: 32 fp32 partial sums (partial j takes queries j, j+32, ... in ascending
-    order), joined by an XOR butterfly (16, 8, 4, 2, 1), one fp32 division by the chunk length, one
-    rounding to the dtype; otherwise ``torch.mean`` itself is called."""
+    fixes what torch leaves open: 128 fp32 partial sums (partial s takes queries s, s+128, ... in ascending
+    order); lane j of 32 joins its four partials as ``((j + (j+32)) + (j+64)) + (j+96)``; an XOR butterfly
+    (16, 8, 4, 2, 1) joins the lanes; one fp32 division by the chunk length, one rounding to the dtype;
+    otherwise ``torch.mean`` itself is called."""
     rot = rotate_chunk_queries(q, n_local, rope_base, rope_scale)
     if not fixed_order:
         return torch.mean(rot.view(rot.shape[0], -1), dim=0).view(rot.shape[1:])
     rot32 = rot.float().numpy()
-    part = np.zeros((32,) + tuple(rot.shape[1:]), dtype=np.float32)
+    p128 = np.zeros((128,) + tuple(rot.shape[1:]), dtype=np.float32)
     for i in range(rot.shape[0]):
-        part[i % 32] = part[i % 32] + rot32[i]
+        p128[i % 128] = p128[i % 128] + rot32[i]
+    part = ((p128[0:32] + p128[32:64]) + p128[64:96]) + p128[96:128]
     lanes = np.arange(32)
     for o in (16, 8, 4, 2, 1):
         part = part + part[lanes ^ o]

@@ -31,10 +31,11 @@ constexpr float kLog2eX = 1.4426950408889634f;
 // ------------------------------------------------------------------------------------------------
 // 1. K/V rows of the chunk into the pools; fingerprint; the (length, request) pair the selection kernel reads
 // ------------------------------------------------------------------------------------------------
-// Fingerprint: a warp owns eight adjacent rotation pairs (h, i0..i0+7).  Lane j rotates the queries
-// t = j, j+32, ... at position (n_local + t) * rope_scale, rounds each to the model dtype (:98-107) and
-// sums them in fp32 in ascending t; an XOR butterfly (16, 8, 4, 2, 1) joins the 32 partial sums; one fp32
-// division by the chunk length, one rounding.  (torch.mean leaves the order open; this one is fixed.)
+// Fingerprint: a warp owns eight adjacent rotation pairs (h, i0..i0+7).  Every query t is rotated at position
+// (n_local + t) * rope_scale and rounded to the model dtype (:98-107).  Summation order (torch.mean leaves
+// it open; this one is fixed): 128 fp32 partial sums, partial s taking t = s, s+128, ... in ascending order;
+// lane j joins its four partials ((j + (j+32)) + (j+64)) + (j+96); an XOR butterfly (16, 8, 4, 2, 1) joins
+// the lanes; one fp32 division by the chunk length, one rounding.
 template <typename T>
 __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendParams e) {
     if (*(volatile int*)e.err != 0) return;
@@ -54,46 +55,60 @@ __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendPa
 #pragma unroll
             for (int u = 0; u < 8; ++u) inv[u] = (float)(1.0 / pow(e.rope_base, (double)(2 * (i0 + u)) / (double)e.d));
         }
+        // four independent chains per lane (queries j, j+32, j+64, j+96 mod 128) keep four loads in flight
+        float a1[4][8], a2[4][8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int u = 0; u < 8; ++u) { a1[c][u] = 0.f; a2[c][u] = 0.f; }
+        for (int t0 = lane; t0 < lq; t0 += 128) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int t = t0 + 32 * c;
+                if (t < lq) {
+                    T x1[8], x2[8];
+                    if constexpr (sizeof(T) == 2) {
+                        *reinterpret_cast<uint4*>(x1) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
+                        *reinterpret_cast<uint4*>(x2) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 8; u += 4) {
+                            *reinterpret_cast<float4*>(x1 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
+                            *reinterpret_cast<float4*>(x2 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
+                        }
+                    }
+                    float2 cs[8];
+                    if (e.chunk_cs != nullptr) {
+                        const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float4 v = src[u];
+                            cs[2 * u] = make_float2(v.x, v.y);
+                            cs[2 * u + 1] = make_float2(v.z, v.w);
+                        }
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
+                            cs[u] = make_float2(cosf(ang), sinf(ang));
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float xa = to_f32<T>(x1[u]), xb = to_f32<T>(x2[u]);
+                        const float r1 = __fadd_rn(__fmul_rn(xa, cs[u].x), __fmul_rn(-xb, cs[u].y));
+                        const float r2 = __fadd_rn(__fmul_rn(xb, cs[u].x), __fmul_rn(xa, cs[u].y));
+                        a1[c][u] = __fadd_rn(a1[c][u], to_f32<T>(from_f32<T>(r1)));
+                        a2[c][u] = __fadd_rn(a2[c][u], to_f32<T>(from_f32<T>(r2)));
+                    }
+                }
+            }
+        }
         float acc1[8], acc2[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { acc1[u] = 0.f; acc2[u] = 0.f; }
-#pragma unroll 4
-        for (int t = lane; t < lq; t += 32) {
-            T x1[8], x2[8];
-            if constexpr (sizeof(T) == 2) {
-                *reinterpret_cast<uint4*>(x1) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
-                *reinterpret_cast<uint4*>(x2) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
-            } else {
-#pragma unroll
-                for (int u = 0; u < 8; u += 4) {
-                    *reinterpret_cast<float4*>(x1 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
-                    *reinterpret_cast<float4*>(x2 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
-                }
-            }
-            float2 cs[8];
-            if (e.chunk_cs != nullptr) {
-                const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const float4 v = src[u];
-                    cs[2 * u] = make_float2(v.x, v.y);
-                    cs[2 * u + 1] = make_float2(v.z, v.w);
-                }
-            } else {
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
-                    cs[u] = make_float2(cosf(ang), sinf(ang));
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float a = to_f32<T>(x1[u]), b = to_f32<T>(x2[u]);
-                const float r1 = __fadd_rn(__fmul_rn(a, cs[u].x), __fmul_rn(-b, cs[u].y));
-                const float r2 = __fadd_rn(__fmul_rn(b, cs[u].x), __fmul_rn(a, cs[u].y));
-                acc1[u] = __fadd_rn(acc1[u], to_f32<T>(from_f32<T>(r1)));
-                acc2[u] = __fadd_rn(acc2[u], to_f32<T>(from_f32<T>(r2)));
-            }
+        for (int u = 0; u < 8; ++u) {
+            acc1[u] = __fadd_rn(__fadd_rn(__fadd_rn(a1[0][u], a1[1][u]), a1[2][u]), a1[3][u]);
+            acc2[u] = __fadd_rn(__fadd_rn(__fadd_rn(a2[0][u], a2[1][u]), a2[2][u]), a2[3][u]);
         }
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) {
