@@ -172,7 +172,8 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* args);
  * at that position; entry j is rotated at position j (:746-772).  The caller loops over chunks of at most
  * ts_config.prefill_chunk tokens exactly as :716-724 does.
  *
- * Needs prefill_chunk > 0 in the configuration, tp_size == 1 and n_init+top_k+n_local >= chunk_len.
+ * Needs prefill_chunk > 0 in the configuration and n_init+top_k+n_local >= chunk_len; with tp_size > 1 the
+ * peers must be attached (ts_tp_attach_peers) and the selection cache off, as for ts_decode_layer.
  * The selection cache, when on, is consulted and updated with the fingerprint as in the reference.
  */
 typedef struct ts_extend_args {

@@ -14,6 +14,7 @@ from oracle import tokenselect_oracle as orc
 
 pytestmark = pytest.mark.gpu
 HQ, HKV, D, N_INIT, N_LOCAL, K, BASE, N = 8, 4, 128, 16, 64, 256, 5e5, 6000
+LQ = 96
 
 
 def _free_port():
@@ -49,8 +50,17 @@ def _worker(rank, world, port, fused, out_dir):
             out = eng.decode_layer(0, q, None, None, None, kp, vp, rtt, ridx, lens, debug=dbg)
         torch.cuda.synchronize()
         eng.raise_on_device_error()
-        torch.save({"slots": dbg["slots"].cpu(), "positions": dbg["positions"].cpu(), "out": out.cpu()},
-                   os.path.join(out_dir, f"rank{rank}.pt"))
+        rec = {"slots": dbg["slots"].cpu(), "positions": dbg["positions"].cpu(), "out": out.cpu()}
+        if fused:
+            # one prefill chunk of LQ tokens closing the same request, heads split the same way
+            qc = synth.make_chunk_queries(91, case, LQ, HQ, D).view(LQ, HQ, D)[:, rank * hq_r:(rank + 1) * hq_r]
+            dbg2 = eng.new_debug_buffers(1)
+            out2 = eng.extend_chunk(0, qc.reshape(LQ, -1).contiguous().to(dev), None, None, None, kp, vp, rtt,
+                                    case.req_pool_idx, N, debug=dbg2)
+            torch.cuda.synchronize()
+            eng.raise_on_device_error()
+            rec.update({"x_slots": dbg2["slots"].cpu(), "x_positions": dbg2["positions"].cpu(), "x_out": out2.cpu()})
+        torch.save(rec, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -77,3 +87,19 @@ def test_two_gpu_tensor_parallel(fused):
                                    case.v_pool[:, r * hkv_r:(r + 1) * hkv_r], res[0]["slots"][0], D ** -0.5, BASE, 1.0,
                                    0.0, torch.float64).reshape(-1)
         assert (res[r]["out"][0].double() - ref).abs().max().item() <= 2e-2
+    if fused:
+        # the prefill chunk: same rows on both ranks, equal to the oracle's tensor-parallel emulation
+        assert torch.equal(res[0]["x_slots"], res[1]["x_slots"]), "ranks selected different rows for the chunk"
+        qc = synth.make_chunk_queries(91, case, LQ, HQ, D)
+        ref = orc.DecodeOracle(ocfg, tp_ranks=world).extend_chunk(0, 1, qc, None, None, None, case.k_pool, case.v_pool,
+                                                                  case.req_to_token[1], N, attn_dtype=torch.float64)
+        got = res[0]["x_positions"][0, N_INIT:N_INIT + K].numpy() - N_INIT
+        want = ref["positions"][N_INIT:N_INIT + K].numpy() - N_INIT
+        ok, why = orc.index_sets_match(got, want, ref["info"]["votes"].double().numpy(), K)
+        assert ok, why
+        for r in range(world):
+            want_o = orc.sparse_prefill_attention(
+                qc.view(LQ, HQ, D)[:, r * hq_r:(r + 1) * hq_r], case.k_pool[:, r * hkv_r:(r + 1) * hkv_r],
+                case.v_pool[:, r * hkv_r:(r + 1) * hkv_r], res[0]["x_slots"][0], D ** -0.5, BASE, 1.0, 0.0,
+                torch.float64).reshape(LQ, -1)
+            assert (res[r]["x_out"].double() - want_o).abs().max().item() <= 2e-2

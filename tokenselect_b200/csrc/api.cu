@@ -434,7 +434,10 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
 int ts_extend_chunk(ts_handle* h, const ts_extend_args* a) {
     if (!h || !a || a->struct_size != sizeof(ts_extend_args)) return TS_ERR_INVALID_ARG;
     const ts_config& c = h->cfg;
-    if (c.prefill_chunk < 1 || c.tp_size != 1) return TS_ERR_UNSUPPORTED;
+    if (c.prefill_chunk < 1) return TS_ERR_UNSUPPORTED;
+    // tensor parallel: only the form that sums the votes inside the selection kernel
+    const bool fused_tp = c.tp_size > 1;
+    if (fused_tp && (!h->peers_attached || c.query_cache)) return TS_ERR_UNSUPPORTED;
     if (a->layer < 0 || a->layer >= c.n_layers) return TS_ERR_INVALID_ARG;
     if (a->chunk_len < 1) return TS_ERR_INVALID_ARG;
     if (a->chunk_len > c.prefill_chunk) return TS_ERR_CAPACITY;
@@ -477,11 +480,11 @@ int ts_extend_chunk(ts_handle* h, const ts_extend_args* a) {
     d.dbg_sel_count = a->dbg_sel_count; d.dbg_flags = a->dbg_flags;
     d.stream = a->stream;
     LayerParams p; Launch l;
-    int s = fill(h, &d, p, l);
+    int s = fill(h, &d, p, l, fused_tp);
     if (s != TS_OK) return s;
     p.q_prerot = 1;
     TS_TRY(launch_extend_prep(e, l), "extend prepare");
-    TS_TRY(launch_fused(p, l, kModeAll), "select");
+    TS_TRY(launch_fused(p, l, fused_tp ? kModeTpFused : kModeAll), "select");
     TS_TRY(launch_extend_attend(e, l), "extend attend");
     if (a->dbg_fingerprint)
         TS_TRY(cudaMemcpyAsync(a->dbg_fingerprint, h->ext_fp, (size_t)c.hq * c.head_dim * h->elem,

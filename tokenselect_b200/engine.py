@@ -132,7 +132,7 @@ class TokenSelectEngine:
         c.max_total_tokens = max_total
         c.tp_rank, c.tp_size = cfg.tp_rank, cfg.tp_size
         c.flags = (_lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0) | {"auto": 0, "direct": 2, "staged": 4}[cfg.score_path]
-        c.prefill_chunk = int(cfg.prefill_chunk) if cfg.tp_size == 1 else 0
+        c.prefill_chunk = int(cfg.prefill_chunk) if (cfg.tp_size == 1 or (cfg.tp_fused and not cfg.query_cache)) else 0
         c.score_cos_sin = score_cs.data_ptr()
         c.attn_cos_sin = attn_cs.data_ptr()
         self._c = c
@@ -342,7 +342,7 @@ class TokenSelectEngine:
         ``count, flags [1]`` and ``fingerprint [Hq*D]`` (model dtype)."""
         cfg = self.cfg
         if self.chunk_cs is None:
-            raise ValueError("prefill needs prefill_chunk > 0 and tp_size == 1")
+            raise ValueError("prefill needs prefill_chunk > 0 (and, with tp_size > 1, the in-kernel vote exchange)")
         lq = q.shape[0]
         hd, kd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
         if out is None:
