@@ -147,3 +147,41 @@ def test_extend_argument_checks():
     eng2 = gu.make_engine(8, 2, 128, 16, 64, 256, 5e5, BF16, max_ctx=4096, max_batch=1, prefill_chunk=0)
     with pytest.raises(ValueError):
         eng2.extend_chunk(0, q[:64], None, None, None, kp, kp.clone(), rtt, 1, 100)
+
+
+def test_selection_cache_across_chunks_and_decode():
+    """Selection cache on: two consecutive chunks with similar queries and a decode step.  The reuse
+    decisions (cosine of the new scoring query against the cached fingerprint, fixed fp32 order) and the
+    emitted positions must equal the oracle's."""
+    hq, hkv, d, n_init, n_local, top_k, base = 8, 2, 128, 16, 64, 256, 5e5
+    n_total, lq = 2200, 64
+    case = synth.make_layer_case(51, n_total, hq, hkv, d, n_init, n_local, base, dtype=BF16)
+    eng = gu.make_engine(hq, hkv, d, n_init, n_local, top_k, base, BF16, max_ctx=n_total + 8, max_batch=1,
+                         prefill_chunk=512, query_cache=True, similarity_threshold=0.9)
+    dev = eng.device
+    eng.reset_request(case.req_pool_idx)
+    o = orc.DecodeOracle(gu.oracle_config(eng))
+    o.reset_request(case.req_pool_idx)
+    kp, vp, rtt = case.k_pool.to(dev), case.v_pool.to(dev), case.req_to_token.to(dev)
+    row = case.req_to_token[case.req_pool_idx]
+    q1 = synth.make_chunk_queries(51, case, lq, hq, d, spread=0.3)
+    q2 = synth.make_chunk_queries(52, case, lq, hq, d, spread=0.3)      # same direction, other noise
+    q3 = -q1                                                             # opposite direction
+    flags = []
+    for step, (qc, n) in enumerate(((q1, 2000), (q2, 2064), (q3, 2128))):
+        dbg = eng.new_debug_buffers(1)
+        eng.extend_chunk(0, qc.to(dev), None, None, None, kp, vp, rtt, case.req_pool_idx, n, debug=dbg)
+        torch.cuda.synchronize()
+        eng.raise_on_device_error()
+        ref = o.extend_chunk(0, case.req_pool_idx, qc, None, None, None, case.k_pool, case.v_pool, row, n)
+        res = {k: v.cpu() for k, v in dbg.items()}
+        assert int(res["flags"][0]) == ref["flag"], (step, ref["info"].get("cos"))
+        flags.append(ref["flag"])
+        if ref["flag"] == orc.FLAG_RECOMPUTE:
+            gu.check_selection(eng, res, 0, ref["positions"], ref["info"]["votes"], n)
+            # keep the oracle's cached set equal to the GPU's (they may differ inside the tie band)
+            o.cache[(case.req_pool_idx, 0)].topk_positions = res["positions"][0, n_init:n_init + top_k].long().clone()
+        else:
+            assert torch.equal(res["positions"][0, : eng.cfg.n_sel].long(), ref["positions"].long())
+    assert flags == [orc.FLAG_RECOMPUTE, orc.FLAG_REUSE, orc.FLAG_RECOMPUTE]
+    assert eng.counters(case.req_pool_idx) == (3, 1)

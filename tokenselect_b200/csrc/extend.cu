@@ -62,42 +62,46 @@ __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendPa
 #pragma unroll
             for (int u = 0; u < 8; ++u) { a1[c][u] = 0.f; a2[c][u] = 0.f; }
         for (int t0 = lane; t0 < lq; t0 += 128) {
+            // all loads of the four chains first (index clamped; the sums below are predicated)
+            T x1[4][8], x2[4][8];
+            float2 cs[4][8];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int t = t0 + 32 * c;
-                if (t < lq) {
-                    T x1[8], x2[8];
-                    if constexpr (sizeof(T) == 2) {
-                        *reinterpret_cast<uint4*>(x1) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
-                        *reinterpret_cast<uint4*>(x2) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
-                    } else {
+                const int t = min(t0 + 32 * c, lq - 1);
+                if constexpr (sizeof(T) == 2) {
+                    *reinterpret_cast<uint4*>(x1[c]) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
+                    *reinterpret_cast<uint4*>(x2[c]) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
+                } else {
 #pragma unroll
-                        for (int u = 0; u < 8; u += 4) {
-                            *reinterpret_cast<float4*>(x1 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
-                            *reinterpret_cast<float4*>(x2 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
-                        }
+                    for (int u = 0; u < 8; u += 4) {
+                        *reinterpret_cast<float4*>(x1[c] + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
+                        *reinterpret_cast<float4*>(x2[c] + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
                     }
-                    float2 cs[8];
-                    if (e.chunk_cs != nullptr) {
-                        const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
+                }
+                if (e.chunk_cs != nullptr) {
+                    const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const float4 v = src[u];
-                            cs[2 * u] = make_float2(v.x, v.y);
-                            cs[2 * u + 1] = make_float2(v.z, v.w);
-                        }
-                    } else {
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
-                            cs[u] = make_float2(cosf(ang), sinf(ang));
-                        }
+                    for (int u = 0; u < 4; ++u) {
+                        const float4 v = src[u];
+                        cs[c][2 * u] = make_float2(v.x, v.y);
+                        cs[c][2 * u + 1] = make_float2(v.z, v.w);
                     }
+                } else {
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
-                        const float xa = to_f32<T>(x1[u]), xb = to_f32<T>(x2[u]);
-                        const float r1 = __fadd_rn(__fmul_rn(xa, cs[u].x), __fmul_rn(-xb, cs[u].y));
-                        const float r2 = __fadd_rn(__fmul_rn(xb, cs[u].x), __fmul_rn(xa, cs[u].y));
+                        const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
+                        cs[c][u] = make_float2(cosf(ang), sinf(ang));
+                    }
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (t0 + 32 * c < lq) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float xa = to_f32<T>(x1[c][u]), xb = to_f32<T>(x2[c][u]);
+                        const float r1 = __fadd_rn(__fmul_rn(xa, cs[c][u].x), __fmul_rn(-xb, cs[c][u].y));
+                        const float r2 = __fadd_rn(__fmul_rn(xb, cs[c][u].x), __fmul_rn(xa, cs[c][u].y));
                         a1[c][u] = __fadd_rn(a1[c][u], to_f32<T>(from_f32<T>(r1)));
                         a2[c][u] = __fadd_rn(a2[c][u], to_f32<T>(from_f32<T>(r2)));
                     }
@@ -462,7 +466,7 @@ __global__ void __launch_bounds__(128, 1) extend_attend_tc_kernel(const ExtendPa
 // ------------------------------------------------------------------------------------------------
 // grid (rows_q / 128, hq), 544 threads, one CTA per SM.  M = 128 query rows per CTA; keys in blocks of 64.
 //   S[b&1] (128 x 64 fp32, TMEM columns 64*(b&1)..)  = Q (smem, K-major SW128) . K_b^T (smem, K-major SW128)
-//   O      (128 x 128 fp32, TMEM columns 128..255)  += P_b (TMEM columns 256..287, packed bf16) . V_b (smem, MN-major SW128)
+//   O      (128 x 128 fp32, TMEM columns 128..255)  += P_b (TMEM columns 256 + 32*(b&1).., packed bf16) . V_b (smem, MN-major SW128)
 // Four threads share TMEM lane r == query row r (a quarter of the columns each): they read S with
 // tcgen05.ld, keep the row's reference maximum and partial sums and write P = 2^(S - ref) back to tensor
 // memory as bf16.  O stays in tensor memory across blocks; it is rescaled (tcgen05.ld / st) only when a
@@ -476,7 +480,7 @@ struct Tc5Smem {
     unsigned char k[kKvStages][kTile * 256];    // 2 halves x [64 keys][128 B]
     unsigned char v[kKvStages][kTile * 256];
     float rowmax[2][4][128];                    // [block parity][column quarter][row]: row maxima; row sums at the end
-    uint64_t qbar, full[kKvStages], s_done[2], o_done, p_ready;
+    uint64_t qbar, full[kKvStages], s_done[2], o_done[2], p_ready[2];
     uint32_t tmem_base;
 };
 
@@ -586,8 +590,10 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
         for (int s = 0; s < kKvStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
         mbar_init(smem_u32(&sm.s_done[0]), 1);
         mbar_init(smem_u32(&sm.s_done[1]), 1);
-        mbar_init(smem_u32(&sm.o_done), 1);
-        mbar_init(smem_u32(&sm.p_ready), kTc5Softmax / 32);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&sm.o_done[i]), 1);
+            mbar_init(smem_u32(&sm.p_ready[i]), kTc5Softmax / 32);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -639,17 +645,17 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
                 if (blk + 1 < nblk) issue_qk(blk + 1);
                 if (blk > 0 && blk - 1 + kKvStages < nblk) {
                     // P.V of the previous block is complete: its stage can take the tile four blocks ahead
-                    mbar_wait(smem_u32(&sm.o_done), (uint32_t)((blk - 1) & 1), e.err, dead, 46);
+                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 46);
                     load_tile(blk - 1 + kKvStages);
                 }
-                mbar_wait(smem_u32(&sm.p_ready), (uint32_t)(blk & 1), e.err, dead, 47);
+                mbar_wait(smem_u32(&sm.p_ready[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 47);
                 tc_fence_after();
                 const uint32_t va = smem_u32(sm.v[blk % kKvStages]);
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks)               // 16 keys per step: 8 packed columns of P
-                    umma_bf16_ts(tmem + kTmemO, tmem + kTmemP + 8u * ks, umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024),
-                                 kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&sm.o_done));
+                    umma_bf16_ts(tmem + kTmemO, tmem + kTmemP + 32u * (blk & 1) + 8u * ks,
+                                 umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024), kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&sm.o_done[blk & 1]));
             }
         }
     } else {
@@ -697,11 +703,11 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
             named_bar_sync(1 + rq, 128);                     // the four warps that share these rows
             mx = fmaxf(fmaxf(rm[0], rm[128]), fmaxf(rm[256], rm[384]));
             if (blk > 0) {
-                // P.V of the previous block is complete: O may be rescaled, P may be overwritten
-                mbar_wait(smem_u32(&sm.o_done), (uint32_t)((blk - 1) & 1), e.err, dead, 44);
-                tc_fence_after();
                 const bool grow = mx > m_ref + 8.f;
                 if (__any_sync(0xffffffffu, grow)) {
+                    // O is rescaled in place: every P.V issued so far must be complete (they run in order)
+                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 44);
+                    tc_fence_after();
                     const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
                     uint32_t r[32];
                     tmem_ld32(t_o, r);
@@ -723,12 +729,16 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
                 sum += p0 + p1;
                 w[u] = pack_bf16(p0, p1);
             }
-            tmem_st8(t_p, w);
+            if (blk >= 2) {                                  // P.V of block blk-2 has finished reading this P buffer
+                mbar_wait(smem_u32(&sm.o_done[blk & 1]), (uint32_t)(((blk - 2) >> 1) & 1), e.err, dead, 48);
+                tc_fence_after();
+            }
+            tmem_st8(t_p + 32u * (blk & 1), w);
             tmem_wait_st();
             l_run += sum;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready));
+            if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[blk & 1]));
         }
         // row sums: the four partial sums of a row share the reference maximum
         float* rs = &sm.rowmax[nblk & 1][0][r_in];
@@ -736,7 +746,7 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
         named_bar_sync(1 + rq, 128);
         const float l_tot = (rs[0] + rs[128]) + (rs[256] + rs[384]);
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        mbar_wait(smem_u32(&sm.o_done), (uint32_t)((nblk - 1) & 1), e.err, dead, 45);
+        mbar_wait(smem_u32(&sm.o_done[(nblk - 1) & 1]), (uint32_t)(((nblk - 1) >> 1) & 1), e.err, dead, 45);
         tc_fence_after();
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + 32 * cq;
         uint32_t r[32];
