@@ -686,15 +686,11 @@ template <typename T, int E>
 static cudaError_t launch_attend_t(const LayerParams& p, const Launch& l) {
     constexpr int D = 16 * E;
     const size_t smem = attn_smem_layout(p.hq, p.hkv, D, p.attn_chunk_tokens, sizeof(T)).total;
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attend_split_kernel<T, E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = smem;
-    }
+    static SmemConfig configured = {};
+    cudaError_t e = ensure_dynamic_smem(attend_split_kernel<T, E>, smem, configured);
+    if (e != cudaSuccess) return e;
     stage_begin(l, kStageAttendSplit);
-    cudaError_t e = launch_pdl(attend_split_kernel<T, E>, dim3(p.attn_chunks, p.batch), dim3(kAttnThreads), smem,
+    e = launch_pdl(attend_split_kernel<T, E>, dim3(p.attn_chunks, p.batch), dim3(kAttnThreads), smem,
                                l.stream, p);
     stage_end(l);
     if (e != cudaSuccess) return e;
@@ -708,15 +704,11 @@ template <int HKV>
 static cudaError_t launch_attend_tc(const LayerParams& p, const Launch& l) {
     constexpr int BPC = 8 / HKV;
     const size_t smem = (size_t)2 * BPC * 16 * (HKV * 256 + 16) + (size_t)BPC * 2 * 4096 + 16;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attend_split_tc_kernel<HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemConfig configured = {};
+    cudaError_t e = ensure_dynamic_smem(attend_split_tc_kernel<HKV>, smem, configured);
+    if (e != cudaSuccess) return e;
     stage_begin(l, kStageAttendSplit);
-    cudaError_t e = launch_pdl(attend_split_tc_kernel<HKV>, dim3((p.attn_chunks + BPC - 1) / BPC, p.batch), dim3(256),
+    e = launch_pdl(attend_split_tc_kernel<HKV>, dim3((p.attn_chunks + BPC - 1) / BPC, p.batch), dim3(256),
                                smem, l.stream, p);
     stage_end(l);
     if (e != cudaSuccess) return e;

@@ -192,6 +192,25 @@ struct Launch {
     StageTimer* timer;
 };
 
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of a kernel: remember, per
+// kernel (one static instance per launcher), the largest size already configured on each device.
+struct SmemConfig {
+    size_t bytes[64];
+};
+template <typename F>
+inline cudaError_t ensure_dynamic_smem(F func, size_t bytes, SmemConfig& cfg) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (bytes > cfg.bytes[dev]) {
+        e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return e;
+        cfg.bytes[dev] = bytes;
+    }
+    return cudaSuccess;
+}
+
 enum Stage { kStagePrep = 0, kStageSelect = 1, kStageSelectTpB = 2, kStageAttendSplit = 3, kStageAttendMerge = 4,
              kStageExtendPrep = 5, kStageExtendGather = 6, kStageExtendAttend = 7 };
 

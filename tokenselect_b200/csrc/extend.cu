@@ -31,23 +31,25 @@ constexpr float kLog2eX = 1.4426950408889634f;
 // ------------------------------------------------------------------------------------------------
 // 1. K/V rows of the chunk into the pools; fingerprint; the (length, request) pair the selection kernel reads
 // ------------------------------------------------------------------------------------------------
-// Fingerprint: a warp owns eight adjacent rotation pairs (h, i0..i0+7).  Every query t is rotated at position
+// Fingerprint: four warps own eight adjacent rotation pairs (h, i0..i0+7).  Every query t is rotated at position
 // (n_local + t) * rope_scale and rounded to the model dtype (:98-107).  Summation order (torch.mean leaves
 // it open; this one is fixed): 128 fp32 partial sums, partial s taking t = s, s+128, ... in ascending order;
 // lane j joins its four partials ((j + (j+32)) + (j+64)) + (j+96); an XOR butterfly (16, 8, 4, 2, 1) joins
 // the lanes; one fp32 division by the chunk length, one rounding.
 template <typename T>
 __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendParams e) {
+    __shared__ float part[2][4][32][16];
     if (*(volatile int*)e.err != 0) return;
     const int half = e.d / 2, hd = e.hq * e.d;
-    const int groups = e.hq * half / 8;                                   // pair groups == warps needed
-    const int fp_blocks = (groups + kExtThreads / 32 - 1) / (kExtThreads / 32);
+    const int groups = e.hq * half / 8;                                   // groups of eight pairs
+    const int fp_blocks = (groups + 1) / 2;                               // two groups per CTA, four warps each
     const int lq = e.chunk_len;
     if (blockIdx.x == 0 && threadIdx.x == 0) { e.meta[0] = e.seq_len; e.meta[1] = e.req; }
     if ((int)blockIdx.x < fp_blocks) {
-        const int lane = threadIdx.x & 31;
-        const int grp = blockIdx.x * (kExtThreads / 32) + (threadIdx.x >> 5);
-        if (grp >= groups) return;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const int gl = warp >> 2, c = warp & 3;                           // group inside the CTA, chain of this warp
+        const int grp = min(blockIdx.x * 2 + gl, groups - 1);
+        const bool live = (int)blockIdx.x * 2 + gl < groups;
         const int h = grp / (half / 8), i0 = (grp - h * (half / 8)) * 8;
         const T* q = reinterpret_cast<const T*>(e.q) + (size_t)h * e.d + i0;
         float inv[8];
@@ -55,64 +57,59 @@ __global__ void __launch_bounds__(kExtThreads) extend_prep_kernel(const ExtendPa
 #pragma unroll
             for (int u = 0; u < 8; ++u) inv[u] = (float)(1.0 / pow(e.rope_base, (double)(2 * (i0 + u)) / (double)e.d));
         }
-        // four independent chains per lane (queries j, j+32, j+64, j+96 mod 128) keep four loads in flight
-        float a1[4][8], a2[4][8];
+        // warp c of a group holds partial sums s = lane + 32c: queries t = s, s+128, ... in ascending order
+        float a1[8], a2[8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int u = 0; u < 8; ++u) { a1[u] = 0.f; a2[u] = 0.f; }
+#pragma unroll 4
+        for (int t = lane + 32 * c; t < lq; t += 128) {
+            T x1[8], x2[8];
+            if constexpr (sizeof(T) == 2) {
+                *reinterpret_cast<uint4*>(x1) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
+                *reinterpret_cast<uint4*>(x2) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
+            } else {
 #pragma unroll
-            for (int u = 0; u < 8; ++u) { a1[c][u] = 0.f; a2[c][u] = 0.f; }
-        for (int t0 = lane; t0 < lq; t0 += 128) {
-            // all loads of the four chains first (index clamped; the sums below are predicated)
-            T x1[4][8], x2[4][8];
-            float2 cs[4][8];
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int t = min(t0 + 32 * c, lq - 1);
-                if constexpr (sizeof(T) == 2) {
-                    *reinterpret_cast<uint4*>(x1[c]) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd);
-                    *reinterpret_cast<uint4*>(x2[c]) = *reinterpret_cast<const uint4*>(q + (size_t)t * hd + half);
-                } else {
-#pragma unroll
-                    for (int u = 0; u < 8; u += 4) {
-                        *reinterpret_cast<float4*>(x1[c] + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
-                        *reinterpret_cast<float4*>(x2[c] + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
-                    }
+                for (int u = 0; u < 8; u += 4) {
+                    *reinterpret_cast<float4*>(x1 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + u);
+                    *reinterpret_cast<float4*>(x2 + u) = *reinterpret_cast<const float4*>(q + (size_t)t * hd + half + u);
                 }
-                if (e.chunk_cs != nullptr) {
-                    const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
+            }
+            float2 cs[8];
+            if (e.chunk_cs != nullptr) {
+                const float4* src = reinterpret_cast<const float4*>(e.chunk_cs + (size_t)t * half + i0);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float4 v = src[u];
-                        cs[c][2 * u] = make_float2(v.x, v.y);
-                        cs[c][2 * u + 1] = make_float2(v.z, v.w);
-                    }
-                } else {
+                for (int u = 0; u < 4; ++u) {
+                    const float4 v = src[u];
+                    cs[2 * u] = make_float2(v.x, v.y);
+                    cs[2 * u + 1] = make_float2(v.z, v.w);
+                }
+            } else {
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
-                        cs[c][u] = make_float2(cosf(ang), sinf(ang));
-                    }
+                for (int u = 0; u < 8; ++u) {
+                    const float ang = __fmul_rn((float)((double)(e.n_local + t) * e.rope_scale), inv[u]);
+                    cs[u] = make_float2(cosf(ang), sinf(ang));
                 }
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                if (t0 + 32 * c < lq) {
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const float xa = to_f32<T>(x1[c][u]), xb = to_f32<T>(x2[c][u]);
-                        const float r1 = __fadd_rn(__fmul_rn(xa, cs[c][u].x), __fmul_rn(-xb, cs[c][u].y));
-                        const float r2 = __fadd_rn(__fmul_rn(xb, cs[c][u].x), __fmul_rn(xa, cs[c][u].y));
-                        a1[c][u] = __fadd_rn(a1[c][u], to_f32<T>(from_f32<T>(r1)));
-                        a2[c][u] = __fadd_rn(a2[c][u], to_f32<T>(from_f32<T>(r2)));
-                    }
-                }
+            for (int u = 0; u < 8; ++u) {
+                const float xa = to_f32<T>(x1[u]), xb = to_f32<T>(x2[u]);
+                const float r1 = __fadd_rn(__fmul_rn(xa, cs[u].x), __fmul_rn(-xb, cs[u].y));
+                const float r2 = __fadd_rn(__fmul_rn(xb, cs[u].x), __fmul_rn(xa, cs[u].y));
+                a1[u] = __fadd_rn(a1[u], to_f32<T>(from_f32<T>(r1)));
+                a2[u] = __fadd_rn(a2[u], to_f32<T>(from_f32<T>(r2)));
             }
         }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { part[gl][c][lane][u] = a1[u]; part[gl][c][lane][8 + u] = a2[u]; }
+        __syncthreads();
+        if (c != 0 || !live) return;
         float acc1[8], acc2[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            acc1[u] = __fadd_rn(__fadd_rn(__fadd_rn(a1[0][u], a1[1][u]), a1[2][u]), a1[3][u]);
-            acc2[u] = __fadd_rn(__fadd_rn(__fadd_rn(a2[0][u], a2[1][u]), a2[2][u]), a2[3][u]);
+            acc1[u] = __fadd_rn(__fadd_rn(__fadd_rn(part[gl][0][lane][u], part[gl][1][lane][u]), part[gl][2][lane][u]),
+                                part[gl][3][lane][u]);
+            acc2[u] = __fadd_rn(__fadd_rn(__fadd_rn(part[gl][0][lane][8 + u], part[gl][1][lane][8 + u]),
+                                          part[gl][2][lane][8 + u]), part[gl][3][lane][8 + u]);
         }
 #pragma unroll
         for (int o = 16; o >= 1; o >>= 1) {
@@ -817,7 +814,7 @@ __global__ void __launch_bounds__(kExtThreads) extend_attend_plain_kernel(const 
 template <typename T>
 cudaError_t launch_extend_prep_t(const ExtendParams& e, const Launch& l) {
     const int groups = e.hq * (e.d / 2) / 8;
-    const int fp_blocks = (groups + kExtThreads / 32 - 1) / (kExtThreads / 32);
+    const int fp_blocks = (groups + 1) / 2;
     const int row_vec = e.hkv * e.d * (int)sizeof(T) / 16;
     int app = e.k_new ? (e.chunk_len * row_vec + kExtThreads - 1) / kExtThreads : 0;
     if (app > 4 * l.num_sms) app = 4 * l.num_sms;
@@ -854,21 +851,15 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     if (err != cudaSuccess) return err;
     stage_begin(l, kStageExtendAttend);
     if (tc5) {
-        static bool configured5 = false;
+        static SmemConfig configured5 = {};
         const size_t smem5 = sizeof(Tc5Smem) + 1024;
-        if (!configured5) {
-            err = cudaFuncSetAttribute(extend_attend_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem5);
-            if (err != cudaSuccess) return err;
-            configured5 = true;
-        }
+        err = ensure_dynamic_smem(extend_attend_tc5_kernel, smem5, configured5);
+        if (err != cudaSuccess) return err;
         extend_attend_tc5_kernel<<<dim3(e.rows_q / 128, e.hq), kTc5Threads, smem5, l.stream>>>(e);
     } else if (tc) {
-        static bool configured = false;
-        if (!configured) {
-            err = cudaFuncSetAttribute(extend_attend_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(ExtSmem));
-            if (err != cudaSuccess) return err;
-            configured = true;
-        }
+        static SmemConfig configured = {};
+        err = ensure_dynamic_smem(extend_attend_tc_kernel, sizeof(ExtSmem), configured);
+        if (err != cudaSuccess) return err;
         extend_attend_tc_kernel<<<dim3(e.rows_q / kQTile, e.hq), 128, sizeof(ExtSmem), l.stream>>>(e);
     } else {
         const int warps = e.chunk_len * e.hq;

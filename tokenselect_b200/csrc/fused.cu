@@ -1406,13 +1406,9 @@ int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group) {
 template <typename T, int HKV, bool DIRECT>
 static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mode) {
     const size_t smem = kFusedDynSmem;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(fused_select_kernel<T, HKV, DIRECT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)smem);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    static SmemConfig configured = {};
+    cudaError_t e0 = ensure_dynamic_smem(fused_select_kernel<T, HKV, DIRECT>, smem, configured);
+    if (e0 != cudaSuccess) return e0;
     LayerParams pp = p;
     int m = mode;
     stage_begin(l, mode == kModeTpB ? kStageSelectTpB : kStageSelect);
