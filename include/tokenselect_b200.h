@@ -242,7 +242,8 @@ const char* ts_last_cuda_error(ts_handle* h);
  *          1 logits  [vote elems, hq] fp32, column c = kv_head*(hq/hkv) + j where j counts the
  *            query heads paired with kv_head in ascending head order
  *          2 votes   [vote elems] fp32 (after max-pool when enabled)
- *          3 sixteen uint64 nanosecond timestamps left by the selection kernel at its phase boundaries
+ *          3 sixty-four uint64 nanosecond timestamps left by the kernels at their phase boundaries
+ *          4 per request [batch] uint32: candidates that shared the vote histogram's threshold bin
  * In 1 and 2 the requests that recomputed their scores follow each other in batch order, each
  * region starting on a multiple of 128 candidates. */
 int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes);

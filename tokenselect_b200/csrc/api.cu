@@ -531,6 +531,7 @@ int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes) {
         case 1: src = p.logits; avail = (size_t)h->cand_capacity * h->cfg.hq * 4; break;
         case 2: src = p.votes_sel; avail = (size_t)h->cand_capacity * 4; break;
         case 3: src = p.phase_ts; avail = 64 * 8; break;
+        case 4: src = p.cand_count; avail = (size_t)h->cfg.max_batch * 4; break;
         default: return TS_ERR_INVALID_ARG;
     }
     if (bytes > avail) return TS_ERR_INVALID_ARG;
