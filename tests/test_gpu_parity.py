@@ -249,3 +249,35 @@ def test_invalid_arguments_are_rejected_on_the_host():
         eng.decode_layer(7, q[:1], None, None, None, pool, pool.clone(), rtt, idx[:1], idx[:1])  # layer out of range
     with pytest.raises(ValueError):
         eng.decode_layer(0, q[:1].float(), None, None, None, pool, pool.clone(), rtt, idx[:1], idx[:1])
+
+
+@pytest.mark.parametrize("gain", [6.0, 20.0], ids=["peaked", "very_peaked"])
+def test_underflowing_votes(gain):
+    """A query scaled until almost every softmax term underflows: most votes are denormal or exactly zero.
+    Votes in the normal fp32 range must select exactly as in the oracle; where the k-th vote itself is
+    denormal or zero, the two evaluations (division folded into the exponent here, exp then divide in the
+    oracle) may disagree only among candidates whose oracle vote is below 2^-120, and zeros are taken from
+    the lowest positions."""
+    hq, hkv, d, n_init, n_local, k, base, n = 8, 2, 128, 16, 64, 256, 5e5, 3000
+    case = synth.make_layer_case(61, n, hq, hkv, d, n_init, n_local, base, dtype=BF16)
+    case.q.mul_(gain)
+    eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, BF16, max_ctx=n + 8)
+    out, res = gu.run_gpu(eng, 0, *gu.case_tensors(case))
+    o = orc.DecodeOracle(gu.oracle_config(eng))
+    flag, pos, info = o.select(0, case.req_pool_idx, case.q.view(hq, d), case.k_pool,
+                               case.req_to_token[case.req_pool_idx], n)
+    votes = info["votes"].double().numpy()
+    got = res["positions"][0, n_init:n_init + k].numpy() - n_init
+    want = pos[n_init:n_init + k].numpy() - n_init
+    assert int(res["count"][0]) == eng.cfg.n_sel and np.all(np.diff(got) > 0)
+    kth = np.sort(votes)[::-1][k - 1]
+    diff = set(got.tolist()) ^ set(want.tolist())
+    tiny = 2.0 ** -120
+    if kth >= tiny:
+        ok, why = orc.index_sets_match(got, want, votes, k, rel_tol=1e-4)
+        assert ok, why
+    else:
+        assert all(votes[i] < tiny for i in diff), sorted(votes[list(diff)])[-3:]
+        # everything in the normal range is in
+        assert set(np.nonzero(votes >= tiny)[0].tolist()) <= set(got.tolist())
+    assert torch.isfinite(out.float()).all()

@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
 }
 
 // ------------------------------------------------------------------------------------------
-// Tensor-core split kernel (bf16, head_dim 128).  grid = (ceil(blocks / BPC), batch), 8 warps; a warp
+// Tensor-core split kernel (bf16, head_dim 128).  grid = (ceil(blocks / BPC), batch), BPC * HKV warps; a warp
 // owns one KV head and one block of 16 listed rows.
 //   S^T[heads x rows] = Q_rot . K_rot^T : A = the KV head's (<= 8) query heads, rotated, from registers;
 //                        B = key rows read with ldmatrix, rotated in registers (both members of a
@@ -386,9 +386,11 @@ __device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uin
     lo = pack_bf16x2(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
 }
 
-template <int HKV>
-__global__ void __launch_bounds__(256, 2) attend_split_tc_kernel(const LayerParams p) {
-    constexpr int BPC = 8 / HKV;                        // 16-row blocks per CTA
+// One warp per (16-row block, KV head): BPC blocks per CTA, 32 * BPC * HKV threads.  Few rows per CTA keep
+// the number of bulk copies one SM has to issue small (the copy engine issues about one per 35 ns).
+template <int HKV, int BPC>
+__global__ void __launch_bounds__(32 * BPC * HKV) attend_split_tc_kernel(const LayerParams p) {
+    constexpr int kThreads = 32 * BPC * HKV;
     constexpr int ROWB = HKV * 256, ROWS = ROWB + 16;   // key/value row bytes in the pool / in shared memory
     extern __shared__ __align__(128) unsigned char smem_raw[];
     unsigned char* sm_k = smem_raw;
@@ -460,7 +462,7 @@ __global__ void __launch_bounds__(256, 2) attend_split_tc_kernel(const LayerPara
             bulk_g2s(smem_u32(sm_cs), p.attn_cs_tile + (size_t)(base / 8) * 256, (uint32_t)tiles * 4096u, bar);
     }
     // rows past the end of the list: zeros, so that 0-weight products stay finite
-    for (int i = cnt * (ROWB / 16) + tid; i < BPC * 16 * (ROWB / 16); i += 256) {
+    for (int i = cnt * (ROWB / 16) + tid; i < BPC * 16 * (ROWB / 16); i += kThreads) {
         const int r = i / (ROWB / 16), c = i - r * (ROWB / 16);
         *reinterpret_cast<uint4*>(sm_k + r * ROWS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
         *reinterpret_cast<uint4*>(sm_v + r * ROWS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -702,13 +704,13 @@ static cudaError_t launch_attend_t(const LayerParams& p, const Launch& l) {
 
 template <int HKV>
 static cudaError_t launch_attend_tc(const LayerParams& p, const Launch& l) {
-    constexpr int BPC = 8 / HKV;
+    constexpr int BPC = HKV == 1 ? 2 : 1;
     const size_t smem = (size_t)2 * BPC * 16 * (HKV * 256 + 16) + (size_t)BPC * 2 * 4096 + 16;
     static SmemConfig configured = {};
-    cudaError_t e = ensure_dynamic_smem(attend_split_tc_kernel<HKV>, smem, configured);
+    cudaError_t e = ensure_dynamic_smem(attend_split_tc_kernel<HKV, BPC>, smem, configured);
     if (e != cudaSuccess) return e;
     stage_begin(l, kStageAttendSplit);
-    e = launch_pdl(attend_split_tc_kernel<HKV>, dim3((p.attn_chunks + BPC - 1) / BPC, p.batch), dim3(256),
+    e = launch_pdl(attend_split_tc_kernel<HKV, BPC>, dim3((p.attn_chunks + BPC - 1) / BPC, p.batch), dim3(32 * BPC * HKV),
                                smem, l.stream, p);
     stage_end(l);
     if (e != cudaSuccess) return e;
