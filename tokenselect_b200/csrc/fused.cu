@@ -16,12 +16,15 @@
 // from get_topk_tokens (:350-359); softmax + head sum (:361); max_pool1d (:366-369); topk + sort
 // (:371-372); the "+ n_init" shift (:433); init || top-k || local (:436-446); the slot gather (:448);
 // the cached-index reuse (:419) and cache write (:415); get_all_tokens (:329-330) for the dense
-// fallback; and (phase 0) what prep.cuh lists.  The tensor-parallel exchange (:363-364) splits the
-// kernel after phase 2: mode A ends with the raw votes, mode B starts from the summed votes.
+// fallback; and (phase 0) what prep.cuh lists.  The tensor-parallel exchange (:363-364) either happens
+// inside the kernel after phase 2 (every CTA flags its peers and sums their votes of its own candidates
+// over peer memory) or splits the kernel there: mode A ends with the raw votes, mode B starts from the
+// summed votes.  A prefill chunk uses the same kernel with its fingerprint as an already rotated query.
 //
 // Scoring, bf16: warp 0 stages the owned part of the request's req_to_token row in shared memory a
 // block at a time and issues one bulk asynchronous copy (TMA engine, mbarrier completion, L2
-// evict-first) per key row of hkv*256 B into a 5-stage shared-memory ring; warps 1..8 each own one
+// evict-first) per key row of hkv*256 B into a 5-stage shared-memory ring (rows of at most four KV
+// heads: eight copy warps move 16-byte cp.async pieces instead); warps 1..8 each own one
 // (16-token, kv-head) unit of a stage, read it with ldmatrix and multiply it with the head group's
 // queries on mma.sync m16n8k16 (tokens = M, query heads of the group = N <= 8, fp32 accumulate; bf16
 // products are exact in fp32).  Rows are padded by 16 B in shared memory so the eight row addresses of

@@ -1,7 +1,7 @@
-"""Drop-in surface of the reference's patcher for the decode path.
+"""Drop-in surface of the reference's patcher for the decode and chunked-prefill path.
 
 The reference monkey-patches a serving stack that is not a dependency here.  This module keeps the
-names, argument meaning and error behaviour of the pieces the decode path touches
+names, argument meaning and error behaviour of the pieces that path touches
 (patcher/token_retrieval.py):
 
 * ``patch(...)``                      -- the knob entry point (:885-921); stores module-level knobs.
