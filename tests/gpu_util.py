@@ -11,8 +11,8 @@ from tokenselect_b200 import TokenSelectConfig, TokenSelectEngine
 
 
 def make_engine(hq, hkv, d, n_init, n_local, top_k, rope_base, dtype, n_layers=1, max_ctx=None,
-                max_reqs=4, max_batch=4, max_total=None, **kw) -> TokenSelectEngine:
-    cfg = TokenSelectConfig(rope_base=rope_base, rope_scale=1.0, max_n_tokens=max_ctx or 1 << 18, top_k=top_k,
+                max_reqs=4, max_batch=4, max_total=None, rope_scale=1.0, **kw) -> TokenSelectEngine:
+    cfg = TokenSelectConfig(rope_base=rope_base, rope_scale=rope_scale, max_n_tokens=max_ctx or 1 << 18, top_k=top_k,
                             n_init=n_init, n_local=n_local, n_layers=n_layers, num_q_heads=hq, num_kv_heads=hkv,
                             head_dim=d, dtype=dtype, max_reqs=max_reqs, max_batch=max_batch,
                             max_total_tokens=max_total or (max_batch * (max_ctx or 1 << 18)), **kw)

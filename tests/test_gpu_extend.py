@@ -185,3 +185,41 @@ def test_selection_cache_across_chunks_and_decode():
             assert torch.equal(res["positions"][0, : eng.cfg.n_sel].long(), ref["positions"].long())
     assert flags == [orc.FLAG_RECOMPUTE, orc.FLAG_REUSE, orc.FLAG_RECOMPUTE]
     assert eng.counters(case.req_pool_idx) == (3, 1)
+
+
+@pytest.mark.parametrize("dtype,tol", [(BF16, 2e-2), (F32, 1e-4)], ids=["bf16", "fp32"])
+def test_rope_scale_and_soft_cap_decode_and_chunk(dtype, tol):
+    """rope_scale != 1 (scoring position n_local * scale, attention frequencies / scale) and a logit soft
+    cap, through a decode step and a prefill chunk of the same request."""
+    hq, hkv, d, n_init, n_local, top_k, base, n, lq = 8, 2, 128, 16, 64, 256, 5e5, 2500, 96
+    scale, cap = 4.0, 20.0
+    case = synth.make_layer_case(71, n, hq, hkv, d, n_init, n_local, base, rope_scale=scale, dtype=dtype)
+    eng = gu.make_engine(hq, hkv, d, n_init, n_local, top_k, base, dtype, max_ctx=n + 8, max_batch=1,
+                         rope_scale=scale, logit_cap=cap, prefill_chunk=512)
+    o = orc.DecodeOracle(gu.oracle_config(eng))
+    row = case.req_to_token[case.req_pool_idx]
+    # decode
+    out, res = gu.run_gpu(eng, 0, *gu.case_tensors(case))
+    flag, pos, info = o.select(0, case.req_pool_idx, case.q.view(hq, d), case.k_pool, row, n)
+    gu.check_selection(eng, res, 0, pos, info["votes"], n)
+    sl = res["slots"][0, : eng.cfg.n_sel]
+    want = orc.sparse_attention(case.q.view(hq, d), case.k_pool, case.v_pool, sl, d ** -0.5, base, scale, cap,
+                                torch.float64).reshape(-1)
+    assert (out[0].double() - want).abs().max().item() <= tol
+    # prefill chunk
+    dev = eng.device
+    qc = synth.make_chunk_queries(71, case, lq, hq, d)
+    dbg = eng.new_debug_buffers(1)
+    dbg["fingerprint"] = torch.zeros(hq * d, dtype=dtype, device=dev)
+    out2 = eng.extend_chunk(0, qc.to(dev), None, None, None, case.k_pool.to(dev), case.v_pool.to(dev),
+                            case.req_to_token.to(dev), case.req_pool_idx, n, debug=dbg)
+    torch.cuda.synchronize()
+    eng.raise_on_device_error()
+    res2 = {k: v.cpu() for k, v in dbg.items()}
+    assert torch.equal(res2["fingerprint"].view(hq, d), orc.chunk_fingerprint(qc.view(lq, hq, d), n_local, base, scale))
+    ref = o.extend_chunk(0, case.req_pool_idx, qc, None, None, None, case.k_pool, case.v_pool, row, n)
+    gu.check_selection(eng, res2, 0, ref["positions"], ref["info"]["votes"], n)
+    sl2 = res2["slots"][0, : eng.cfg.n_sel]
+    want2 = orc.sparse_prefill_attention(qc.view(lq, hq, d), case.k_pool, case.v_pool, sl2, d ** -0.5, base, scale, cap,
+                                         torch.float64).reshape(lq, -1)
+    assert (out2.cpu().double() - want2).abs().max().item() <= tol
