@@ -63,6 +63,8 @@ def parse_args():
                     help="diagnostic: run ONE rank's share of an N-way KV-head split on a single GPU, no exchange")
     ap.add_argument("--phase-times", action="store_true",
                     help="print the selection kernel's phase split (CTA 0 timestamps of the last launch) to stderr")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="single GPU: launch every kernel from the host instead of replaying one CUDA graph per token")
     ap.add_argument("--prefill", action="store_true",
                     help="secondary measurement: chunked prefill of one request of --ctx tokens (512-token chunks) "
                          "through ts_extend_chunk instead of the decode step")
@@ -386,20 +388,53 @@ def main():
     barrier()
     eng.raise_on_device_error()
 
+    # Single GPU: the 3 x layers launches of a token are captured once as a CUDA graph (the calls enqueue on
+    # the capturing stream, nothing in them synchronises or allocates) and replayed per token; the token's
+    # inputs are first copied into the buffers the graph was captured on.  Under tensor parallelism every
+    # call carries a fresh exchange epoch, so the kernels are launched from the host.
+    use_graph = tp == 1 and not args.no_graph
+    d_in = (hq + 2 * hkv) * D
+    sqkv = torch.empty(layers, 1, d_in, dtype=torch.bfloat16, device=dev)
+    sq, sk, sv = sqkv[..., :hq * D], sqkv[..., hq * D:(hq + hkv) * D], sqkv[..., (hq + hkv) * D:]
+    smeta = torch.zeros(2, dtype=torch.int32, device=dev)           # pool row of the new token, sequence length
+    sloc, slens = smeta[0:1], smeta[1:2]
+    launches_per_token = 3 * layers
+    graph = None
+    if use_graph:
+        qkv_all = torch.cat([qs, ks, vs], dim=-1).contiguous()       # [steps, layers, 1, d_in]
+        meta_all = torch.cat([locs_all.view(-1, 1), lens_all.view(-1, 1)], dim=1).contiguous()
+        sqkv.copy_(qkv_all[0])
+        smeta.copy_(meta_all[0])
+        c0 = eng.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for li in range(layers):
+                eng.decode_layer(li, sq[li], sk[li], sv[li], sloc, k_pools[li], v_pools[li], rtt, ridx, slens,
+                                 out=outs[li], vote_elems=ve)
+        launches_per_token = eng.launch_count - c0
+        torch.cuda.synchronize()
+
+    def run_token(i):
+        if graph is None:
+            step(i)
+        else:
+            sqkv.copy_(qkv_all[i])
+            smeta.copy_(meta_all[i])
+            graph.replay()
+
     # ---- timed region 1: inputs resident in HBM -------------------------------------------------
     sampler = ClockSampler(local_rank)
     sampler.start()
-    launches0 = eng.launch_count
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
     for i in range(args.warmup, total_steps):
-        step(i)
+        run_token(i)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
-    launches = eng.launch_count - launches0
+    launches = launches_per_token * args.steps
     eng.raise_on_device_error()
     retrievals, reuses = eng.counters(1) if args.query_cache else (0, 0)
     if tp > 1:
@@ -410,18 +445,43 @@ def main():
     # ---- timed region 2: through the same call with HOST buffers ---------------------------------
     # The caller's q | k | v of a layer sit in one pinned host block (the layout a fused QKV projection
     # produces), so a layer needs one host-to-device copy; its output goes back on a second stream as soon
-    # as the layer's kernels are done, while the next layer already runs.
+    # as the layer's kernels are done, while the next layer already runs.  Single GPU: the token's graph
+    # starts with ONE copy of the token's inputs (all layers) from the pinned block the host fills before
+    # every replay and ends with ONE copy of all layers' outputs back to pinned memory.
     qkv_pin = torch.cat([qs[args.warmup:], ks[args.warmup:], vs[args.warmup:]], dim=-1).cpu().pin_memory()
     out_pin = torch.empty(layers, 1, hq * D, dtype=torch.bfloat16).pin_memory()
-    dqkv = torch.empty(layers, 1, (hq + 2 * hkv) * D, dtype=torch.bfloat16, device=dev)
+    dqkv = torch.empty(layers, 1, d_in, dtype=torch.bfloat16, device=dev)
     dq, dk, dv = dqkv[..., :hq * D], dqkv[..., hq * D:(hq + hkv) * D], dqkv[..., (hq + hkv) * D:]
     main, side = torch.cuda.current_stream(), torch.cuda.Stream()
     done = [torch.cuda.Event() for _ in range(layers)]
+    graph2 = None
+    if use_graph:
+        in_pin = torch.empty(layers, 1, d_in, dtype=torch.bfloat16).pin_memory()
+        meta_pin = torch.zeros(2, dtype=torch.int32).pin_memory()
+        meta_cpu = meta_all.cpu()
+        in_pin.copy_(qkv_pin[0])
+        meta_pin.copy_(meta_cpu[args.warmup])
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2):
+            # the token's inputs (all layers' q | k | v, the new row and the length) in, every layer, all outputs out
+            smeta.copy_(meta_pin, non_blocking=True)
+            dqkv.copy_(in_pin, non_blocking=True)
+            for li in range(layers):
+                eng.decode_layer(li, dq[li], dk[li], dv[li], sloc, k_pools[li], v_pools[li], rtt, ridx, slens,
+                                 out=outs[li], vote_elems=ve)
+            out_pin.copy_(outs, non_blocking=True)
+        torch.cuda.synchronize()
     # rewind the request: the same tokens are appended again at the same rows
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e2.record()
     for j, i in enumerate(range(args.warmup, total_steps)):
+        if graph2 is not None:
+            in_pin.copy_(qkv_pin[j])                   # the caller's buffers of this token (host memory)
+            meta_pin.copy_(meta_cpu[i])
+            graph2.replay()
+            main.synchronize()                         # the token's result is on the host
+            continue
         for li in range(layers):
             dqkv[li].copy_(qkv_pin[j, li], non_blocking=True)
             eng.decode_layer(li, dq[li], dk[li], dv[li], locs_all[i], k_pools[li], v_pools[li], rtt, ridx,
@@ -480,7 +540,8 @@ def main():
                        "parallelism": (f"tp{tp} by KV head, votes summed "
                                        f"{'in the kernel over NVLink peer memory' if eng.fused_tp else 'by NCCL all-reduce'}")
                        if tp > 1 else "single GPU",
-                       "l2": "inputs larger than L2: each layer streams its own 268 MB of keys"},
+                       "l2": "inputs larger than L2: each layer streams its own 268 MB of keys",
+                       "launch": "one CUDA graph replay per token" if use_graph else "kernels launched from the host"},
             "us_per_layer": us_layer,
             "layer_roofline": {"bytes": ab["layer"], "achieved_gbs": ab["layer"] / (us_layer * 1e-6) / 1e9,
                                "frac_of_measured_copy": ab["layer"] / (us_layer * 1e-6) / 1e9 / peak,
