@@ -64,7 +64,7 @@ def parse_args():
     ap.add_argument("--phase-times", action="store_true",
                     help="print the selection kernel's phase split (CTA 0 timestamps of the last launch) to stderr")
     ap.add_argument("--no-graph", action="store_true",
-                    help="single GPU: launch every kernel from the host instead of replaying one CUDA graph per token")
+                    help="launch every kernel from the host instead of replaying one CUDA graph per token")
     ap.add_argument("--prefill", action="store_true",
                     help="secondary measurement: chunked prefill of one request of --ctx tokens (512-token chunks) "
                          "through ts_extend_chunk instead of the decode step")
@@ -390,9 +390,10 @@ def main():
 
     # Single GPU: the 3 x layers launches of a token are captured once as a CUDA graph (the calls enqueue on
     # the capturing stream, nothing in them synchronises or allocates) and replayed per token; the token's
-    # inputs are first copied into the buffers the graph was captured on.  Under tensor parallelism every
-    # call carries a fresh exchange epoch, so the kernels are launched from the host.
-    use_graph = tp == 1 and not args.no_graph
+    # inputs are first copied into the buffers the graph was captured on.  Under tensor parallelism this holds
+    # for the form that exchanges votes inside the kernel (the NCCL form has host-driven collectives between
+    # the calls).
+    use_graph = (tp == 1 or eng.fused_tp) and not args.no_graph
     d_in = (hq + 2 * hkv) * D
     sqkv = torch.empty(layers, 1, d_in, dtype=torch.bfloat16, device=dev)
     sq, sk, sv = sqkv[..., :hq * D], sqkv[..., hq * D:(hq + hkv) * D], sqkv[..., (hq + hkv) * D:]

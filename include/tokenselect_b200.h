@@ -223,7 +223,9 @@ int ts_tp_select_attend(ts_handle* h, const ts_decode_args* args);
  * passes the device addresses of ALL ranks' buffers, in rank order, to ts_tp_attach_peers().  After that
  * ts_decode_layer() works with tp_size > 1: each rank writes its raw votes to its own buffer, flags its
  * peers, waits (bounded) for theirs and sums the ranks' votes in rank order, so all ranks select from
- * bit-identical sums.  All ranks must issue the same sequence of calls.  Not available with the selection
+ * bit-identical sums.  All ranks must issue the same sequence of calls (the exchanges are counted on the
+ * device, per CTA; ts_tp_attach_peers() restarts the count, so after a device-side time-out every rank
+ * attaches again).  Not available with the selection
  * cache on (its cosine terms would need a second exchange): use the three ts_tp_* calls then. */
 int ts_tp_symmetric_bytes(const ts_config* cfg, size_t* bytes);
 int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count);

@@ -24,7 +24,7 @@ struct ts_handle {
     StageTimer timer;
     // tensor-parallel exchange through peer memory
     bool peers_attached;
-    unsigned tp_epoch;
+    unsigned* dev_cta_epoch;                // [grid] exchanges done, per CTA
     unsigned char* peer_base[kMaxTp];      // every rank's symmetric buffer (host copy)
     float** dev_peer_votes;                 // [2][kMaxTp] device array of pointers
     unsigned** dev_peer_flags;              // [kMaxTp]
@@ -101,6 +101,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_ts = cv.take(64 * 8);
     size_t o_pv = cv.take(2 * kMaxTp * sizeof(void*));
     size_t o_pf = cv.take(kMaxTp * sizeof(void*));
+    size_t o_ep = cv.take((size_t)grid * 4);
     size_t o_cand = cv.take((size_t)cap * 8);
     size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
     size_t o_pos = cv.take((size_t)c->max_batch * n_sel * 4);
@@ -153,6 +154,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.phase_ts = reinterpret_cast<unsigned long long*>(a + o_ts);
         h->dev_peer_votes = reinterpret_cast<float**>(a + o_pv);
         h->dev_peer_flags = reinterpret_cast<unsigned**>(a + o_pf);
+        h->dev_cta_epoch = reinterpret_cast<unsigned*>(a + o_ep);
         p.cand = reinterpret_cast<uint2*>(a + o_cand);
         p.sel_slots = reinterpret_cast<int*>(a + o_slots);
         p.sel_pos = reinterpret_cast<int*>(a + o_pos);
@@ -219,15 +221,11 @@ int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l, bool 
         if (h->cfg.kernel_size <= 0) p.votes_sel = p.votes;
     }
     if (fused_tp) {
-        // raw votes go to this rank's symmetric buffer (parity alternates per call so that a fast rank
-        // never overwrites votes a slow peer is still reading); the sum lands in the workspace
-        const unsigned epoch = ++h->tp_epoch;
-        const int parity = (int)(epoch & 1u);
-        p.epoch = epoch;
-        p.flag_parity = parity;
-        p.peer_votes = h->dev_peer_votes + parity * kMaxTp;
+        // raw votes go to this rank's peer-visible buffer (the kernel alternates between two per exchange, so
+        // that a fast rank never overwrites votes a slow peer is still reading); the sum lands in the workspace
+        p.peer_votes = h->dev_peer_votes;
         p.peer_flags = h->dev_peer_flags;
-        p.votes = reinterpret_cast<float*>(h->peer_base[h->cfg.tp_rank] + sym_votes_offset(h->cand_capacity, parity));
+        p.cta_epoch = h->dev_cta_epoch;
         p.votes_final = h->base.votes;
     }
     l.stream = reinterpret_cast<cudaStream_t>(a->stream);
@@ -411,8 +409,9 @@ int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count
     }
     TS_TRY(cudaMemcpy(h->dev_peer_votes, votes, sizeof(votes), cudaMemcpyHostToDevice), "peer table");
     TS_TRY(cudaMemcpy(h->dev_peer_flags, flags, sizeof(flags), cudaMemcpyHostToDevice), "peer table");
+    // every rank attaches at the same point of its call sequence: the exchange counts restart together
+    TS_TRY(cudaMemset(h->dev_cta_epoch, 0, (size_t)h->grid * 4), "reset exchange counts");
     h->peers_attached = true;
-    h->tp_epoch = 0;
     return TS_OK;
 }
 

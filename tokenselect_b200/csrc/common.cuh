@@ -66,10 +66,12 @@ struct LayerParams {
     unsigned* sure_count;      // [max_batch, grid] winners above the threshold bin, per CTA
     unsigned* grid_bar;        // [1] self-resetting grid barrier word
     // tensor-parallel exchange over peer memory (mode kModeTpFused)
-    float* const* peer_votes;  // [tp_size] every rank's raw-vote buffer of this call's parity (own included)
+    float* const* peer_votes;  // [2][kMaxTp] every rank's raw-vote buffer (own included), one set per parity
     unsigned* const* peer_flags;  // [tp_size] every rank's flag pad [2][tp_size][kFlagPad]
-    unsigned epoch;            // value the flags of this call carry
-    int tp_rank, flag_parity;
+    unsigned* cta_epoch;       // [grid] exchanges done so far, kept per CTA: the next one carries count + 1 in
+                               // its flags and uses the buffers of parity (count + 1) & 1; all ranks' same-numbered
+                               // CTAs count alike, and nothing on the host changes from call to call
+    int tp_rank;
     unsigned long long* phase_ts;  // [16] nanosecond timestamps of CTA 0 at the phase boundaries
     int* sel_slots;            // [max_batch, n_sel]
     int* sel_pos;              // [max_batch, n_sel]

@@ -82,6 +82,7 @@ struct FusedShared {
     unsigned long long full[kScoreStages];
     unsigned long long empty[kScoreStages];
     int idx[2][kIdxBlock];
+    unsigned epoch;                    // tensor-parallel exchange: value this launch's flags carry
 };
 
 template <int HKV>
@@ -774,7 +775,7 @@ __device__ __forceinline__ void vote_prefetch(const LayerParams& p, FusedShared&
 }
 
 __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist,
-                                           uint32_t& stage_parity, bool& dead) {
+                                           uint32_t& stage_parity, bool& dead, float* votes_raw) {
     const int tid = threadIdx.x;
     const int hq = p.hq;
     const VoteGeom g = vote_geom(p);
@@ -789,7 +790,7 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
         const float* lg = p.logits + (size_t)sh.plan.off[sg.b] * hq;
-        float* votes = p.votes + sh.plan.off[sg.b];
+        float* votes = votes_raw + sh.plan.off[sg.b];
         for (int r0 = sg.t0; r0 < sg.t1; r0 += g.cap_rows) {
             const int r1 = min(sg.t1, r0 + g.cap_rows);
             const bool first = r0 == sg.t0;
@@ -912,15 +913,17 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
     if (tid < tp && tid != me) {
         // release at system scope: the CTA's votes (ordered before this store by the barrier above) are
         // visible to the peer that observes the flag
-        unsigned* dst = p.peer_flags[tid] + ((size_t)(p.flag_parity * tp + me) * kFlagPad + blockIdx.x);
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(p.epoch) : "memory");
+        const unsigned epoch = sh.epoch;
+        const int parity = (int)(epoch & 1u);
+        unsigned* dst = p.peer_flags[tid] + ((size_t)(parity * tp + me) * kFlagPad + blockIdx.x);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
         stamp(p, 26);
-        const unsigned* src = p.peer_flags[me] + ((size_t)(p.flag_parity * tp + tid) * kFlagPad + blockIdx.x);
+        const unsigned* src = p.peer_flags[me] + ((size_t)(parity * tp + tid) * kFlagPad + blockIdx.x);
         const long long t0 = clock64();
         unsigned v = 0, spins = 0;
         while (!dead) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
-            if (v == p.epoch) break;
+            if (v == epoch) break;
             if ((++spins & 63u) == 0u && clock64() - t0 > kWaitCycles) {
                 set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + tid);
                 dead = true;
@@ -929,6 +932,7 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
     }
     __syncthreads();
     stamp(p, 25);
+    float* const* peer_votes = p.peer_votes + (sh.epoch & 1u) * kMaxTp;
     for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
     __syncthreads();
     for (int s = 0; s < sh.nseg; ++s) {
@@ -942,7 +946,7 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
 #pragma unroll
             for (int r = 0; r < kMaxTp; ++r) {
                 if (r < tp) {
-                    const float* src = p.peer_votes[r] + off + t;
+                    const float* src = peer_votes[r] + off + t;
                     asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
                                  : "=f"(x[r].x), "=f"(x[r].y), "=f"(x[r].z), "=f"(x[r].w)
                                  : "l"(src));
@@ -1257,6 +1261,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     __shared__ FusedShared sh;
     const int tid = threadIdx.x;
     bool dead = false;
+    // Tensor-parallel exchange inside this kernel: this CTA's exchange count picks the flag value and the
+    // buffer parity (a fast rank must not overwrite votes a slow peer is still reading).  Published to the
+    // CTA by the barriers that precede the first use.
+    if (mode == kModeTpFused && tid == 0) {
+        const unsigned e = p.cta_epoch[blockIdx.x] + 1u;
+        p.cta_epoch[blockIdx.x] = e;
+        sh.epoch = e;
+    }
 
     // The attention kernels that follow are launched with programmatic serialization: let them be
     // scheduled as soon as SMs free up; they wait for this grid to finish before reading anything.
@@ -1318,6 +1330,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     }
     __syncthreads();
     uint32_t stage_parity = 0;
+    // raw votes of this rank: the workspace, or (exchange inside the kernel) this rank's peer-visible buffer
+    float* votes_raw = mode == kModeTpFused ? p.peer_votes[(sh.epoch & 1u) * kMaxTp + p.tp_rank] : p.votes;
 
     const bool pooled = p.kernel_size > 0;
     stamp(p, 1);
@@ -1356,7 +1370,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         grid_barrier(p, dead);
         stamp(p, 3);
         // ---- phase 2: votes ----
-        if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead);
+        if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead, votes_raw);
         stamp(p, 4);
         if (mode == kModeTpA) return;
         if (mode == kModeTpFused) tp_exchange_phase(p, sh, ok && !pooled, dead);
