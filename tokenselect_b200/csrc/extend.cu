@@ -565,10 +565,13 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 // row exchange the row maximum through shared memory (a 128-thread named barrier per lane quarter) and
 // keep separate partial sums.  P goes back to tensor memory as packed bf16 and is the A operand of P.V.
 // Lane 0 of the issuer warp requests tiles and issues every MMA.
-constexpr int kTc5Softmax = 512;
-constexpr int kTc5Threads = kTc5Softmax + 32;
 constexpr uint32_t kTmemCols = 512, kTmemO = 128, kTmemP = 256;
-__global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const ExtendParams e) {
+// NS = threads per query row (column slices of S): 4 -> 16 columns each (512 softmax threads), 2 -> 32 columns.
+template <int NS>
+__global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(const ExtendParams e) {
+    constexpr int kTc5Softmax = 128 * NS;
+    constexpr int W = 64 / NS;                               // S columns per thread
+    constexpr int OW = 128 / NS;                             // O columns per thread
     extern __shared__ unsigned char tc5_dyn[];
     // the swizzled operand tiles need 1024-byte alignment
     Tc5Smem& sm = *reinterpret_cast<Tc5Smem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
@@ -657,12 +660,12 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
         }
     } else {
         // ---------------- softmax ----------------
-        const int cq = warp >> 2, rq = warp & 3;             // column quarter, row (lane) quarter
+        const int cq = warp >> 2, rq = warp & 3;             // column slice, row (lane) quarter
         const int r_in = rq * 32 + lane;                     // row inside the 128-row tile
         const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
-        const uint32_t t_s[2] = {tmem + lane_base + 16u * cq, tmem + lane_base + 64u + 16u * cq};
-        const uint32_t t_o = tmem + lane_base + kTmemO + 32u * cq;
-        const uint32_t t_p = tmem + lane_base + kTmemP + 8u * cq;
+        const uint32_t t_s[2] = {tmem + lane_base + (uint32_t)(W * cq), tmem + lane_base + 64u + (uint32_t)(W * cq)};
+        const uint32_t t_o = tmem + lane_base + kTmemO + (uint32_t)(OW * cq);
+        const uint32_t t_p = tmem + lane_base + kTmemP + (uint32_t)(W / 2 * cq);
         const int row = qt * 128 + r_in;
         const int lim = base_vis + row;
         const float cap = e.logit_cap;
@@ -672,33 +675,35 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
         for (int blk = 0; blk < nblk; ++blk) {
             mbar_wait(smem_u32(&sm.s_done[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 43);
             tc_fence_after();
-            float x[16];
+            float x[W];
             {
-                uint32_t r0[16];
-                tmem_ld16(t_s[blk & 1], r0);
+                uint32_t r0[W / 16][16];
+#pragma unroll
+                for (int j = 0; j < W / 16; ++j) tmem_ld16(t_s[blk & 1] + 16u * j, r0[j]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int c = 0; c < 16; ++c) x[c] = __uint_as_float(r0[c]);
+                for (int c = 0; c < W; ++c) x[c] = __uint_as_float(r0[c / 16][c % 16]);
             }
             // x keeps S in raw units unless the soft cap is on; the scale goes into the exponent's FMA
             float mx = -INFINITY;
-            const int key0 = blk * kTile + 16 * cq;
+            const int key0 = blk * kTile + W * cq;
             if (cap > 0.f) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
+                for (int c = 0; c < W; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
             }
             if (blk * kTile + kTile - 1 > base_vis + qt * 128) {      // only blocks that reach the diagonal are masked
 #pragma unroll
-                for (int c = 0; c < 16; ++c)
+                for (int c = 0; c < W; ++c)
                     if (key0 + c > lim) x[c] = -INFINITY;
             }
 #pragma unroll
-            for (int c = 0; c < 16; ++c) mx = fmaxf(mx, x[c]);
+            for (int c = 0; c < W; ++c) mx = fmaxf(mx, x[c]);
             mx *= mul;                                               // base-2 units (mul > 0)
             float* rm = &sm.rowmax[blk & 1][0][r_in];
             rm[cq * 128] = mx;
-            named_bar_sync(1 + rq, 128);                     // the four warps that share these rows
-            mx = fmaxf(fmaxf(rm[0], rm[128]), fmaxf(rm[256], rm[384]));
+            named_bar_sync(1 + rq, 32 * NS);                 // the warps that share these rows
+            mx = fmaxf(rm[0], rm[128]);
+            if (NS == 4) mx = fmaxf(mx, fmaxf(rm[256], rm[384]));
             if (blk > 0) {
                 const bool grow = mx > m_ref + 8.f;
                 if (__any_sync(0xffffffffu, grow)) {
@@ -706,12 +711,15 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
                     mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 44);
                     tc_fence_after();
                     const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
-                    uint32_t r[32];
-                    tmem_ld32(t_o, r);
-                    tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-                    tmem_st32(t_o, r);
+                    for (int j = 0; j < OW / 32; ++j) {
+                        uint32_t r[32];
+                        tmem_ld32(t_o + 32u * j, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                        tmem_st32(t_o + 32u * j, r);
+                    }
                     l_run *= corr;
                     if (grow) m_ref = mx;
                 }
@@ -719,18 +727,19 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
                 m_ref = mx == -INFINITY ? 0.f : mx;
             }
             float sum = 0.f;
-            uint32_t w[8];
+            uint32_t w[W / 16][8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
+            for (int u = 0; u < W / 2; ++u) {
                 const float p0 = ex2_fast(fmaf(x[2 * u], mul, -m_ref)), p1 = ex2_fast(fmaf(x[2 * u + 1], mul, -m_ref));
                 sum += p0 + p1;
-                w[u] = pack_bf16(p0, p1);
+                w[u / 8][u % 8] = pack_bf16(p0, p1);
             }
             if (blk >= 2) {                                  // P.V of block blk-2 has finished reading this P buffer
                 mbar_wait(smem_u32(&sm.o_done[blk & 1]), (uint32_t)(((blk - 2) >> 1) & 1), e.err, dead, 48);
                 tc_fence_after();
             }
-            tmem_st8(t_p + 32u * (blk & 1), w);
+#pragma unroll
+            for (int j = 0; j < W / 16; ++j) tmem_st8(t_p + 32u * (blk & 1) + 8u * j, w[j]);
             tmem_wait_st();
             l_run += sum;
             tc_fence_before();
@@ -740,24 +749,27 @@ __global__ void __launch_bounds__(kTc5Threads, 1) extend_attend_tc5_kernel(const
         // row sums: the four partial sums of a row share the reference maximum
         float* rs = &sm.rowmax[nblk & 1][0][r_in];
         rs[cq * 128] = l_run;
-        named_bar_sync(1 + rq, 128);
-        const float l_tot = (rs[0] + rs[128]) + (rs[256] + rs[384]);
+        named_bar_sync(1 + rq, 32 * NS);
+        const float l_tot = NS == 4 ? (rs[0] + rs[128]) + (rs[256] + rs[384]) : rs[0] + rs[128];
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
         mbar_wait(smem_u32(&sm.o_done[(nblk - 1) & 1]), (uint32_t)(((nblk - 1) >> 1) & 1), e.err, dead, 45);
         tc_fence_after();
-        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + 32 * cq;
-        uint32_t r[32];
-        tmem_ld32(t_o, r);
-        tmem_wait_ld();
-        if (row < lq) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + OW * cq;
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
-                uint4 w;
-                w.x = pack_bf16(__uint_as_float(r[c8 * 8 + 0]) * inv, __uint_as_float(r[c8 * 8 + 1]) * inv);
-                w.y = pack_bf16(__uint_as_float(r[c8 * 8 + 2]) * inv, __uint_as_float(r[c8 * 8 + 3]) * inv);
-                w.z = pack_bf16(__uint_as_float(r[c8 * 8 + 4]) * inv, __uint_as_float(r[c8 * 8 + 5]) * inv);
-                w.w = pack_bf16(__uint_as_float(r[c8 * 8 + 6]) * inv, __uint_as_float(r[c8 * 8 + 7]) * inv);
-                *reinterpret_cast<uint4*>(out + c8 * 8) = w;
+        for (int j = 0; j < OW / 32; ++j) {
+            uint32_t r[32];
+            tmem_ld32(t_o + 32u * j, r);
+            tmem_wait_ld();
+            if (row < lq) {
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint4 w;
+                    w.x = pack_bf16(__uint_as_float(r[c8 * 8 + 0]) * inv, __uint_as_float(r[c8 * 8 + 1]) * inv);
+                    w.y = pack_bf16(__uint_as_float(r[c8 * 8 + 2]) * inv, __uint_as_float(r[c8 * 8 + 3]) * inv);
+                    w.z = pack_bf16(__uint_as_float(r[c8 * 8 + 4]) * inv, __uint_as_float(r[c8 * 8 + 5]) * inv);
+                    w.w = pack_bf16(__uint_as_float(r[c8 * 8 + 6]) * inv, __uint_as_float(r[c8 * 8 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(out + 32 * j + c8 * 8) = w;
+                }
             }
         }
     }
@@ -853,9 +865,16 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     if (tc5) {
         static SmemConfig configured5 = {};
         const size_t smem5 = sizeof(Tc5Smem) + 1024;
-        err = ensure_dynamic_smem(extend_attend_tc5_kernel, smem5, configured5);
-        if (err != cudaSuccess) return err;
-        extend_attend_tc5_kernel<<<dim3(e.rows_q / 128, e.hq), kTc5Threads, smem5, l.stream>>>(e);
+        if (l.flags & TS_CFG_EXTEND_WIDE_SOFTMAX) {
+            static SmemConfig configured2 = {};
+            err = ensure_dynamic_smem(extend_attend_tc5_kernel<2>, smem5, configured2);
+            if (err != cudaSuccess) return err;
+            extend_attend_tc5_kernel<2><<<dim3(e.rows_q / 128, e.hq), 128 * 2 + 32, smem5, l.stream>>>(e);
+        } else {
+            err = ensure_dynamic_smem(extend_attend_tc5_kernel<4>, smem5, configured5);
+            if (err != cudaSuccess) return err;
+            extend_attend_tc5_kernel<4><<<dim3(e.rows_q / 128, e.hq), 128 * 4 + 32, smem5, l.stream>>>(e);
+        }
     } else if (tc) {
         static SmemConfig configured = {};
         err = ensure_dynamic_smem(extend_attend_tc_kernel, sizeof(ExtSmem), configured);

@@ -52,6 +52,7 @@ class TokenSelectConfig:
     score_path: str = "auto"               # "auto" | "direct" (keys to registers) | "staged" (bulk copies to smem)
     tp_fused: bool = True                  # tp_size > 1: sum the votes inside the kernel through peer memory
     prefill_chunk: int = 512               # PREFILL_CHUNK_SIZE (:917); 0: no prefill workspace
+    extra_flags: int = 0                   # further TS_CFG_* diagnostic bits, passed through
 
     @property
     def n_sel(self) -> int:
@@ -131,7 +132,7 @@ class TokenSelectEngine:
         c.max_reqs, c.max_batch, c.max_ctx = cfg.max_reqs, cfg.max_batch, cfg.max_n_tokens
         c.max_total_tokens = max_total
         c.tp_rank, c.tp_size = cfg.tp_rank, cfg.tp_size
-        c.flags = (_lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0) | {"auto": 0, "direct": 2, "staged": 4}[cfg.score_path]
+        c.flags = (_lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0) | {"auto": 0, "direct": 2, "staged": 4}[cfg.score_path] | int(cfg.extra_flags)
         c.prefill_chunk = int(cfg.prefill_chunk) if (cfg.tp_size == 1 or (cfg.tp_fused and not cfg.query_cache)) else 0
         c.score_cos_sin = score_cs.data_ptr()
         c.attn_cos_sin = attn_cs.data_ptr()
