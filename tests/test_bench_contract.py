@@ -1,0 +1,30 @@
+"""The bench's reference arm (CPU oracle timed on the host cores) and its byte accounting, on CPU."""
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_arm_prints_the_contract_line():
+    out = subprocess.check_output([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--ctx", "4096",
+                                   "--layers", "2", "--steps", "2", "--warmup", "1"], text=True, timeout=600)
+    line = json.loads(out.strip().splitlines()[-1])
+    for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
+                "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["impl"] == "reference" and line["unit"] == "tok/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert "workload" in line["config"]
+
+
+def test_algorithmic_bytes_of_the_headline_shape():
+    sys.path.insert(0, ROOT)
+    import bench
+    ab = bench.algorithmic_bytes(131072, 32, 8, 128)
+    # key rows + row numbers + query + index list; K and V rows of the list + row numbers + query + output
+    assert ab["select"] == 130432 * 2048 + 130432 * 4 + 32 * 128 * 2 + 2688 * 4
+    assert ab["attend"] == 2 * 2688 * 2048 + 2688 * 4 + 2 * 32 * 128 * 2
+    assert abs(ab["layer"] / 1e6 - 278.7) < 0.1
