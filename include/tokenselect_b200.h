@@ -59,7 +59,7 @@ extern "C" {
 #define TS_CFG_PLAIN_SCORE 1u     /* score with the plain-load kernel also for bf16 (diagnostic) */
 #define TS_CFG_DIRECT_SCORE 2u    /* bf16: load keys straight into mma fragments whatever the row size */
 #define TS_CFG_EXTEND_MMA_SYNC 8u /* prefill attention with mma.sync instead of tcgen05 (diagnostic) */
-#define TS_CFG_EXTEND_WIDE_SOFTMAX 16u /* prefill attention: two threads per query row instead of four (diagnostic) */
+#define TS_CFG_EXTEND_FOUR_PER_ROW 16u /* prefill attention: four threads per query row instead of two (diagnostic) */
 #define TS_CFG_STAGED_SCORE 4u    /* bf16: stage keys through shared memory by bulk copies whatever the row size */
 
 /*

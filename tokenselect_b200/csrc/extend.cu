@@ -560,10 +560,10 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// 16 softmax warps + 1 issuer warp.  Softmax thread (column quarter c = warp / 4, lane quarter w = warp % 4,
-// lane l) owns query row 32w + l and the columns [16c, 16c+16) of S, [32c, 32c+32) of O; the four threads of a
-// row exchange the row maximum through shared memory (a 128-thread named barrier per lane quarter) and
-// keep separate partial sums.  P goes back to tensor memory as packed bf16 and is the A operand of P.V.
+// 4 * NS softmax warps + 1 issuer warp (NS = 2 by default).  Softmax thread (column slice c = warp / 4, lane
+// quarter w = warp % 4, lane l) owns query row 32w + l and the columns [64c/NS, 64(c+1)/NS) of S,
+// [128c/NS, 128(c+1)/NS) of O; the NS threads of a row exchange the row maximum through shared memory (a named
+// barrier per lane quarter) and keep separate partial sums.  P goes back to tensor memory as packed bf16 and is the A operand of P.V.
 // Lane 0 of the issuer warp requests tiles and issues every MMA.
 constexpr uint32_t kTmemCols = 512, kTmemO = 128, kTmemP = 256;
 // NS = threads per query row (column slices of S): 4 -> 16 columns each (512 softmax threads), 2 -> 32 columns.
@@ -865,7 +865,7 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     if (tc5) {
         static SmemConfig configured5 = {};
         const size_t smem5 = sizeof(Tc5Smem) + 1024;
-        if (l.flags & TS_CFG_EXTEND_WIDE_SOFTMAX) {
+        if (!(l.flags & TS_CFG_EXTEND_FOUR_PER_ROW)) {
             static SmemConfig configured2 = {};
             err = ensure_dynamic_smem(extend_attend_tc5_kernel<2>, smem5, configured2);
             if (err != cudaSuccess) return err;
