@@ -25,7 +25,10 @@ from unittest import mock
 
 import torch
 
-DEFAULT_REFERENCE_ROOT = os.environ.get("TOKENSELECT_REFERENCE_ROOT", "/root/reference")
+# where the reference checkout lives: the environment variable, else a sibling "reference" directory of the repository
+DEFAULT_REFERENCE_ROOT = os.environ.get(
+    "TOKENSELECT_REFERENCE_ROOT",
+    os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 _STUBBED = [
     "sglang", "sglang.srt", "sglang.srt.managers", "sglang.srt.managers.schedule_batch",
     "sglang.srt.model_executor", "sglang.srt.model_executor.forward_batch_info",
