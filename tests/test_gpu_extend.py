@@ -223,3 +223,25 @@ def test_rope_scale_and_soft_cap_decode_and_chunk(dtype, tol):
     want2 = orc.sparse_prefill_attention(qc.view(lq, hq, d), case.k_pool, case.v_pool, sl2, d ** -0.5, base, scale, cap,
                                          torch.float64).reshape(lq, -1)
     assert (out2.cpu().double() - want2).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("flags", [8, 16], ids=["mma_sync_kernel", "four_threads_per_row"])
+def test_diagnostic_attention_variants_agree(flags):
+    """The two diagnostic variants of the prefill attention (TS_CFG_EXTEND_MMA_SYNC, TS_CFG_EXTEND_FOUR_PER_ROW)
+    against the oracle on a full chunk and a tail chunk."""
+    hq, hkv, d, n_init, n_local, top_k, base = 8, 2, 128, 16, 512, 256, 5e5
+    for seed, n, lq in ((91, 3000, 512), (92, 2100, 77)):
+        case = synth.make_layer_case(seed, n, hq, hkv, d, n_init, n_local, base, dtype=BF16)
+        qc = synth.make_chunk_queries(seed, case, lq, hq, d)
+        eng = gu.make_engine(hq, hkv, d, n_init, n_local, top_k, base, BF16, max_ctx=n + 8, max_batch=1,
+                             prefill_chunk=512, extra_flags=flags)
+        dev = eng.device
+        dbg = eng.new_debug_buffers(1)
+        out = eng.extend_chunk(0, qc.to(dev), None, None, None, case.k_pool.to(dev), case.v_pool.to(dev),
+                               case.req_to_token.to(dev), case.req_pool_idx, n, debug=dbg)
+        torch.cuda.synchronize()
+        eng.raise_on_device_error()
+        sl = dbg["slots"][0, : int(dbg["count"][0])].cpu()
+        want = orc.sparse_prefill_attention(qc.view(lq, hq, d), case.k_pool, case.v_pool, sl, d ** -0.5, base, 1.0, 0.0,
+                                            torch.float64).reshape(lq, -1)
+        assert (out.cpu().double() - want).abs().max().item() <= 2e-2
