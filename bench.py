@@ -552,9 +552,9 @@ def main():
                          "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                          "peak_source": peak_kind, "bytes_per_launch": ab["select"],
                          "us_per_launch": score_us,
-                         # dram read+write of one launch from the ncu capture in profiles/ (277.04 MB at
+                         # dram read+write of one launch from the ncu capture in profiles/ (277.37 MB at
                          # 267.70 MB algorithmic), scaled with the algorithmic bytes; single-GPU shape only
-                         "traffic": (ab["select"] * 277.04 / 267.70) if tp == 1 else None},
+                         "traffic": (ab["select"] * 277.37 / 267.70) if tp == 1 else None},
             "e2e": {"value": args.steps / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches),
