@@ -368,7 +368,8 @@ def main():
                             n_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=D, max_reqs=2, max_batch=1,
                             max_total_tokens=max_ctx, query_cache=args.query_cache,
                             similarity_threshold=args.threshold, tp_rank=rank, tp_size=tp,
-                            tp_fused=not args.tp_split, score_path=args.score_path)
+                            tp_fused=not args.tp_split, score_path=args.score_path,
+                            extra_flags=32 if args.phase_times else 0)   # TS_CFG_PHASE_STAMPS
     eng = TokenSelectEngine(cfg, device=dev)
     eng.reset_request(1)
     ve = eng.vote_elems_for([max_ctx], N_INIT, N_LOCAL)

@@ -60,6 +60,7 @@ extern "C" {
 #define TS_CFG_DIRECT_SCORE 2u    /* bf16: load keys straight into mma fragments whatever the row size */
 #define TS_CFG_EXTEND_MMA_SYNC 8u /* prefill attention with mma.sync instead of tcgen05 (diagnostic) */
 #define TS_CFG_EXTEND_FOUR_PER_ROW 16u /* prefill attention: four threads per query row instead of two (diagnostic) */
+#define TS_CFG_PHASE_STAMPS 32u   /* kernels record %globaltimer at their phase boundaries for ts_debug_read(3) (diagnostic; off: no timer reads) */
 #define TS_CFG_STAGED_SCORE 4u    /* bf16: stage keys through shared memory by bulk copies whatever the row size */
 
 /*
@@ -246,6 +247,7 @@ const char* ts_last_cuda_error(ts_handle* h);
  *            query heads paired with kv_head in ascending head order
  *          2 votes   [vote elems] fp32 (after max-pool when enabled)
  *          3 sixty-four uint64 nanosecond timestamps left by the kernels at their phase boundaries
+ *            (recorded only when ts_config.flags has TS_CFG_PHASE_STAMPS; all zero otherwise)
  *          4 per request [batch] uint32: candidates that shared the vote histogram's threshold bin
  * In 1 and 2 the requests that recomputed their scores follow each other in batch order, each
  * region starting on a multiple of 128 candidates. */

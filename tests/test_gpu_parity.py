@@ -281,3 +281,25 @@ def test_underflowing_votes(gain):
         # everything in the normal range is in
         assert set(np.nonzero(votes >= tiny)[0].tolist()) <= set(got.tolist())
     assert torch.isfinite(out.float()).all()
+
+
+def test_phase_stamps_only_with_the_diagnostic_flag():
+    """TS_CFG_PHASE_STAMPS (32): CTA 0 records nanosecond timestamps at the selection kernel's phase boundaries,
+    read back with ts_debug_read(3).  Without the flag the kernels read no timer and the slots stay zero; the
+    results are the same either way."""
+    hq, hkv, d, n_init, n_local, top_k, base, n = 8, 2, 128, 16, 64, 256, 5e5, 3000
+    case = synth.make_layer_case(97, n, hq, hkv, d, n_init, n_local, base, dtype=BF16)
+    outs = []
+    for flags in (0, 32):
+        eng = gu.make_engine(hq, hkv, d, n_init, n_local, top_k, base, BF16, max_ctx=n + 8, max_batch=1,
+                             extra_flags=flags)
+        out, dbg = gu.run_gpu(eng, 0, *gu.case_tensors(case))
+        eng.raise_on_device_error()
+        ts = eng.debug_read(3, 64, torch.int64)
+        if flags == 0:
+            assert int(ts.abs().sum()) == 0
+        else:
+            phase = ts[:9]                        # start, plan, score, barrier, vote, barrier, filter, barrier, emit
+            assert int(phase.min()) > 0 and bool((phase[1:] >= phase[:-1]).all())
+        outs.append((out, dbg["slots"]))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])

@@ -16,6 +16,7 @@ TS_DTYPE_BF16, TS_DTYPE_F32 = 0, 1
 TS_GQA_MOD, TS_GQA_DIV = 0, 1
 TS_FLAG_DENSE, TS_FLAG_RECOMPUTE, TS_FLAG_REUSE = 0, 1, 2
 TS_CFG_PLAIN_SCORE = 1
+TS_CFG_PHASE_STAMPS = 32
 TS_ABI_VERSION = 2
 
 # every symbol include/tokenselect_b200.h declares

@@ -152,6 +152,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.sure_count = reinterpret_cast<unsigned*>(a + o_sure);
         p.grid_bar = reinterpret_cast<unsigned*>(a + o_bar);
         p.phase_ts = reinterpret_cast<unsigned long long*>(a + o_ts);
+        p.stamps = (c->flags & TS_CFG_PHASE_STAMPS) ? 1 : 0;
         h->dev_peer_votes = reinterpret_cast<float**>(a + o_pv);
         h->dev_peer_flags = reinterpret_cast<unsigned**>(a + o_pf);
         h->dev_cta_epoch = reinterpret_cast<unsigned*>(a + o_ep);

@@ -84,7 +84,7 @@ __host__ __device__ inline AttnSmem attn_smem_layout(int hq, int hkv, int d, int
     return a;
 }
 
-#define ATT_STAMP(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.phase_ts[(i)] = t_; } } while (0)
+#define ATT_STAMP(i) do { if (p.stamps && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); p.phase_ts[(i)] = t_; } } while (0)
 template <typename T, int E>
 __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerParams p) {
     constexpr int D = 16 * E, HALF = 8 * E;

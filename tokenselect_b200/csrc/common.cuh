@@ -72,7 +72,8 @@ struct LayerParams {
                                // its flags and uses the buffers of parity (count + 1) & 1; all ranks' same-numbered
                                // CTAs count alike, and nothing on the host changes from call to call
     int tp_rank;
-    unsigned long long* phase_ts;  // [16] nanosecond timestamps of CTA 0 at the phase boundaries
+    unsigned long long* phase_ts;  // [64] nanosecond timestamps of CTA 0 at the phase boundaries
+    int stamps;                // record them (TS_CFG_PHASE_STAMPS); reading %globaltimer is slow, so off by default
     int* sel_slots;            // [max_batch, n_sel]
     int* sel_pos;              // [max_batch, n_sel]
     int* sel_count;            // [max_batch]

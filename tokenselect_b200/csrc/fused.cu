@@ -50,7 +50,7 @@ constexpr int kBulkMinHkv = 4;        // staged scoring: bulk copies for rows of
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // CTA 0 leaves a nanosecond timestamp at every phase boundary (read back with ts_debug_read).
 __device__ __forceinline__ void stamp(const LayerParams& p, int i) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (p.stamps && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         p.phase_ts[i] = t;
@@ -818,34 +818,47 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                 // softmax statistics of the request: merge every CTA's (max, sum exp) in two levels, each
                 // as a max pass followed by independent exponentials; head c then contributes
                 // exp2(x*log2e + bias_c) with bias_c = -(M_c*log2e + log2 L_c)
-                const int nsl = kFusedThreads / hq;                 // slices per head
+                // Each level requests all its operands before the first is used: a loop that waits for one
+                // shared-memory load per step costs more than the whole merge otherwise.
+                constexpr int kMaxSlices = 16, kPerSlice = 10;
+                const int nsl = min(kFusedThreads / hq, kMaxSlices);   // slices per head
                 const int c = tid % hq, sl = tid / hq;
                 float2* lvl = reinterpret_cast<float2*>(sh.idx);   // [nsl][hq] scratch
                 if (sl < nsl) {
-                    float m = -INFINITY;
-#pragma unroll 6
-                    for (int i = sl; i < p.grid; i += nsl) m = fmaxf(m, part_s[i * hq + c].x);
-                    float l = 0.f;
-                    if (m > -INFINITY) {
-#pragma unroll 6
-                        for (int i = sl; i < p.grid; i += nsl) {
-                            const float2 v = part_s[i * hq + c];
-                            l += v.y * ex2_approx((v.x - m) * kLog2e);
+                    float m = -INFINITY, l = 0.f;
+                    for (int i0 = sl; i0 < p.grid; i0 += nsl * kPerSlice) {   // one trip for grids up to 160 CTAs
+                        float2 v[kPerSlice];
+#pragma unroll
+                        for (int u = 0; u < kPerSlice; ++u) {
+                            const int i = i0 + u * nsl;
+                            v[u] = i < p.grid ? part_s[i * hq + c] : make_float2(-INFINITY, 0.f);
                         }
+                        float mn = m;
+#pragma unroll
+                        for (int u = 0; u < kPerSlice; ++u) mn = fmaxf(mn, v[u].x);
+                        if (mn > -INFINITY) {
+                            float acc = 0.f;
+#pragma unroll
+                            for (int u = 0; u < kPerSlice; ++u) acc += v[u].y * ex2_approx((v[u].x - mn) * kLog2e);
+                            l = l * ex2_approx((m - mn) * kLog2e) + acc;
+                        }
+                        m = mn;
                     }
                     lvl[sl * hq + c] = make_float2(m, l);
                 }
                 __syncthreads();
                 if (tid < hq) {
+                    float2 v[kMaxSlices];
+#pragma unroll
+                    for (int i = 0; i < kMaxSlices; ++i)
+                        v[i] = i < nsl ? lvl[i * hq + tid] : make_float2(-INFINITY, 0.f);
                     float m = -INFINITY;
-#pragma unroll 4
-                    for (int i = 0; i < nsl; ++i) m = fmaxf(m, lvl[i * hq + tid].x);
+#pragma unroll
+                    for (int i = 0; i < kMaxSlices; ++i) m = fmaxf(m, v[i].x);
                     float l = 0.f;
-#pragma unroll 4
-                    for (int i = 0; i < nsl; ++i) {
-                        const float2 v = lvl[i * hq + tid];
-                        if (v.x > -INFINITY) l += v.y * ex2_approx((v.x - m) * kLog2e);
-                    }
+#pragma unroll
+                    for (int i = 0; i < kMaxSlices; ++i)
+                        if (v[i].x > -INFINITY) l += v[i].y * ex2_approx((v[i].x - m) * kLog2e);
                     sh.s_m[tid] = kVoteShift - (m * kLog2e + log2f(l));
                 }
                 __syncthreads();
@@ -1276,7 +1289,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // ---- phase 0 ----
     stamp(p, 0);
     stamp(p, 52 + (p.layer & 1));
-    if (threadIdx.x == 0) {
+    if (p.stamps && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         if (blockIdx.x == 0) { p.phase_ts[9] = t; p.phase_ts[10] = t; p.phase_ts[13] = ~0ull; p.phase_ts[14] = 0ull; }
@@ -1361,7 +1374,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         }
         if (ok) vote_prefetch(p, sh, ring);
         stamp(p, 2);
-        if (threadIdx.x == 0) {
+        if (p.stamps && threadIdx.x == 0) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
             atomicMin(p.phase_ts + 13, t);
@@ -1392,7 +1405,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // ---- phase 4 ----
     if (ok) emit_phase(p, sh, ring);
     stamp(p, 8);
-    if (threadIdx.x == 0) {
+    if (p.stamps && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         atomicMax(p.phase_ts + 12, t);
