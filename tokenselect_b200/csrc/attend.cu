@@ -577,6 +577,7 @@ __global__ void __launch_bounds__(kMergeThreads) attend_merge_kernel(const Layer
     __shared__ float s_acc[NW][D];
     __shared__ float s_red[2 * NW];
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next layer's first kernel may be placed
     const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hq = p.hq;
     ATT_STAMP(48 + 2 * (p.layer & 1));

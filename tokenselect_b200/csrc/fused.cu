@@ -1274,6 +1274,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     __shared__ FusedShared sh;
     const int tid = threadIdx.x;
     bool dead = false;
+    // Launched with programmatic serialization where the runtime accepts it together with a cooperative
+    // launch: the CTAs may be placed while the previous kernel drains; nothing is read or written before it
+    // has finished (no effect under a plain launch).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // Tensor-parallel exchange inside this kernel: this CTA's exchange count picks the flag value and the
     // buffer parity (a fast rank must not overwrite votes a slow peer is still reading).  Published to the
     // CTA by the barriers that precede the first use.
@@ -1449,12 +1453,21 @@ static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mod
     cfg.blockDim = dim3(kFusedThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = l.stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    static bool overlap_ok = true;      // cleared the first time the runtime refuses the pair of attributes
+    cfg.numAttrs = overlap_ok ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, fused_select_kernel<T, HKV, DIRECT>, pp, m);
+    if (e != cudaSuccess && cfg.numAttrs == 2) {
+        (void)cudaGetLastError();
+        overlap_ok = false;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, fused_select_kernel<T, HKV, DIRECT>, pp, m);
+    }
     stage_end(l);
     return e;
 }
