@@ -97,18 +97,24 @@ struct ScoreGeom {
 
 // Self-resetting grid barrier (bounded).  Every CTA of the grid must call it the same number of
 // times.  The word returns to its start value once all have arrived: CTA 0 adds 0x80000000-(G-1), the
-// others add 1, and everyone waits for the top bit to flip.
-__device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead) {
+// others add 1, and everyone waits for the top bit to flip.  Thread 0 keeps the top bit of the current
+// generation in `gen` (read once at the start of the kernel: the bit cannot flip before this CTA has
+// arrived), so arriving is a reduction that returns nothing and the wait starts at once.
+__device__ __forceinline__ unsigned grid_barrier_generation(const LayerParams& p) {
+    return *(volatile unsigned*)p.grid_bar & 0x80000000u;
+}
+__device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead, unsigned& gen) {
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned expected = gridDim.x;
         const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (expected - 1u)) : 1u;
-        __threadfence();
-        const unsigned old = atomicAdd(p.grid_bar, add);
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.grid_bar), "r"(add) : "memory");
         if (!dead) {
             const long long t0 = clock64();
-            unsigned spins = 0;
-            while ((((old ^ *(volatile unsigned*)p.grid_bar) & 0x80000000u) == 0u)) {
+            unsigned spins = 0, v;
+            while (true) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.grid_bar) : "memory");
+                if (((v ^ gen) & 0x80000000u) != 0u) break;
                 if ((++spins & 255u) == 0u && clock64() - t0 > kWaitCycles) {
                     set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 10);
                     dead = true;
@@ -116,7 +122,7 @@ __device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead) {
                 }
             }
         }
-        __threadfence();
+        gen ^= 0x80000000u;
     }
     __syncthreads();
 }
@@ -1302,6 +1308,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // The sticky error word is requested here and looked at only after the plan's own loads have been
     // issued, so that the two round trips overlap (CTAs that prepare a request need it at once).
     const int err0 = *(volatile int*)p.err;
+    unsigned bar_gen = tid == 0 ? grid_barrier_generation(p) : 0u;   // needed at the first barrier only
     const bool need_flags_barrier = p.query_cache != 0;
     if (mode != kModeTpB) {
         for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
@@ -1309,7 +1316,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
             if (mode == kModeAll || mode == kModeTpFused) prepare_request<T, true>(p, b, sh.prep);
             else if (p.query_cache) decide_request<T>(p, b, sh.prep);
         }
-        if (need_flags_barrier) grid_barrier(p, dead);
+        if (need_flags_barrier) grid_barrier(p, dead, bar_gen);
     }
     // Flags: from the length guard alone when the selection cache is off (nothing to wait for).
     bool ok;
@@ -1384,7 +1391,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
             atomicMin(p.phase_ts + 13, t);
             atomicMax(p.phase_ts + 14, t);
         }
-        grid_barrier(p, dead);
+        grid_barrier(p, dead, bar_gen);
         stamp(p, 3);
         // ---- phase 2: votes ----
         if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead, votes_raw);
@@ -1393,18 +1400,18 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         if (mode == kModeTpFused) tp_exchange_phase(p, sh, ok && !pooled, dead);
         stamp(p, 24);
         if (pooled) {
-            grid_barrier(p, dead);
+            grid_barrier(p, dead, bar_gen);
             if (ok) hist_phase(p, sh);
         }
     } else {
         if (ok) hist_phase(p, sh);
     }
-    grid_barrier(p, dead);
+    grid_barrier(p, dead, bar_gen);
     stamp(p, 5);
     // ---- phase 3 ----
     if (ok) filter_phase(p, sh);
     stamp(p, 6);
-    grid_barrier(p, dead);
+    grid_barrier(p, dead, bar_gen);
     stamp(p, 7);
     // ---- phase 4 ----
     if (ok) emit_phase(p, sh, ring);
