@@ -111,3 +111,27 @@ def make_chunk_queries(seed: int, case: LayerCase, lq: int, hq: int, d: int, spr
     that the chunk's mean fingerprint keeps a direction (the mean of independent queries would be ~0)."""
     noise = normal(seed, 11, (lq, hq * d))
     return (case.q.float().view(1, -1) + spread * noise).to(case.q.dtype)
+
+
+@dataclasses.dataclass
+class AttentionCase:
+    """Inputs of one sparse-attention call: a request's pools plus an attended row list."""
+    q: torch.Tensor              # [Hq*D] un-rotated decode query (the last listed token's)
+    q_chunk: torch.Tensor        # [Lq, Hq*D] un-rotated queries of a prefill chunk closing the list
+    k_pool: torch.Tensor         # [rows, Hkv, D]
+    v_pool: torch.Tensor
+    slots: torch.Tensor          # [n] int32 pool rows in list order
+
+
+def make_attention_case(seed: int, n_list: int, lq: int, hq: int, hkv: int, d: int,
+                        dtype: torch.dtype = torch.bfloat16, pool_rows: Optional[int] = None) -> AttentionCase:
+    """N(0,1) pools of ``pool_rows`` rows and a list of ``n_list`` distinct rows in a seeded order (what a
+    selected index set looks like after the slot map: unordered pool rows).  ``q`` is the decode query,
+    ``q_chunk`` the ``lq`` queries of a prefill chunk whose own rows are the last ``lq`` of the list."""
+    pool_rows = pool_rows or (n_list + 97)
+    q = normal(seed, 21, (hq * d,)).to(dtype)
+    q_chunk = (q.float().view(1, -1) + 0.5 * normal(seed, 22, (max(lq, 1), hq * d))).to(dtype)
+    k_pool = normal(seed, 23, (pool_rows, hkv, d)).to(dtype)
+    v_pool = normal(seed, 24, (pool_rows, hkv, d)).to(dtype)
+    slots = permutation(seed, 25, pool_rows)[:n_list].to(torch.int32)
+    return AttentionCase(q=q, q_chunk=q_chunk, k_pool=k_pool, v_pool=v_pool, slots=slots)

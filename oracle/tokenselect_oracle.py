@@ -261,12 +261,15 @@ def sparse_prefill_attention(
     rope_scale: float = 1.0,
     logit_cap: float = 0.0,
     compute_dtype: torch.dtype = torch.float32,
+    operand_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """Causal attention of a prefill chunk over ``slots`` as the reference's third-party paged prefill
     wrapper computes it in its Llama-RoPE mode with ``causal=True`` (call site
     token_retrieval.py:746-772): with ``n`` listed keys and ``Lq`` queries, query i sits at position
     ``n - Lq + i`` and sees the listed keys ``j <= n - Lq + i``; key j is rotated at position j; the
-    rest as in :func:`sparse_attention`.  Returns ``[Lq, Hq, D]``."""
+    rest as in :func:`sparse_attention`.  Returns ``[Lq, Hq, D]``.  ``operand_dtype`` (e.g. bf16) rounds the
+    rotated queries and keys to that type before the dot products, which is what the library's tensor-core
+    prefill kernel does with bf16 inputs; ``None`` keeps them exact (the truth used for tolerances)."""
     lq, hq, d = q.shape
     hkv = k_pool.shape[1]
     group = hq // hkv
@@ -287,6 +290,9 @@ def sparse_prefill_attention(
     ks = k_pool[slots.long()].to(compute_dtype)
     vs = v_pool[slots.long()].to(compute_dtype)
     k_rot = ks * cos_k.to(compute_dtype)[:, None, :] + rotate_half(ks) * sin_k.to(compute_dtype)[:, None, :]
+    if operand_dtype is not None:
+        q_rot = q_rot.float().to(operand_dtype).to(compute_dtype)
+        k_rot = k_rot.float().to(operand_dtype).to(compute_dtype)
     visible = torch.arange(n)[None, :] <= (n - lq + torch.arange(lq))[:, None]       # [Lq, n]
     out = torch.empty((lq, hq, d), dtype=compute_dtype)
     for h in range(hq):

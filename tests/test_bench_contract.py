@@ -18,6 +18,14 @@ def test_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in line["config"]
+    # one step is one decoded token (all layers), the counts printed are the counts really run, and the
+    # workload string is the GPU arm's
+    sys.path.insert(0, ROOT)
+    import bench
+    assert line["steps"] == 2 and line["warmup"] == 1
+    assert line["config"]["workload"] == bench.workload_string(4096, 2)
+    assert abs(line["ms_per_step"] * 1e-3 * line["value"] - 1.0) < 1e-6
+    assert abs(line["us_per_layer"] * 2 - line["ms_per_step"] * 1e3) < 1e-3
 
 
 def test_algorithmic_bytes_of_the_headline_shape():
