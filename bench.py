@@ -72,6 +72,7 @@ def parse_args():
     ap.add_argument("--prefill", action="store_true",
                     help="secondary measurement: chunked prefill of one request of --ctx tokens (512-token chunks) "
                          "through ts_extend_chunk instead of the decode step")
+    ap.add_argument("--flags", type=int, default=0, help="further TS_CFG_* diagnostic bits for the engine")
     ap.add_argument("--no-check", action="store_true", help="skip the untimed check against the CPU oracle")
     ap.add_argument("--seed", type=int, default=2024)
     return ap.parse_args()
@@ -468,7 +469,7 @@ def main():
                             max_total_tokens=max_ctx, query_cache=args.query_cache,
                             similarity_threshold=args.threshold, tp_rank=rank, tp_size=tp,
                             tp_fused=not args.tp_split, score_path=args.score_path,
-                            extra_flags=32 if args.phase_times else 0)   # TS_CFG_PHASE_STAMPS
+                            extra_flags=(32 if args.phase_times else 0) | args.flags)   # TS_CFG_PHASE_STAMPS
     eng = TokenSelectEngine(cfg, device=dev)
     eng.reset_request(1)
     ve = eng.vote_elems_for([max_ctx], N_INIT, N_LOCAL)
@@ -658,13 +659,18 @@ def main():
 
     if args.phase_times:
         ts = eng.debug_read(3, 64, torch.int64).tolist()
-        names = ["prepare+plan", "score", "barrier", "vote", "barrier/exchange", "filter", "barrier", "emit"]
+        names = ["prepare+plan", "score", "barrier 1", "vote", "barrier 2/exchange", "filter", "barrier 3", "emit"]
         split = {n: (ts[i + 1] - ts[i]) / 1e3 for i, n in enumerate(names)}
         if tp > 1 and eng.fused_tp:
             split["exchange: signal sent"] = (ts[26] - ts[4]) / 1e3
             split["exchange: flags"] = (ts[25] - ts[4]) / 1e3
             split["exchange: sum"] = (ts[24] - ts[25]) / 1e3
         print(f"[rank {rank}] selection kernel phases (us): {split}", file=sys.stderr, flush=True)
+        t0 = ts[0]
+        print(f"[rank {rank}] raw stamps (us after the kernel's start, by index): "
+              f"{ {i: round((t - t0) / 1e3, 2) for i, t in enumerate(ts) if t > 0 and abs(t - t0) < 1e9} }; "
+              f"threshold-bin members of the last launch: {eng.debug_read(4, 1, torch.int32).tolist()}",
+              file=sys.stderr, flush=True)
     if rank == 0:
         ab = algorithmic_bytes(ctx + args.warmup + args.steps // 2, hq, hkv, D)
         peak, peak_kind = hbm_peak()

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define TS_ABI_VERSION 2
+#define TS_ABI_VERSION 3
 
 /* status codes */
 #define TS_OK 0
@@ -61,6 +61,7 @@ extern "C" {
 #define TS_CFG_EXTEND_MMA_SYNC 8u /* prefill attention with mma.sync instead of tcgen05 (diagnostic) */
 #define TS_CFG_EXTEND_FOUR_PER_ROW 16u /* prefill attention: four threads per query row instead of two (diagnostic) */
 #define TS_CFG_PHASE_STAMPS 32u   /* kernels record %globaltimer at their phase boundaries for ts_debug_read(3) (diagnostic; off: no timer reads) */
+#define TS_CFG_SPLIT_ATTEND 256u  /* attention in separate kernels after the selection kernel whatever the shape (diagnostic) */
 #define TS_CFG_STAGED_SCORE 4u    /* bf16: stage keys through shared memory by bulk copies whatever the row size */
 
 /*
@@ -96,6 +97,12 @@ typedef struct ts_config {
     uint32_t flags;                /* TS_CFG_* */
     int32_t prefill_chunk;         /* longest prefill chunk ts_extend_chunk() accepts (the reference uses
                                     * 512, :917); 0: no prefill workspace is allocated */
+    uint32_t wait_limit_us;        /* bound of every device-side wait (grid barriers, copy completions, the
+                                    * peers' flags of the tensor-parallel exchange) in microseconds at the
+                                    * device's nominal clock; 0: one second.  A wait that runs out sets
+                                    * TS_ERR_DEVICE_TIMEOUT and the kernel carries on to its end; while the
+                                    * error word is set every later wait of the handle gives up at once */
+    uint32_t reserved0;
     /* Optional host tables built the way RotaryEmbedding builds them (:73-96).  NULL: computed
      * by the library from rope_base / rope_scale.
      *   score_cos_sin: [head_dim/2][2] cos,sin at position n_local*rope_scale (:380-388)
@@ -226,8 +233,9 @@ int ts_tp_select_attend(ts_handle* h, const ts_decode_args* args);
  * ts_decode_layer() works with tp_size > 1: each rank writes its raw votes to its own buffer, flags its
  * peers, waits (bounded) for theirs and sums the ranks' votes in rank order, so all ranks select from
  * bit-identical sums.  All ranks must issue the same sequence of calls (the exchanges are counted on the
- * device, per CTA; ts_tp_attach_peers() restarts the count, so after a device-side time-out every rank
- * attaches again).  Not available with the selection
+ * device, per CTA, by every launch whether it ran to its end or gave up on a wait, so the ranks' counts stay
+ * aligned across a device-side time-out and nothing has to be attached again after one; a rank that creates
+ * a NEW handle must pair it with new, zero-filled buffers on every rank).  Not available with the selection
  * cache on (its cosine terms would need a second exchange): use the three ts_tp_* calls then. */
 int ts_tp_symmetric_bytes(const ts_config* cfg, size_t* bytes);
 int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count);
@@ -289,7 +297,9 @@ int ts_timing_end(ts_handle* h, double* ms_by_stage, uint64_t* launches_by_stage
  *     (each call writes every partial it later reads), but two calls whose kernels overlap on the GPU
  *     race on it -- order them on one stream or with events;
  *   - the first call on a device looks up the array's device address; make that first call before any
- *     stream capture begins;
+ *     stream capture begins, and from one thread: the per-device address table behind this call is not
+ *     guarded, so two threads making the first call on a device at the same time race on it (later calls
+ *     only read it);
  *   - `status`, if not NULL, is a device int the kernels set to TS_ERR_BAD_SLOT when a listed row lies
  *     outside [0, pool_rows) (that row is then read as row 0).
  */

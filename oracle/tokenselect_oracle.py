@@ -185,6 +185,27 @@ def cosine_terms_fixed_order(q: np.ndarray, c: np.ndarray) -> np.ndarray:
     return acc[:, 0].copy()
 
 
+def cosine_terms_fixed_order_batch(q: np.ndarray, c: np.ndarray) -> np.ndarray:
+    """:func:`cosine_terms_fixed_order` for a batch of (query, cached query) pairs ``[B, n]`` at once (same
+    order of operations per pair, hence the same bits); returns ``[B, 3]``.  Used to replay the reuse
+    decisions of many layers per step (token_retrieval.py:394-421 keeps one cached query per layer)."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    c = np.ascontiguousarray(c, dtype=np.float32)
+    assert q.shape == c.shape and q.ndim == 2 and q.shape[1] % 32 == 0
+    bsz = q.shape[0]
+    q2 = q.reshape(bsz, -1, 32)
+    c2 = c.reshape(bsz, -1, 32)
+    acc = np.zeros((3, bsz, 32), dtype=np.float32)
+    for i in range(q2.shape[1]):
+        acc[0] = acc[0] + q2[:, i] * c2[:, i]
+        acc[1] = acc[1] + q2[:, i] * q2[:, i]
+        acc[2] = acc[2] + c2[:, i] * c2[:, i]
+    lanes = np.arange(32)
+    for off in (16, 8, 4, 2, 1):
+        acc = acc + acc[:, :, lanes ^ off]
+    return np.ascontiguousarray(acc[:, :, 0].T)
+
+
 def cosine_from_terms(terms: np.ndarray) -> np.float32:
     """``dot / (sqrt(qq) * sqrt(cc))`` with every operation rounded to fp32."""
     dot, qq, cc = (np.float32(t) for t in terms)

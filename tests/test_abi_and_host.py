@@ -76,16 +76,18 @@ def test_struct_layout_matches_header():
     src = ('#include "tokenselect_b200.h"\n#include <stdio.h>\n#include <stddef.h>\n'
            'int main(){printf("%zu %zu %zu %zu %zu %zu %zu\\n", sizeof(ts_config), sizeof(ts_decode_args),'
            ' offsetof(ts_config, rope_base), offsetof(ts_decode_args, stream), sizeof(ts_extend_args),'
-           ' offsetof(ts_extend_args, chunk_cos_sin), offsetof(ts_config, prefill_chunk));return 0;}\n')
+           ' offsetof(ts_extend_args, chunk_cos_sin), offsetof(ts_config, prefill_chunk));'
+           'printf("%zu %zu\\n", offsetof(ts_config, wait_limit_us), offsetof(ts_config, score_cos_sin));return 0;}\n')
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "s.c"), "w").write(src)
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), os.path.join(d, "s.c"), "-o",
                                os.path.join(d, "s")])
-        a, b, c, e, x, y, z = map(int, subprocess.check_output([os.path.join(d, "s")]).split())
+        a, b, c, e, x, y, z, w, v = map(int, subprocess.check_output([os.path.join(d, "s")]).split())
     assert a == C.sizeof(_lib.TsConfig) and b == C.sizeof(_lib.TsDecodeArgs)
     assert c == _lib.TsConfig.rope_base.offset and e == _lib.TsDecodeArgs.stream.offset
     assert x == C.sizeof(_lib.TsExtendArgs) and y == _lib.TsExtendArgs.chunk_cos_sin.offset
     assert z == _lib.TsConfig.prefill_chunk.offset
+    assert w == _lib.TsConfig.wait_limit_us.offset and v == _lib.TsConfig.score_cos_sin.offset
 
 
 def test_rotation_tables_match_oracle_bitwise():

@@ -90,3 +90,12 @@ def test_chunk_fingerprint_fixed_order_matches_torch_mean():
     assert (a - b).abs().max().item() <= 2 ** -8 * b.abs().max().item()
     one = orc.chunk_fingerprint(q[:1], 16, 1e4, 1.0, True)
     assert torch.equal(one, orc.rotate_scoring_query(q[0], 16, 1e4, 1.0))
+
+
+def test_batched_fixed_order_cosine_terms_equal_the_single_pair_form_bitwise():
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((5, 1024)).astype(np.float32)
+    c = rng.standard_normal((5, 1024)).astype(np.float32)
+    got = orc.cosine_terms_fixed_order_batch(q, c)
+    for i in range(5):
+        assert np.array_equal(got[i], orc.cosine_terms_fixed_order(q[i], c[i]))

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtokenselect_b200.so")
+# TOKENSELECT_B200_LIB points at another build of the same sources (e.g. one compiled with diagnostic macros)
+LIB_PATH = os.environ.get("TOKENSELECT_B200_LIB") or os.path.join(HERE, "libtokenselect_b200.so")
 
 TS_OK = 0
 TS_DTYPE_BF16, TS_DTYPE_F32 = 0, 1
@@ -17,7 +18,7 @@ TS_GQA_MOD, TS_GQA_DIV = 0, 1
 TS_FLAG_DENSE, TS_FLAG_RECOMPUTE, TS_FLAG_REUSE = 0, 1, 2
 TS_CFG_PLAIN_SCORE = 1
 TS_CFG_PHASE_STAMPS = 32
-TS_ABI_VERSION = 2
+TS_ABI_VERSION = 3
 
 # every symbol include/tokenselect_b200.h declares
 EXPORTS = [
@@ -38,6 +39,7 @@ class TsConfig(C.Structure):
         ("rope_scale", C.c_double), ("sm_scale", C.c_float), ("logit_cap", C.c_float), ("max_reqs", C.c_int32),
         ("max_batch", C.c_int32), ("max_ctx", C.c_int32), ("max_total_tokens", C.c_int64),
         ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("flags", C.c_uint32), ("prefill_chunk", C.c_int32),
+        ("wait_limit_us", C.c_uint32), ("reserved0", C.c_uint32),
         ("score_cos_sin", C.c_void_p), ("attn_cos_sin", C.c_void_p),
     ]
 

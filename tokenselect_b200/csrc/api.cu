@@ -29,6 +29,7 @@ struct ts_handle {
     float** dev_peer_votes;                 // [2][kMaxTp] device array of pointers
     unsigned** dev_peer_flags;              // [kMaxTp]
     int last_batch;
+    long long wait_cycles;                  // ts_config.wait_limit_us in SM clock cycles
     // prefill chunks
     void* ext_fp; int* ext_meta; void* ext_k; void* ext_v; void* ext_q;
     int ext_rows_k, ext_rows_q;
@@ -51,6 +52,7 @@ int validate(const ts_config* c) {
     if (c->max_ctx < 1 || c->max_total_tokens < 1) return TS_ERR_INVALID_ARG;
     if (c->gqa_map != TS_GQA_MOD && c->gqa_map != TS_GQA_DIV) return TS_ERR_INVALID_ARG;
     if (c->tp_size < 1 || c->tp_rank < 0 || c->tp_rank >= c->tp_size) return TS_ERR_INVALID_ARG;
+    if (c->tp_size > kMaxTp) return TS_ERR_UNSUPPORTED;       // the peer tables hold kMaxTp ranks
     if (!(c->rope_base > 0.0) || !(c->rope_scale > 0.0)) return TS_ERR_INVALID_ARG;
     if (c->prefill_chunk < 0 || c->prefill_chunk > 4096) return TS_ERR_INVALID_ARG;
     return TS_OK;
@@ -124,6 +126,14 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_xk = cv.take(ext > 0 ? (size_t)c->hkv * rows_k * c->head_dim * elem : 16);
     size_t o_xv = cv.take(ext > 0 ? (size_t)c->hkv * rows_k * c->head_dim * elem : 16);
     size_t o_xq = cv.take(ext > 0 ? (size_t)c->hq * rows_q * c->head_dim * elem : 16);
+    // attention inside the selection kernel: per-(request, CTA) records, partials, rotation frequencies
+    const bool inl = fused_attends(c->dtype, c->flags, c->hkv, c->head_dim, c->hq / c->hkv, c->kernel_size, grid);
+    const int arows = fused_attn_rows(c->hkv);
+    const size_t pslots = inl ? (size_t)grid + (size_t)c->max_batch * (2 + (n_sel + arows - 1) / arows) : 1;
+    size_t o_rec = cv.take((size_t)c->max_batch * grid * 128);
+    size_t o_po = cv.take(pslots * hd * 4);
+    size_t o_pml = cv.take(pslots * c->hq * 8);
+    size_t o_inv = cv.take((size_t)(c->head_dim / 2) * 4);
     if (h) {
         unsigned char* a = h->arena;
         LayerParams& p = h->base;
@@ -173,6 +183,11 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.pos_cache = reinterpret_cast<int*>(a + o_pc);
         p.valid = reinterpret_cast<int*>(a + o_valid);
         p.counters = reinterpret_cast<unsigned long long*>(a + o_cnt);
+        p.attn_inline = inl ? 1 : 0;
+        p.records = reinterpret_cast<SelRecord*>(a + o_rec);
+        p.part_o = reinterpret_cast<float*>(a + o_po);
+        p.part_ml = reinterpret_cast<float2*>(a + o_pml);
+        p.attn_inv_freq = reinterpret_cast<const float*>(a + o_inv);
         h->ext_fp = a + o_xfp; h->ext_meta = reinterpret_cast<int*>(a + o_xmeta);
         h->ext_k = a + o_xk; h->ext_v = a + o_xv; h->ext_q = a + o_xq;
         h->ext_rows_k = rows_k; h->ext_rows_q = rows_q;
@@ -181,6 +196,8 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     }
     return cv.off;
 }
+
+bool n_sel_rows_ok(const ts_handle* h) { return h->n_sel >= 1; }   // the table has a row for position 1
 
 int cuda_fail(ts_handle* h, cudaError_t e, const char* what) {
     if (h) snprintf(h->cuda_msg, sizeof(h->cuda_msg), "%s: %s", what, cudaGetErrorString(e));
@@ -312,9 +329,18 @@ int ts_create(const ts_config* cfg, ts_handle** out) {
     h->cfg.score_cos_sin = nullptr;
     h->cfg.attn_cos_sin = nullptr;
     if (num_sms_of(cfg->device, &h->num_sms) != TS_OK) { delete h; return TS_ERR_CUDA; }
+    // one flag per CTA and source rank in the tensor-parallel flag pad; one record per CTA in the top-k's scratch
+    if (fused_grid_size(h->num_sms) > kFlagPad) { delete h; return TS_ERR_UNSUPPORTED; }
+    int clock_khz = 0;
+    if (cudaDeviceGetAttribute(&clock_khz, cudaDevAttrClockRate, cfg->device) != cudaSuccess || clock_khz <= 0)
+        clock_khz = 2000000;
+    h->wait_cycles = cfg->wait_limit_us ? (long long)cfg->wait_limit_us * clock_khz / 1000 : kWaitCycles;
     h->arena_bytes = layout(cfg, h->num_sms, nullptr);
     if (cudaMalloc(&h->arena, h->arena_bytes) != cudaSuccess) { delete h; return TS_ERR_CUDA; }
     layout(cfg, h->num_sms, h);
+    h->base.wait_cycles = h->wait_cycles;
+    h->base.diag_no_side = (cfg->flags & 64u) ? 1 : 0;
+    h->base.diag_plain_hist = (cfg->flags & 128u) ? 1 : 0;
     const LayerParams& p = h->base;
     const int half = cfg->head_dim / 2;
     cudaError_t e = cudaMemset(h->arena, 0, h->arena_bytes);
@@ -332,6 +358,8 @@ int ts_create(const ts_config* cfg, ts_handle** out) {
     if (e == cudaSuccess && p.attn_tc)
         e = launch_tile_order_table(p.attn_cs, const_cast<float4*>(p.attn_cs_tile), h->n_sel + 1,
                                     (h->n_sel + 1 + 15) / 16 * 2, 0);
+    if (e == cudaSuccess && n_sel_rows_ok(h))
+        e = launch_inv_freq_table(p.attn_cs, const_cast<float*>(p.attn_inv_freq), cfg->head_dim, 0);
     if (e == cudaSuccess) e = cudaDeviceSynchronize();
     if (e != cudaSuccess) { cudaFree(h->arena); delete h; return TS_ERR_CUDA; }
     *out = h;
@@ -376,6 +404,7 @@ int ts_tp_score_vote(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l);
     if (s != TS_OK) return s;
+    p.attn_inline = 0;
     TS_TRY(launch_fused(p, l, kModeTpA), "score+vote");
     return TS_OK;
 }
@@ -384,6 +413,7 @@ int ts_tp_select_attend(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l);
     if (s != TS_OK) return s;
+    p.attn_inline = 0;
     TS_TRY(launch_fused(p, l, kModeTpB), "select");
     TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);
@@ -410,8 +440,9 @@ int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count
     }
     TS_TRY(cudaMemcpy(h->dev_peer_votes, votes, sizeof(votes), cudaMemcpyHostToDevice), "peer table");
     TS_TRY(cudaMemcpy(h->dev_peer_flags, flags, sizeof(flags), cudaMemcpyHostToDevice), "peer table");
-    // every rank attaches at the same point of its call sequence: the exchange counts restart together
-    TS_TRY(cudaMemset(h->dev_cta_epoch, 0, (size_t)h->grid * 4), "reset exchange counts");
+    // The per-CTA exchange counts are NOT restarted: every launch of every rank counts, also one that gave
+    // up on a wait, so the ranks stay aligned and a flag left in a pad by an earlier exchange can never equal
+    // a later exchange's number.
     h->peers_attached = true;
     return TS_OK;
 }
@@ -427,7 +458,7 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
     int s = fill(h, a, p, l, fused_tp);
     if (s != TS_OK) return s;
     TS_TRY(launch_fused(p, l, fused_tp ? kModeTpFused : kModeAll), "select");
-    TS_TRY(launch_attend(p, l), "attend");
+    if (!p.attn_inline) TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);
 }
 
@@ -465,6 +496,7 @@ int ts_extend_chunk(ts_handle* h, const ts_extend_args* a) {
     e.rows_k = h->ext_rows_k; e.rows_q = (a->chunk_len + 127) / 128 * 128;
     e.sel_slots = h->base.sel_slots; e.sel_count = h->base.sel_count; e.attn_cs = h->base.attn_cs;
     e.err = h->base.err;
+    e.wait_cycles = h->wait_cycles;
 
     // the selection kernel sees a batch of one request whose query is the fingerprint
     ts_decode_args d;
@@ -483,6 +515,7 @@ int ts_extend_chunk(ts_handle* h, const ts_extend_args* a) {
     int s = fill(h, &d, p, l, fused_tp);
     if (s != TS_OK) return s;
     p.q_prerot = 1;
+    p.attn_inline = 0;                   // the chunk's causal attention has kernels of its own
     TS_TRY(launch_extend_prep(e, l), "extend prepare");
     TS_TRY(launch_fused(p, l, fused_tp ? kModeTpFused : kModeAll), "select");
     TS_TRY(launch_extend_attend(e, l), "extend attend");

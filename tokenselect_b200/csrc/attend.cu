@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
     ATT_STAMP(35);
     {
         bool dead = false;
-        mbar_wait(bar, 0u, p.err, dead, 20);
+        mbar_wait(bar, 0u, p.err, dead, 20, p.wait_cycles);
     }
     ATT_STAMP(36);
 
@@ -377,14 +377,6 @@ __global__ void __launch_bounds__(kAttnThreads) attend_split_kernel(const LayerP
 // values arrive by bulk asynchronous copies; key/value rows are padded by 16 bytes in shared memory so
 // that ldmatrix phases hit distinct banks.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
-    hi = pack_bf16x2(a, b);
-    lo = pack_bf16x2(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
-}
 
 // One warp per (16-row block, KV head): BPC blocks per CTA, 32 * BPC * HKV threads.  Few rows per CTA keep
 // the number of bulk copies one SM has to issue small (the copy engine issues about one per 35 ns).
@@ -470,7 +462,7 @@ __global__ void __launch_bounds__(32 * BPC * HKV) attend_split_tc_kernel(const L
     __syncthreads();
     {
         bool dead = false;
-        mbar_wait(bar, 0u, p.err, dead, 21);
+        mbar_wait(bar, 0u, p.err, dead, 21, p.wait_cycles);
     }
     ATT_STAMP(35);
     const int cntb = min(16, cnt - wb * 16);             // rows of this warp's block

@@ -9,6 +9,8 @@
 
 namespace ts {
 
+struct SelRecord;
+
 constexpr int kMaxBatch = 256;        // requests per call (plan arrays live in shared memory)
 constexpr int kMaxHq = 64;            // query heads per rank
 constexpr int kCandAlign = 128;       // each request's candidate region starts on this multiple
@@ -19,7 +21,7 @@ constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stag
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
 constexpr int kFlagPad = 256;          // per-CTA flags per (parity, source rank) in the tensor-parallel flag pad
 constexpr int kMaxTp = 8;
-constexpr int kFusedDynSmem = 174080; // dynamic shared memory of the selection kernel (5 stages of 34 KB)
+constexpr int kFusedDynSmem = 196608; // dynamic shared memory of the selection kernel (5 stages of 34 KB; the tail needs more)
 constexpr int kAttnThreads = 256;
 constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
 
@@ -93,11 +95,20 @@ struct LayerParams {
     int* valid;                // [max_reqs, n_layers]
     unsigned long long* counters;  // [max_reqs, 2] retrievals, reuses
     int* err;                  // [2] sticky (code, detail)
+    long long wait_cycles;     // bound of every device-side wait, in SM clock cycles
+    int diag_no_side, diag_plain_hist;
+    // attention inside the selection kernel
+    int attn_inline;               // 1: phases 5 and 6 run in the selection kernel, no attention kernels follow
+    struct SelRecord* records;     // [max_batch, grid] what each CTA found for each request (phase 3)
+    float* part_o;                 // [pslots, hq, d] unnormalised partial outputs, one per (request, CTA)
+    float2* part_ml;               // [pslots, hq] (max in base-2 units, sum)
+    const float* attn_inv_freq;    // [d/2] rotation frequencies of the attention positions (already / rope_scale)
 };
 
 // Per-request plan, rebuilt in shared memory by every kernel from seq_lens and flags.
 struct Plan {
     int n[kMaxBatch];          // sequence length
+    int req[kMaxBatch];        // request slot (row of req_to_token), clamped into range
     int flag[kMaxBatch];
     int nc[kMaxBatch];         // candidates scored this step (0 unless RECOMPUTE)
     int off[kMaxBatch + 1];    // start of the request's candidate region (multiple of kCandAlign)
@@ -123,15 +134,16 @@ template <bool kGuardOnly = false>
 __device__ __forceinline__ bool build_plan(const LayerParams& p, Plan& s) {
     for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
         int n = p.seq_lens[b];
+        const int req = p.req_pool_indices[b];
+        const bool bad = n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs;
         int f;
         if (kGuardOnly) {
-            const int req = p.req_pool_indices[b];
-            const bool bad = n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs;
             f = (bad || p.n_sel >= n) ? TS_FLAG_DENSE : TS_FLAG_RECOMPUTE;
         } else {
             f = __ldcg(p.flags + b);
         }
         s.n[b] = n;
+        s.req[b] = bad ? 0 : req;
         s.flag[b] = f;
         s.nc[b] = (f == TS_FLAG_RECOMPUTE) ? (n - p.n_init - p.n_local) : 0;
     }
@@ -282,6 +294,7 @@ struct ExtendParams {
     const int* sel_count;
     const float2* attn_cs;
     int* err;
+    long long wait_cycles;
 };
 
 cudaError_t launch_extend_prep(const ExtendParams& e, const Launch& l);
@@ -291,6 +304,9 @@ cudaError_t launch_prep(const LayerParams& p, const Launch& l);
 cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode);
 cudaError_t launch_attend(const LayerParams& p, const Launch& l);
 int fused_grid_size(int num_sms);
+bool fused_attends(int dtype, unsigned flags, int hkv, int d, int group, int kernel_size, int grid);
+int fused_attn_rows(int hkv);
+cudaError_t launch_inv_freq_table(const float2* attn_cs, float* inv_freq, int d, cudaStream_t stream);
 int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group);
 
 }  // namespace ts

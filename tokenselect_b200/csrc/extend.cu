@@ -311,7 +311,7 @@ __global__ void __launch_bounds__(128, 1) extend_attend_tc_kernel(const ExtendPa
         }
     }
     __syncthreads();
-    mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40);
+    mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40, e.wait_cycles);
 
     float o[2][16][4];
 #pragma unroll
@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(128, 1) extend_attend_tc_kernel(const ExtendPa
 
     for (int blk = 0; blk < nblk; ++blk) {
         const int s = blk & 1;
-        mbar_wait(smem_u32(&sm.full[s]), (uint32_t)((blk >> 1) & 1), e.err, dead, 41);
+        mbar_wait(smem_u32(&sm.full[s]), (uint32_t)((blk >> 1) & 1), e.err, dead, 41, e.wait_cycles);
         float sc[2][8][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
@@ -624,7 +624,7 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
             constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
             auto issue_qk = [&](int b) {                     // S[b&1] = Q . K_b^T
                 const int st = b % kKvStages;
-                mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42);
+                mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42, e.wait_cycles);
                 tc_fence_after();
                 const uint32_t qa = smem_u32(sm.q), ka = smem_u32(sm.k[st]);
 #pragma unroll
@@ -639,16 +639,16 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
             mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
             bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
             for (int b = 0; b < kKvStages && b < nblk; ++b) load_tile(b);
-            mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40);
+            mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40, e.wait_cycles);
             issue_qk(0);
             for (int blk = 0; blk < nblk; ++blk) {
                 if (blk + 1 < nblk) issue_qk(blk + 1);
                 if (blk > 0 && blk - 1 + kKvStages < nblk) {
                     // P.V of the previous block is complete: its stage can take the tile four blocks ahead
-                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 46);
+                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 46, e.wait_cycles);
                     load_tile(blk - 1 + kKvStages);
                 }
-                mbar_wait(smem_u32(&sm.p_ready[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 47);
+                mbar_wait(smem_u32(&sm.p_ready[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 47, e.wait_cycles);
                 tc_fence_after();
                 const uint32_t va = smem_u32(sm.v[blk % kKvStages]);
 #pragma unroll
@@ -673,7 +673,7 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
         float m_ref = 0.f, l_run = 0.f;
 
         for (int blk = 0; blk < nblk; ++blk) {
-            mbar_wait(smem_u32(&sm.s_done[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 43);
+            mbar_wait(smem_u32(&sm.s_done[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 43, e.wait_cycles);
             tc_fence_after();
             float x[W];
             {
@@ -708,7 +708,7 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
                 const bool grow = mx > m_ref + 8.f;
                 if (__any_sync(0xffffffffu, grow)) {
                     // O is rescaled in place: every P.V issued so far must be complete (they run in order)
-                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 44);
+                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 1]), (uint32_t)(((blk - 1) >> 1) & 1), e.err, dead, 44, e.wait_cycles);
                     tc_fence_after();
                     const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
 #pragma unroll
@@ -735,7 +735,7 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
                 w[u / 8][u % 8] = pack_bf16(p0, p1);
             }
             if (blk >= 2) {                                  // P.V of block blk-2 has finished reading this P buffer
-                mbar_wait(smem_u32(&sm.o_done[blk & 1]), (uint32_t)(((blk - 2) >> 1) & 1), e.err, dead, 48);
+                mbar_wait(smem_u32(&sm.o_done[blk & 1]), (uint32_t)(((blk - 2) >> 1) & 1), e.err, dead, 48, e.wait_cycles);
                 tc_fence_after();
             }
 #pragma unroll
@@ -752,7 +752,7 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
         named_bar_sync(1 + rq, 32 * NS);
         const float l_tot = NS == 4 ? (rs[0] + rs[128]) + (rs[256] + rs[384]) : rs[0] + rs[128];
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        mbar_wait(smem_u32(&sm.o_done[(nblk - 1) & 1]), (uint32_t)(((nblk - 1) >> 1) & 1), e.err, dead, 45);
+        mbar_wait(smem_u32(&sm.o_done[(nblk - 1) & 1]), (uint32_t)(((nblk - 1) >> 1) & 1), e.err, dead, 45, e.wait_cycles);
         tc_fence_after();
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + OW * cq;
 #pragma unroll

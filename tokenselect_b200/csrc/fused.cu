@@ -60,6 +60,15 @@ __device__ __forceinline__ void stamp(const LayerParams& p, int i) {
 // ------------------------------------------------------------------------------------------
 // shared state
 // ------------------------------------------------------------------------------------------
+constexpr int kOwnCap = 1536;          // a CTA's candidates whose votes and pool rows stay in shared memory
+// Shared-memory copies of the CTA's own votes and pool rows (top of the dynamic shared memory; the ring of
+// the scoring phase ends below them).
+__device__ __forceinline__ float* own_votes(unsigned char* dyn) {
+    return reinterpret_cast<float*>(dyn + kFusedDynSmem - 2 * kOwnCap * 4);
+}
+__device__ __forceinline__ int* own_slots(unsigned char* dyn) {
+    return reinterpret_cast<int*>(dyn + kFusedDynSmem - kOwnCap * 4);
+}
 struct Seg { int b, t0, t1; };        // candidates [t0, t1) of request b owned by this CTA
 
 struct FusedShared {
@@ -81,8 +90,11 @@ struct FusedShared {
     unsigned seg_above[kMaxBatch], seg_cnt[kMaxBatch];
     unsigned long long full[kScoreStages];
     unsigned long long empty[kScoreStages];
-    int idx[2][kIdxBlock];
+    __align__(16) int idx[2][kIdxBlock];   // (the tail's scratch overlays it and reads 16 bytes at a time)
     unsigned epoch;                    // tensor-parallel exchange: value this launch's flags carry
+    int seg_off[kMaxBatch];            // start of a segment in the CTA's shared-memory copies of its votes / pool rows
+    int pbase[kMaxBatch + 1];          // first attention partial of every request (see static_share)
+    int own_in_smem;                   // the CTA's candidates are few enough for those copies
 };
 
 template <int HKV>
@@ -92,7 +104,7 @@ struct ScoreGeom {
     static constexpr int kRowStride = kRowBytes + 16;       // padded row in shared memory
     static constexpr int kStageBytes = kTok * kRowStride;
     static constexpr int kRowsPerLane = (kTok + 31) / 32;
-    static_assert(kScoreStages * kStageBytes <= kFusedDynSmem, "ring must fit the dynamic shared memory");
+    static_assert(kScoreStages * kStageBytes <= kFusedDynSmem - 2 * kOwnCap * 4, "ring must fit below the own-candidate copies");
 };
 
 // Self-resetting grid barrier (bounded).  Every CTA of the grid must call it the same number of
@@ -115,10 +127,15 @@ __device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead, u
             while (true) {
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.grid_bar) : "memory");
                 if (((v ^ gen) & 0x80000000u) != 0u) break;
-                if ((++spins & 255u) == 0u && clock64() - t0 > kWaitCycles) {
-                    set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 10);
-                    dead = true;
-                    break;
+                if ((++spins & 255u) == 0u) {
+                    if (clock64() - t0 > p.wait_cycles) {
+                        set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 10);
+                        dead = true;
+                        break;
+                    }
+#ifndef TS_DIAG_NO_ERRPOLL
+                    if (*(volatile int*)p.err != 0) { dead = true; break; }
+#endif
                 }
             }
         }
@@ -184,6 +201,16 @@ __device__ __forceinline__ void find_threshold(FusedShared& sh, unsigned k) {
 
 __device__ __forceinline__ unsigned vote_bin(float v) { return (__float_as_uint(v) >> 20) & (kHistBins - 1); }
 
+// Count `bin` in a shared-memory histogram.  All 32 lanes of the warp call this together; lanes that hit the
+// same bin elect one of them to add their number (most votes of a warp fall into a handful of bins, and
+// shared-memory atomics on one address serialise).
+__device__ __forceinline__ void hist_add(unsigned* hist, unsigned bin, bool valid, bool plain = false) {
+    if (plain) { if (valid) atomicAdd(hist + bin, 1u); return; }
+    const unsigned key = valid ? bin : 0xFFFFFFFFu;
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    if (valid && (__ffs(peers) - 1) == (int)(threadIdx.x & 31)) atomicAdd(hist + bin, (unsigned)__popc(peers));
+}
+
 __device__ __forceinline__ unsigned long long cand_key(uint2 c) {
     return ((unsigned long long)(c.y & 0xFFFFFu) << 32) | (unsigned long long)(0xFFFFFFFFu - c.x);
 }
@@ -212,6 +239,36 @@ __device__ __forceinline__ T rotated_q(const LayerParams& p, const T* q, int h, 
 }
 
 // ------------------------------------------------------------------------------------------
+// Work of a layer step that the key stream does not depend on: the K/V append, the rotated scoring query
+// and cache bookkeeping of the requests this CTA prepares, the window / dense / cached parts of the index
+// sets it writes, and the empty softmax statistics it owes for requests it scores nothing of.  Run by a
+// thread group: the whole CTA, or (staged scoring) the multiplying warps while the first key rows are in
+// flight, so that the copy warps request the first key bytes as soon as the plan stands.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& sh, const ThreadGroup& tg);
+
+template <typename T>
+__device__ __forceinline__ void side_work(const LayerParams& p, FusedShared& sh, int mode, int err0, bool ok,
+                                          const ThreadGroup& tg) {
+    if (mode == kModeAll || mode == kModeTpFused) {
+        for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
+            if (err0 != 0) break;
+            prepare_request<T, true>(p, b, sh.prep, tg);
+        }
+    }
+    if (!ok) return;
+    if (mode != kModeTpA) emit_windows(p, sh, tg);
+    // a CTA without candidates of request b still owes (-inf, 0) statistics for it
+    for (int i = tg.tid; i < p.batch * p.hq; i += tg.nthr) {
+        const int b = i / p.hq, c = i - b * p.hq;
+        bool mine = false;
+        for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
+        if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
+            p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // phase 1, bf16: TMA ring + mma
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void producer_bar() { asm volatile("bar.sync 2, 256;" ::: "memory"); }
@@ -227,8 +284,9 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 // !kBulk: the eight warps that do not multiply (0 and 9..15) copy the rows in 16-byte pieces with
 // cp.async, each thread arriving on the stage's mbarrier when its pieces have landed -- right for short
 // rows, where the per-copy cost of the bulk engine would bound the rate.
-template <int HKV, bool kBulk>
-__device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShared& sh, unsigned char* ring, bool& dead) {
+template <typename T, int HKV, bool kBulk>
+__device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShared& sh, unsigned char* ring, bool& dead,
+                                                bool side, int mode, int err0) {
     using G = ScoreGeom<HKV>;
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -239,6 +297,7 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
     if (!kBulk && (warp == 0 || warp > 8)) {
         // ---------------- eight copying warps ----------------
         const int ptid = (warp == 0 ? 0 : warp - 8) * 32 + lane;         // 0..255
+        int* slot_s = own_slots(ring);
         const unsigned char* kpool = reinterpret_cast<const unsigned char*>(p.k_pool);
         const uint64_t pol = l2_evict_first_policy();
         constexpr int kChunksPerRow = HKV * 16;                           // 16-byte pieces of a key row
@@ -247,7 +306,7 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
         uint32_t phase = 0;
         for (int s = 0; s < sh.nseg; ++s) {
             const Seg sg = sh.seg[s];
-            const int* row = p.rtt + (long long)p.req_pool_indices[sg.b] * p.rtt_stride + p.n_init;
+            const int* row = p.rtt + (long long)sh.plan.req[sg.b] * p.rtt_stride + p.n_init;
             for (int tb0 = sg.t0; tb0 < sg.t1; tb0 += 2 * kIdxBlock) {
                 const int nidx = min(2 * kIdxBlock, sg.t1 - tb0);
                 int* idx = &sh.idx[0][0];
@@ -259,11 +318,12 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
                         v = 0;
                     }
                     idx[i] = v;
+                    if (sh.own_in_smem) slot_s[sh.seg_off[s] + (tb0 + i - sg.t0)] = v;
                 }
                 producer_bar();
                 for (int t0 = 0; t0 < nidx; t0 += G::kTok) {
                     const int ntok = min(G::kTok, nidx - t0);
-                    if (lane == 0) mbar_wait(smem_u32(&sh.empty[stage]), phase ^ 1u, p.err, dead, 1);
+                    if (lane == 0) mbar_wait(smem_u32(&sh.empty[stage]), phase ^ 1u, p.err, dead, 1, p.wait_cycles);
                     __syncwarp();
                     const uint32_t dst0 = ring_base + stage * G::kStageBytes;
 #pragma unroll
@@ -293,7 +353,7 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
         int buf = 0;
         for (int s = 0; s < sh.nseg; ++s) {
             const Seg sg = sh.seg[s];
-            const int* row = p.rtt + (long long)p.req_pool_indices[sg.b] * p.rtt_stride + p.n_init;
+            const int* row = p.rtt + (long long)sh.plan.req[sg.b] * p.rtt_stride + p.n_init;
             // index blocks: the next block's loads are in flight while this block's rows are issued
             int pre[kIdxBlock / 32];
             auto load_block = [&](int t_begin) {
@@ -303,7 +363,8 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
                     pre[j] = (t < sg.t1) ? __ldg(row + t) : 0;
                 }
             };
-            auto store_block = [&](int which) {
+            int* slot_s = own_slots(ring) + sh.seg_off[s] - sg.t0;
+            auto store_block = [&](int which, int t_begin) {
 #pragma unroll
                 for (int j = 0; j < kIdxBlock / 32; ++j) {
                     int v = pre[j];
@@ -312,18 +373,20 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
                         v = 0;
                     }
                     sh.idx[which][lane + 32 * j] = v;
+                    const int t = t_begin + lane + 32 * j;
+                    if (sh.own_in_smem && t < sg.t1) slot_s[t] = v;
                 }
                 __syncwarp();
             };
             load_block(sg.t0);
-            store_block(buf);
+            store_block(buf, sg.t0);
             for (int tb0 = sg.t0; tb0 < sg.t1; tb0 += kIdxBlock) {
                 const int tb1 = min(tb0 + kIdxBlock, sg.t1);
                 const bool more = tb1 < sg.t1;
                 if (more) load_block(tb1);
                 for (int t0 = tb0; t0 < tb1; t0 += G::kTok) {
                     const int ntok = min(G::kTok, sg.t1 - t0);
-                    mbar_wait(smem_u32(&sh.empty[stage]), phase ^ 1u, p.err, dead, 1);
+                    mbar_wait(smem_u32(&sh.empty[stage]), phase ^ 1u, p.err, dead, 1, p.wait_cycles);
                     const uint32_t full = smem_u32(&sh.full[stage]);
                     if (lane == 0) mbar_expect_tx(full, (uint32_t)(ntok * G::kRowBytes));
                     __syncwarp();
@@ -341,13 +404,13 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
                     last_parity_mask = (last_parity_mask & ~(1u << stage)) | (phase << stage);
                     if (++stage == kScoreStages) { stage = 0; phase ^= 1u; }
                 }
-                if (more) { buf ^= 1; store_block(buf); }
+                if (more) { buf ^= 1; store_block(buf, tb1); }
             }
         }
         // Do not leave the phase while copies into this CTA's shared memory may still be in flight.
         for (int s = 0; s < kScoreStages; ++s)
             if (issued_mask & (1u << s))
-                mbar_wait(smem_u32(&sh.full[s]), (last_parity_mask >> s) & 1u, p.err, dead, 2);
+                mbar_wait(smem_u32(&sh.full[s]), (last_parity_mask >> s) & 1u, p.err, dead, 2, p.wait_cycles);
         return;
     }
 
@@ -355,6 +418,8 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
     // ---------------- consumers: 8 warps, one (16-token, kv-head) unit each ----------------
     const int cw = warp - 1;
     const int ctid = tid - 32;
+    // the first key rows are on their way: time for the work nothing here waits for
+    if (side) side_work<T>(p, sh, mode, err0, true, ThreadGroup{ctid, 256, 1});
     const int kvh = cw % HKV;
     const int tb = cw / HKV;
     const int g = lane >> 2, t4 = lane & 3;
@@ -392,7 +457,7 @@ __device__ __forceinline__ void score_phase_tma(const LayerParams& p, FusedShare
         float* lg_base = p.logits + (size_t)sh.plan.off[sg.b] * hq + kvh * group;
         for (int t0 = sg.t0; t0 < sg.t1; t0 += G::kTok) {
             const int ntok = min(G::kTok, sg.t1 - t0);
-            mbar_wait(smem_u32(&sh.full[stage]), phase, p.err, dead, 3);
+            mbar_wait(smem_u32(&sh.full[stage]), phase, p.err, dead, 3, p.wait_cycles);
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             const uint32_t a_base = ring_base + stage * G::kStageBytes + lane_off;
 #pragma unroll
@@ -747,7 +812,7 @@ __device__ __forceinline__ VoteGeom vote_geom(const LayerParams& p) {
     g.part_bytes = ((p.grid * p.hq + 1) & ~1) * 8;
     g.bulk = (p.hq & 3) == 0;
     g.row_bytes = g.bulk ? p.hq * 4 : logit_row_stride(p.hq);
-    g.cap_rows = (kFusedDynSmem - g.part_bytes) / g.row_bytes;
+    g.cap_rows = (kFusedDynSmem - 2 * kOwnCap * 4 - g.part_bytes) / g.row_bytes;   // below the own-candidate copies
     return g;
 }
 
@@ -797,6 +862,7 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
         const Seg sg = sh.seg[s];
         const float* lg = p.logits + (size_t)sh.plan.off[sg.b] * hq;
         float* votes = votes_raw + sh.plan.off[sg.b];
+        float* votes_s = own_votes(dyn) + sh.seg_off[s] - sg.t0;     // kept for the phases that follow
         for (int r0 = sg.t0; r0 < sg.t1; r0 += g.cap_rows) {
             const int r1 = min(sg.t1, r0 + g.cap_rows);
             const bool first = r0 == sg.t0;
@@ -804,7 +870,7 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
             if (g.bulk) {
                 const bool prefetched = s == 0 && first;
                 if (tid == 0) vote_issue(p, sh, dyn, g, sg, r0, r1, !prefetched, first, !prefetched);
-                mbar_wait(smem_u32(&sh.stage_bar), stage_parity, p.err, dead, 4);
+                mbar_wait(smem_u32(&sh.stage_bar), stage_parity, p.err, dead, 4, p.wait_cycles);
                 stage_parity ^= 1u;
             } else {
                 if (first) {
@@ -883,8 +949,10 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                     bbr[k] = k < nch ? *reinterpret_cast<const float4*>(&sh.s_m[c4 * 4]) : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
                 const uint32_t rows_u32 = smem_u32(rows_s);
-                for (int t = r0 + tid; t < r1; t += kFusedThreads) {
-                    const uint32_t row = rows_u32 + (uint32_t)(t - r0) * (uint32_t)g.row_bytes;
+                for (int tb = r0; tb < r1; tb += kFusedThreads) {      // warp-uniform trip count
+                    const int t = tb + tid;
+                    const bool live = t < r1;
+                    const uint32_t row = rows_u32 + (uint32_t)((live ? t : r1 - 1) - r0) * (uint32_t)g.row_bytes;
                     float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
 #pragma unroll
                     for (int k = 0; k < 16; ++k) {
@@ -901,17 +969,25 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                         }
                     }
                     const float v = ((v0 + v1) + (v2 + v3)) * kVoteUnshift;
-                    votes[t] = v;
-                    if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+                    if (live) {
+                        votes[t] = v;
+                        if (sh.own_in_smem) votes_s[t] = v;
+                    }
+                    if (with_hist) hist_add(sh.hist, vote_bin(v), live, p.diag_plain_hist);
                 }
             } else {
-                for (int t = r0 + tid; t < r1; t += kFusedThreads) {
-                    const float* rf = reinterpret_cast<const float*>(rows_s + (size_t)(t - r0) * g.row_bytes);
+                for (int tb = r0; tb < r1; tb += kFusedThreads) {
+                    const int t = tb + tid;
+                    const bool live = t < r1;
+                    const float* rf = reinterpret_cast<const float*>(rows_s + (size_t)((live ? t : r1 - 1) - r0) * g.row_bytes);
                     float v = 0.f;
                     for (int c = 0; c < hq; ++c) v += ex2_ftz(fmaf(rf[c], kLog2e, sh.s_m[c]));
                     v *= kVoteUnshift;
-                    votes[t] = v;
-                    if (with_hist) atomicAdd(&sh.hist[vote_bin(v)], 1u);
+                    if (live) {
+                        votes[t] = v;
+                        if (sh.own_in_smem) votes_s[t] = v;
+                    }
+                    if (with_hist) hist_add(sh.hist, vote_bin(v), live, p.diag_plain_hist);
                 }
             }
         }
@@ -925,7 +1001,8 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
 // its raw votes are written, waits for theirs, and sums the ranks' votes of its own candidates in rank
 // order (so every rank gets bit-identical sums).  Replaces dist.all_reduce (token_retrieval.py:363-364).
 // All ranks run the same plan, hence the same ownership.  The wait is bounded.
-__device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedShared& sh, bool with_hist, bool& dead) {
+__device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist,
+                                                  bool& dead) {
     const int tid = threadIdx.x;
     const int tp = p.tp_size, me = p.tp_rank;
     __syncthreads();                                   // this CTA's raw votes are written
@@ -943,9 +1020,13 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
         while (!dead) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
             if (v == epoch) break;
-            if ((++spins & 63u) == 0u && clock64() - t0 > kWaitCycles) {
-                set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + tid);
-                dead = true;
+            if ((++spins & 63u) == 0u) {
+                if (clock64() - t0 > p.wait_cycles) {
+                    set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + tid);
+                    dead = true;
+                } else if (*(volatile int*)p.err != 0) {
+                    dead = true;
+                }
             }
         }
     }
@@ -958,13 +1039,16 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
         const Seg sg = sh.seg[s];
         const size_t off = (size_t)sh.plan.off[sg.b];
         float* out = p.votes_final + off;
-        for (int t = sg.t0 + 4 * tid; t < sg.t1; t += 4 * kFusedThreads) {
+        for (int tb = sg.t0; tb < sg.t1; tb += 4 * kFusedThreads) {     // warp-uniform trip count
+            const int t = tb + 4 * tid;
+            const bool live = t < sg.t1;
             // all ranks' pieces are requested before the first is used (one NVLink round trip), then
             // added in rank order
             float4 x[kMaxTp];
 #pragma unroll
             for (int r = 0; r < kMaxTp; ++r) {
-                if (r < tp) {
+                x[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < tp && live) {
                     const float* src = peer_votes[r] + off + t;
                     asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
                                  : "=f"(x[r].x), "=f"(x[r].y), "=f"(x[r].z), "=f"(x[r].w)
@@ -976,12 +1060,21 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
             for (int r = 0; r < kMaxTp; ++r) {
                 if (r < tp) { acc.x += x[r].x; acc.y += x[r].y; acc.z += x[r].z; acc.w += x[r].w; }
             }
-            *reinterpret_cast<float4*>(out + t) = acc;
+            if (live) {
+                *reinterpret_cast<float4*>(out + t) = acc;
+                if (sh.own_in_smem) {        // segments start on multiples of four inside a 128-aligned region
+                    float* vs = own_votes(dyn) + sh.seg_off[s] + (t - sg.t0);
+                    vs[0] = acc.x;
+                    if (t + 1 < sg.t1) vs[1] = acc.y;
+                    if (t + 2 < sg.t1) vs[2] = acc.z;
+                    if (t + 3 < sg.t1) vs[3] = acc.w;
+                }
+            }
             if (with_hist) {
-                atomicAdd(&sh.hist[vote_bin(acc.x)], 1u);
-                if (t + 1 < sg.t1) atomicAdd(&sh.hist[vote_bin(acc.y)], 1u);
-                if (t + 2 < sg.t1) atomicAdd(&sh.hist[vote_bin(acc.z)], 1u);
-                if (t + 3 < sg.t1) atomicAdd(&sh.hist[vote_bin(acc.w)], 1u);
+                hist_add(sh.hist, vote_bin(acc.x), live);
+                hist_add(sh.hist, vote_bin(acc.y), live && t + 1 < sg.t1);
+                hist_add(sh.hist, vote_bin(acc.z), live && t + 2 < sg.t1);
+                hist_add(sh.hist, vote_bin(acc.w), live && t + 3 < sg.t1);
             }
         }
         if (with_hist) flush_hist(p, sh, sg.b);
@@ -1100,8 +1193,8 @@ __device__ __forceinline__ void filter_phase(const LayerParams& p, FusedShared& 
 // ------------------------------------------------------------------------------------------
 // phase 4: remaining radix levels (every CTA for itself), ordered emission
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& sh) {
-    const int tid = threadIdx.x;
+__device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& sh, const ThreadGroup& tg) {
+    const int tid = tg.tid;
     const int k = p.top_k;
     // windows, dense requests and cached index sets: request b is handled by CTA grid-1 - b % grid (the
     // low-numbered CTAs prepare requests at the same time)
@@ -1117,12 +1210,12 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
         int* out_slots = p.sel_slots + (size_t)b * p.n_sel;
         int* out_pos = p.sel_pos + (size_t)b * p.n_sel;
         if (flag == TS_FLAG_DENSE) {                       // every token, position order (:329-330)
-            for (int i = tid; i < n; i += kFusedThreads) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
+            for (int i = tid; i < n; i += tg.nthr) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
             if (tid == 0) p.sel_count[b] = n;
             continue;
         }
-        for (int i = tid; i < p.n_init; i += kFusedThreads) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
-        for (int i = tid; i < p.n_local; i += kFusedThreads) {   // (:438-444)
+        for (int i = tid; i < p.n_init; i += tg.nthr) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
+        for (int i = tid; i < p.n_local; i += tg.nthr) {   // (:438-444)
             const int pos = n - p.n_local + i;
             out_pos[p.n_init + k + i] = pos;
             out_slots[p.n_init + k + i] = checked_slot(p, row, pos);
@@ -1130,7 +1223,7 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
         if (tid == 0) p.sel_count[b] = p.n_sel;
         if (flag == TS_FLAG_REUSE) {                       // cached positions (:419)
             const int* cache_pos = p.pos_cache + ((size_t)req * p.n_layers + p.layer) * k;
-            for (int i = tid; i < k; i += kFusedThreads) {
+            for (int i = tid; i < k; i += tg.nthr) {
                 const int pos = cache_pos[i];
                 out_pos[p.n_init + i] = pos;
                 out_slots[p.n_init + i] = checked_slot(p, row, pos);
@@ -1269,6 +1362,10 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
     }
 }
 
+}  // namespace ts
+#include "step_tail.cuh"
+namespace ts {
+
 // ------------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------------
@@ -1308,12 +1405,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // The sticky error word is requested here and looked at only after the plan's own loads have been
     // issued, so that the two round trips overlap (CTAs that prepare a request need it at once).
     const int err0 = *(volatile int*)p.err;
+#ifndef TS_DIAG_CONST_DEAD
+    dead = err0 != 0;                   // a handle in error waits for nothing (its kernels do nothing either)
+#endif
     unsigned bar_gen = tid == 0 ? grid_barrier_generation(p) : 0u;   // needed at the first barrier only
     const bool need_flags_barrier = p.query_cache != 0;
-    if (mode != kModeTpB) {
+    // Staged scoring with the selection cache off: the flags follow from the lengths alone, so the plan is
+    // built first and the per-request preparation runs on the multiplying warps while the first key rows
+    // are in flight (side_work).  Otherwise the preparation (and, with the cache on, a grid barrier that
+    // publishes the decisions) comes first.
+    const bool side = (HKV > 0 && !DIRECT) && !need_flags_barrier && mode != kModeTpB && !p.diag_no_side;
+    if (mode != kModeTpB && !side) {
         for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
             if (err0 != 0) break;
-            if (mode == kModeAll || mode == kModeTpFused) prepare_request<T, true>(p, b, sh.prep);
+            if (mode == kModeAll || mode == kModeTpFused) prepare_request<T, true>(p, b, sh.prep, whole_cta());
             else if (p.query_cache) decide_request<T>(p, b, sh.prep);
         }
         if (need_flags_barrier) grid_barrier(p, dead, bar_gen);
@@ -1343,6 +1448,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
             }
         }
         sh.nseg = ns;
+        // shared-memory copies of the own votes and pool rows, when the CTA's candidates are few enough
+        int own_total = 0;
+        for (int s = 0; s < ns; ++s) { sh.seg_off[s] = own_total; own_total += (sh.seg[s].t1 - sh.seg[s].t0 + 3) & ~3; }
+        sh.own_in_smem = (HKV > 0 && !DIRECT && mode != kModeTpB && own_total <= kOwnCap) ? 1 : 0;
+        // attention partials: one per (request, CTA that has a share of the request's rows)
+        int pb = 0;
+        for (int b = 0; b < p.batch; ++b) {
+            sh.pbase[b] = pb;
+            if (ok && p.attn_inline) pb += static_share(p, sh, b, AttnGeom<(HKV > 0 ? HKV : 1)>::kRows).np;
+        }
+        sh.pbase[p.batch] = pb;
         mbar_init(smem_u32(&sh.stage_bar), 1);
         if (HKV > 0) {
             for (int s = 0; s < kScoreStages; ++s) {
@@ -1362,25 +1478,48 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // Nothing recomputes (every request reuses its cached set or attends to everything): every CTA sees
     // the same empty plan, so all of them skip the scoring phases and their barriers together.  In the
     // fused tensor-parallel form the ranks decide alike for the same reason.
+    const bool nothing_to_score = sh.tile_off[p.batch] == 0;
+    // attention inside this kernel: decode steps with the tensor-core shapes (the host does not launch the
+    // attention kernels then)
+    const bool attn = (HKV > 0 && !DIRECT) && p.attn_inline != 0 && (mode == kModeAll || mode == kModeTpFused);
+    if (side && (nothing_to_score || !ok)) side_work<T>(p, sh, mode, err0, ok, whole_cta());
     // The parts of the index sets that do not depend on votes are written now, off the kernel's tail.
-    if (ok && mode != kModeTpA) emit_windows(p, sh);
-    if (sh.tile_off[p.batch] == 0) {
+    if (!side && ok && mode != kModeTpA) emit_windows(p, sh, whole_cta());
+    if (nothing_to_score) {
+        if constexpr (HKV > 0 && !DIRECT) {
+            if (attn) {
+                // no request recomputes: the lists are the cached or the complete ones; attend to them
+                __syncthreads();
+                if (tid == 0) {
+                    mbar_init(smem_u32(&tail_scratch(sh).kv_bar), 1);
+                    tail_scratch(sh).fast = 0;
+                    tail_scratch(sh).fast_b = -1;
+                    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                }
+                __syncthreads();
+                if (ok) resolve_and_attend<HKV>(p, sh, ring, true, dead);
+                grid_barrier(p, dead, bar_gen);
+                if (ok) merge_phase(p, sh);
+            }
+        }
         stamp(p, 8);
         return;
     }
     if (mode != kModeTpB) {
         // ---- phase 1: score ----
         if (ok) {
-            // a CTA without candidates of request b still owes (-inf, 0) statistics for it
-            for (int i = tid; i < p.batch * p.hq; i += kFusedThreads) {
-                const int b = i / p.hq, c = i - b * p.hq;
-                bool mine = false;
-                for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
-                if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
-                    p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
+            if (!side) {
+                // a CTA without candidates of request b still owes (-inf, 0) statistics for it
+                for (int i = tid; i < p.batch * p.hq; i += kFusedThreads) {
+                    const int b = i / p.hq, c = i - b * p.hq;
+                    bool mine = false;
+                    for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
+                    if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
+                        p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
+                }
             }
-            if constexpr (HKV > 0 && DIRECT) score_phase_direct<HKV>(p, sh);
-            else if constexpr (HKV > 0) score_phase_tma<HKV, (HKV > kBulkMinHkv)>(p, sh, ring, dead);
+            if constexpr (HKV > 0 && !DIRECT) score_phase_tma<T, HKV, (HKV > kBulkMinHkv)>(p, sh, ring, dead, side, mode, err0);
+            else if constexpr (HKV > 0) score_phase_direct<HKV>(p, sh);
             else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
         }
         if (ok) vote_prefetch(p, sh, ring);
@@ -1397,7 +1536,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead, votes_raw);
         stamp(p, 4);
         if (mode == kModeTpA) return;
-        if (mode == kModeTpFused) tp_exchange_phase(p, sh, ok && !pooled, dead);
+        if (mode == kModeTpFused) tp_exchange_phase(p, sh, ring, ok && !pooled, dead);
         stamp(p, 24);
         if (pooled) {
             grid_barrier(p, dead, bar_gen);
@@ -1408,14 +1547,31 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     }
     grid_barrier(p, dead, bar_gen);
     stamp(p, 5);
-    // ---- phase 3 ----
-    if (ok) filter_phase(p, sh);
-    stamp(p, 6);
-    grid_barrier(p, dead, bar_gen);
-    stamp(p, 7);
-    // ---- phase 4 ----
-    if (ok) emit_phase(p, sh, ring);
-    stamp(p, 8);
+    if (pooled) {
+        // max-pooled votes: the general top-k path on the pooled vote vector; attention kernels follow
+        if (ok) filter_phase(p, sh);
+        stamp(p, 6);
+        grid_barrier(p, dead, bar_gen);
+        stamp(p, 7);
+        if (ok) emit_phase(p, sh, ring);
+        stamp(p, 8);
+    } else {
+        // ---- phase 3: threshold bin, records, early request of the possible winners' rows ----
+        if (ok) classify_phase<HKV>(p, sh, ring, attn);
+        stamp(p, 6);
+        grid_barrier(p, dead, bar_gen);
+        stamp(p, 7);
+        // ---- phases 4 and 5: final set, attention over the CTA's rows ----
+        if (ok) resolve_and_attend<HKV>(p, sh, ring, attn, dead);
+        stamp(p, 8);
+        if (attn) {
+            grid_barrier(p, dead, bar_gen);
+            stamp(p, 15);
+            // ---- phase 6: merge of the partials ----
+            if (ok) merge_phase(p, sh);
+            stamp(p, 16);
+        }
+    }
     if (p.stamps && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -1438,6 +1594,13 @@ static bool use_direct(unsigned flags, int hkv) {
     (void)hkv;
     return (flags & TS_CFG_DIRECT_SCORE) != 0;
 }
+
+// The selection kernel can run the attention itself for the shapes its staged tensor-core scoring handles.
+bool fused_attends(int dtype, unsigned flags, int hkv, int d, int group, int kernel_size, int grid) {
+    return use_mma(dtype, flags, hkv, d, group) && !use_direct(flags, hkv) && kernel_size <= 0 && grid <= kMaxGrid &&
+           !(flags & TS_CFG_SPLIT_ATTEND);
+}
+int fused_attn_rows(int hkv) { return hkv >= 4 ? 32 : 64; }
 
 int fused_tile_tokens(int dtype, unsigned flags, int hkv, int d, int group) {
     if (!use_mma(dtype, flags, hkv, d, group) || use_direct(flags, hkv)) return 16;

@@ -64,12 +64,24 @@ cudaError_t launch_tile_order_table(const float2* attn_cs, float4* attn_cs_tile,
     return cudaGetLastError();
 }
 
+// Rotation frequency i of the attention positions, recovered from the table's row of position 1
+// (angle = 1 * frequency, far below pi): the in-kernel attention rotates at positions it only learns at run
+// time and evaluates cos/sin of position * frequency itself.
+__global__ void inv_freq_kernel(const float2* attn_cs, float* inv_freq, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < half) inv_freq[i] = atan2f(attn_cs[half + i].y, attn_cs[half + i].x);
+}
+cudaError_t launch_inv_freq_table(const float2* attn_cs, float* inv_freq, int d, cudaStream_t stream) {
+    inv_freq_kernel<<<1, 128, 0, stream>>>(attn_cs, inv_freq, d / 2);
+    return cudaGetLastError();
+}
+
 // grid = batch, block = 256.
 template <typename T>
 __global__ void __launch_bounds__(256) prep_kernel(const LayerParams p) {
     __shared__ PrepShared ps;
     if (*(volatile int*)p.err != 0) return;
-    prepare_request<T, false>(p, blockIdx.x, ps);
+    prepare_request<T, false>(p, blockIdx.x, ps, whole_cta());
 }
 
 cudaError_t launch_prep(const LayerParams& p, const Launch& l) {

@@ -37,11 +37,21 @@ struct PrepShared {
     float terms[3];
 };
 
-// All threads of the CTA call this for request b (uniformly).  kFusedDecide: decide and update the
+// A group of `nthr` consecutive threads of the CTA (all of them, or some of its warps) that synchronises
+// on hardware barrier `bar`; `tid` is the thread's index inside the group.
+struct ThreadGroup {
+    int tid, nthr, bar;
+    __device__ __forceinline__ void sync() const {
+        asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(nthr) : "memory");
+    }
+};
+__device__ __forceinline__ ThreadGroup whole_cta() { return ThreadGroup{(int)threadIdx.x, (int)blockDim.x, 0}; }
+
+// All threads of the group call this for request b (uniformly).  kFusedDecide: decide and update the
 // cache here; otherwise only publish the cosine terms (they are summed over ranks first).
 template <typename T, bool kFusedDecide>
-__device__ __forceinline__ void prepare_request(const LayerParams& p, int b, PrepShared& ps) {
-    const int tid = threadIdx.x;
+__device__ __forceinline__ void prepare_request(const LayerParams& p, int b, PrepShared& ps, const ThreadGroup& tg) {
+    const int tid = tg.tid;
     int& s_flag = ps.flag;
     float* s_terms = ps.terms;
 
@@ -65,11 +75,11 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         const uint4* vs = reinterpret_cast<const uint4*>(p.v_new) + (size_t)b * row_vec;
         uint4* kd = reinterpret_cast<uint4*>(p.k_pool) + (size_t)loc * row_vec;
         uint4* vd = reinterpret_cast<uint4*>(p.v_pool) + (size_t)loc * row_vec;
-        for (int i = tid; i < row_vec; i += blockDim.x) { kd[i] = ks[i]; vd[i] = vs[i]; }
+        for (int i = tid; i < row_vec; i += tg.nthr) { kd[i] = ks[i]; vd[i] = vs[i]; }
     }
 
     // 2. clear this request's first-level histogram and candidate counter
-    for (int i = tid; i < kHistBins; i += blockDim.x) p.hist[(size_t)b * kHistBins + i] = 0u;
+    for (int i = tid; i < kHistBins; i += tg.nthr) p.hist[(size_t)b * kHistBins + i] = 0u;
     if (tid == 0) p.cand_count[b] = 0u;
 
     // 3. guard (:376-378): short requests attend to everything
@@ -84,7 +94,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     const T* q = reinterpret_cast<const T*>(p.q) + (size_t)b * hd;
     T* qr = reinterpret_cast<T*>(p.q_rot) + (size_t)b * hd;
     const int half = p.d / 2;
-    for (int e = tid; e < p.hq * half; e += blockDim.x) {
+    for (int e = tid; e < p.hq * half; e += tg.nthr) {
         int h = e / half, i = e % half;
         if (p.q_prerot) {                                  // a prefill chunk's fingerprint: copy
             qr[h * p.d + i] = q[h * p.d + i];
@@ -99,7 +109,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         qr[h * p.d + i] = from_f32<T>(r1);
         qr[h * p.d + i + half] = from_f32<T>(r2);
     }
-    __syncthreads();
+    tg.sync();
 
     // 5. cosine terms against the cached query in a fixed order: lane j sums elements j + 32*i in
     //    ascending i, then an XOR butterfly (16, 8, 4, 2, 1) joins the 32 partial sums.
@@ -134,7 +144,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         if (tid == 0) p.flags[b] = TS_FLAG_RECOMPUTE;   // provisional: decide_kernel overwrites it
         return;
     }
-    __syncthreads();
+    tg.sync();
 
     // 6. decision and cache update (:395-421)
     if (tid == 0) {
@@ -142,10 +152,10 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         p.flags[b] = f;
         s_flag = f;
     }
-    __syncthreads();
+    tg.sync();
     if (p.query_cache && s_flag == TS_FLAG_RECOMPUTE) {    // query_fingerprints_cache[layer] = q (:416)
         T* fpw = reinterpret_cast<T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
-        for (int e = tid; e < hd; e += blockDim.x) fpw[e] = qr[e];
+        for (int e = tid; e < hd; e += tg.nthr) fpw[e] = qr[e];
     }
 }
 

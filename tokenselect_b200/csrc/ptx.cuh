@@ -29,16 +29,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kWaitCycles, records TS_ERR_DEVICE_TIMEOUT and lets the caller carry
-// on (control flow stays uniform so no barrier is left short of a participant).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead, int where) {
+// Bounded wait: gives up after `limit` clock cycles (or as soon as the sticky error word is set), records
+// TS_ERR_DEVICE_TIMEOUT and lets the caller carry on (control flow stays uniform so no barrier is left
+// short of a participant).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead, int where,
+                                          long long limit = kWaitCycles) {
     if (mbar_try_wait(bar, parity)) return;
     if (dead) return;
     const long long t0 = clock64();
     unsigned spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 1023u) == 0u) {
+#ifdef TS_DIAG_CONST_WAIT
             if (clock64() - t0 > kWaitCycles) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); dead = true; return; }
+#else
+            if (clock64() - t0 > limit) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); dead = true; return; }
+#endif
             if (*(volatile int*)err != 0) { dead = true; return; }
         }
     }
@@ -77,5 +83,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
         "{%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Two fp32 values as packed bf16, and as a bf16 high part plus a bf16 low part (hi + lo keeps ~16 mantissa bits).
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    hi = pack_bf16x2(a, b);
+    lo = pack_bf16x2(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xFFFF0000u));
 }
 }  // namespace ts

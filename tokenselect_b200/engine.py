@@ -53,6 +53,7 @@ class TokenSelectConfig:
     tp_fused: bool = True                  # tp_size > 1: sum the votes inside the kernel through peer memory
     prefill_chunk: int = 512               # PREFILL_CHUNK_SIZE (:917); 0: no prefill workspace
     extra_flags: int = 0                   # further TS_CFG_* diagnostic bits, passed through
+    wait_limit_us: int = 0                 # bound of every device-side wait in microseconds; 0: one second
 
     @property
     def n_sel(self) -> int:
@@ -134,6 +135,7 @@ class TokenSelectEngine:
         c.tp_rank, c.tp_size = cfg.tp_rank, cfg.tp_size
         c.flags = (_lib.TS_CFG_PLAIN_SCORE if cfg.plain_score else 0) | {"auto": 0, "direct": 2, "staged": 4}[cfg.score_path] | int(cfg.extra_flags)
         c.prefill_chunk = int(cfg.prefill_chunk) if (cfg.tp_size == 1 or (cfg.tp_fused and not cfg.query_cache)) else 0
+        c.wait_limit_us = int(cfg.wait_limit_us)
         c.score_cos_sin = score_cs.data_ptr()
         c.attn_cos_sin = attn_cs.data_ptr()
         self._c = c
@@ -164,10 +166,8 @@ class TokenSelectEngine:
         if not dist.is_available() or not dist.is_initialized():
             return
         import torch.distributed._symmetric_memory as symm_mem
-        nbytes = C.c_size_t()
-        check(self.lib.ts_tp_symmetric_bytes(C.byref(self._c), C.byref(nbytes)), "ts_tp_symmetric_bytes")
         group = self.group if self.group is not None else dist.group.WORLD
-        self._symm = symm_mem.empty(nbytes.value, dtype=torch.uint8, device=self.device)
+        self._symm = symm_mem.empty(self.symmetric_bytes(), dtype=torch.uint8, device=self.device)
         self._symm.zero_()
         handle = symm_mem.rendezvous(self._symm, group)
         ptrs = [int(x) for x in handle.buffer_ptrs]
@@ -175,9 +175,20 @@ class TokenSelectEngine:
             raise RuntimeError("symmetric-memory group does not match tp_rank / tp_size")
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                 # every buffer is zeroed before anyone raises a flag
-        arr = (C.c_uint64 * len(ptrs))(*ptrs)
-        check(self.lib.ts_tp_attach_peers(self._h, arr, len(ptrs)), "ts_tp_attach_peers", self._h)
+        self.attach_peer_buffers(ptrs)
         self._symm_handle = handle
+
+    def symmetric_bytes(self) -> int:
+        """Bytes of peer-visible, zero-filled memory every rank provides for the in-kernel vote exchange."""
+        nbytes = C.c_size_t()
+        check(self.lib.ts_tp_symmetric_bytes(C.byref(self._c), C.byref(nbytes)), "ts_tp_symmetric_bytes")
+        return nbytes.value
+
+    def attach_peer_buffers(self, ptrs: Sequence[int]) -> None:
+        """Hand the library the device addresses of ALL ranks' exchange buffers, in rank order
+        (``ts_tp_attach_peers``); from then on ``decode_layer`` sums the votes inside the selection kernel."""
+        arr = (C.c_uint64 * len(ptrs))(*[int(x) for x in ptrs])
+        check(self.lib.ts_tp_attach_peers(self._h, arr, len(ptrs)), "ts_tp_attach_peers", self._h)
         self.fused_tp = True
 
     # ------------------------------------------------------------------------------------------
@@ -421,6 +432,15 @@ def attend_rows_static(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
     supplied by the caller for the same reason.  At most ``4 MiB / (heads * (head_dim + 2) * 4)`` chunks
     of 32 rows; calls that overlap on the GPU race on the shared array, so keep them on one stream."""
     lib = _lib.load()
+    if rows.dtype != torch.int32 or not rows.is_cuda or not rows.is_contiguous():
+        raise ValueError("rows must be a contiguous CUDA int32 tensor")       # int64 rows would be read as (value, 0) pairs
+    for name, t in (("q", q), ("k_pool", k_pool), ("v_pool", v_pool), ("out", out)):
+        if not t.is_cuda or not t.is_contiguous() or t.dtype != q.dtype:
+            raise ValueError(f"{name}: expected a contiguous CUDA tensor of {q.dtype}")
+    if q.dtype not in (torch.bfloat16, torch.float32) or k_pool.dim() != 3 or k_pool.shape != v_pool.shape:
+        raise ValueError("q must be bf16 or fp32; pools must be [rows, num_kv_heads, head_dim] of equal shape")
+    if status is not None and (status.dtype != torch.int32 or not status.is_cuda):
+        raise ValueError("status must be a CUDA int32 tensor")
     hq = q.numel() // k_pool.shape[2]
     a = _lib.TsAttendStaticArgs()
     a.struct_size = C.sizeof(_lib.TsAttendStaticArgs)
