@@ -658,9 +658,14 @@ def main():
     eng.raise_on_device_error()
 
     if args.phase_times:
-        ts = eng.debug_read(3, 64, torch.int64).tolist()
-        names = ["prepare+plan", "score", "barrier 1", "vote", "barrier 2/exchange", "filter", "barrier 3", "emit"]
-        split = {n: (ts[i + 1] - ts[i]) / 1e3 for i, n in enumerate(names)}
+        ts = eng.debug_read(3, 128, torch.int64).tolist()
+        # stamp indices of the selection kernel: 0 start, 1 plan, 2 scoring done, 3 barrier passed, 4 votes done,
+        # 24 exchange done, 5 barrier passed, 6 classified (records out, rows requested), 7 barrier passed,
+        # 8 set final + own rows attended, 15 barrier passed, 16 partials merged
+        marks = [("plan", 0, 1), ("score", 1, 2), ("barrier 1", 2, 3), ("vote", 3, 4), ("exchange", 4, 24),
+                 ("barrier 2", 24, 5), ("classify", 5, 6), ("barrier 3", 6, 7), ("resolve+attend", 7, 8),
+                 ("barrier 4", 8, 15), ("merge", 15, 16)]
+        split = {n: (ts[j] - ts[i]) / 1e3 for n, i, j in marks if ts[i] > 0 and ts[j] > 0}
         if tp > 1 and eng.fused_tp:
             split["exchange: signal sent"] = (ts[26] - ts[4]) / 1e3
             split["exchange: flags"] = (ts[25] - ts[4]) / 1e3

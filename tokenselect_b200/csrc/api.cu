@@ -100,7 +100,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_ccount = cv.take((size_t)c->max_batch * 4);
     size_t o_sure = cv.take((size_t)c->max_batch * grid * 4);
     size_t o_bar = cv.take(16);
-    size_t o_ts = cv.take(64 * 8);
+    size_t o_ts = cv.take(128 * 8);
     size_t o_pv = cv.take(2 * kMaxTp * sizeof(void*));
     size_t o_pf = cv.take(kMaxTp * sizeof(void*));
     size_t o_ep = cv.take((size_t)grid * 4);
@@ -563,7 +563,7 @@ int ts_debug_read(ts_handle* h, int32_t which, void* host_dst, size_t bytes) {
         case 0: src = p.q_rot; avail = (size_t)h->cfg.max_batch * hd * h->elem; break;
         case 1: src = p.logits; avail = (size_t)h->cand_capacity * h->cfg.hq * 4; break;
         case 2: src = p.votes_sel; avail = (size_t)h->cand_capacity * 4; break;
-        case 3: src = p.phase_ts; avail = 64 * 8; break;
+        case 3: src = p.phase_ts; avail = 128 * 8; break;
         case 4: src = p.cand_count; avail = (size_t)h->cfg.max_batch * 4; break;
         default: return TS_ERR_INVALID_ARG;
     }

@@ -105,6 +105,8 @@ struct LayerParams {
     const float* attn_inv_freq;    // [d/2] rotation frequencies of the attention positions (already / rope_scale)
 };
 
+static_assert(sizeof(LayerParams) % 4 == 0 && sizeof(LayerParams) / 4 <= kFusedThreads, "one word of the parameters per thread");
+
 // Per-request plan, rebuilt in shared memory by every kernel from seq_lens and flags.
 struct Plan {
     int n[kMaxBatch];          // sequence length
@@ -132,6 +134,7 @@ __host__ __device__ __forceinline__ int pooled_len(int nc, int kernel_size) {
 // the flags a previous phase wrote.
 template <bool kGuardOnly = false>
 __device__ __forceinline__ bool build_plan(const LayerParams& p, Plan& s) {
+#pragma unroll 1
     for (int b = threadIdx.x; b < p.batch; b += blockDim.x) {
         int n = p.seq_lens[b];
         const int req = p.req_pool_indices[b];
@@ -150,6 +153,7 @@ __device__ __forceinline__ bool build_plan(const LayerParams& p, Plan& s) {
     __syncthreads();
     if (threadIdx.x < 32) {
         int carry = 0;
+#pragma unroll 1
         for (int base = 0; base < p.batch; base += 32) {
             int b = base + threadIdx.x;
             int v = (b < p.batch) ? ((s.nc[b] + kCandAlign - 1) / kCandAlign) * kCandAlign : 0;

@@ -49,12 +49,44 @@ constexpr int kBulkMinHkv = 4;        // staged scoring: bulk copies for rows of
 
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // CTA 0 leaves a nanosecond timestamp at every phase boundary (read back with ts_debug_read).
-__device__ __forceinline__ void stamp(const LayerParams& p, int i) {
-    if (p.stamps && blockIdx.x == 0 && threadIdx.x == 0) {
+// (Out of line: with the stamps off, a stamp site must cost the kernel next to no instruction bytes.)
+__device__ __noinline__ void stamp_slow(unsigned long long* ts, int i) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        p.phase_ts[i] = t;
+        ts[i] = t;
     }
+}
+// Earliest / latest CTA at the kernel's start (0), at the end of scoring (1) and at the kernel's end (2).
+__device__ __noinline__ void stamp_range_slow(unsigned long long* ts, int which) {
+    if (threadIdx.x != 0) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    if (which == 0) {
+        if (blockIdx.x == 0) { ts[9] = t; ts[10] = t; ts[13] = ~0ull; ts[14] = 0ull; }
+        else atomicMin(ts + 11, t);
+    } else if (which == 1) {
+        atomicMin(ts + 13, t);
+        atomicMax(ts + 14, t);
+    } else {
+        atomicMax(ts + 12, t);
+    }
+}
+__device__ __forceinline__ void stamp(const LayerParams& p, int i) {
+    if (p.stamps) stamp_slow(p.phase_ts, i);
+}
+
+// Finer stamps of one ordinary CTA (CTA 1; CTA 0 also prepares the request): thread 0 at index 64 + i, a thread
+// of another warp group at 96 + i.
+__device__ __noinline__ void fstamp_slow(unsigned long long* ts, int i) {
+    if (blockIdx.x == 1 && (threadIdx.x == 0 || threadIdx.x == 256)) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        ts[(threadIdx.x == 0 ? 64 : 96) + i] = t;
+    }
+}
+__device__ __forceinline__ void fstamp(const LayerParams& p, int i) {
+    if (p.stamps) fstamp_slow(p.phase_ts, i);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -95,7 +127,16 @@ struct FusedShared {
     int seg_off[kMaxBatch];            // start of a segment in the CTA's shared-memory copies of its votes / pool rows
     int pbase[kMaxBatch + 1];          // first attention partial of every request (see static_share)
     int own_in_smem;                   // the CTA's candidates are few enough for those copies
+    unsigned tq, tr;                   // tiles per CTA: the first `tr` CTAs own tq + 1 tiles, the others tq
 };
+
+// Work tiles are dealt out in contiguous ranges, as evenly as 32-bit arithmetic makes easy: CTA c owns tiles
+// [tile_lo(c), tile_lo(c + 1)).
+__device__ __forceinline__ unsigned tile_lo(const FusedShared& sh, unsigned c) { return c * sh.tq + min(c, sh.tr); }
+__device__ __forceinline__ int tile_owner(const FusedShared& sh, unsigned T) {
+    const unsigned big = sh.tr * (sh.tq + 1u);
+    return (int)(T < big ? T / (sh.tq + 1u) : sh.tr + (T - big) / sh.tq);
+}
 
 template <int HKV>
 struct ScoreGeom {
@@ -115,37 +156,39 @@ struct ScoreGeom {
 __device__ __forceinline__ unsigned grid_barrier_generation(const LayerParams& p) {
     return *(volatile unsigned*)p.grid_bar & 0x80000000u;
 }
+// The arrival and the bounded poll, out of line (one copy for the kernel's five barriers).  Returns true
+// when the wait was given up.
+__device__ __noinline__ bool grid_barrier_poll(unsigned* bar, int* err, long long limit, unsigned gen, bool skip_wait) {
+    const unsigned expected = gridDim.x;
+    const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (expected - 1u)) : 1u;
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(bar), "r"(add) : "memory");
+    if (skip_wait) return true;
+    const long long t0 = clock64();
+    unsigned spins = 0, v;
+    while (true) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bar) : "memory");
+        if (((v ^ gen) & 0x80000000u) != 0u) return false;
+        if ((++spins & 255u) == 0u) {
+            if (clock64() - t0 > limit) {
+                set_error(err, TS_ERR_DEVICE_TIMEOUT, 10);
+                return true;
+            }
+            if (*(volatile int*)err != 0) return true;
+        }
+    }
+}
 __device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead, unsigned& gen) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned expected = gridDim.x;
-        const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (expected - 1u)) : 1u;
-        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.grid_bar), "r"(add) : "memory");
-        if (!dead) {
-            const long long t0 = clock64();
-            unsigned spins = 0, v;
-            while (true) {
-                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p.grid_bar) : "memory");
-                if (((v ^ gen) & 0x80000000u) != 0u) break;
-                if ((++spins & 255u) == 0u) {
-                    if (clock64() - t0 > p.wait_cycles) {
-                        set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 10);
-                        dead = true;
-                        break;
-                    }
-#ifndef TS_DIAG_NO_ERRPOLL
-                    if (*(volatile int*)p.err != 0) { dead = true; break; }
-#endif
-                }
-            }
-        }
+        dead = grid_barrier_poll(p.grid_bar, p.err, p.wait_cycles, gen, dead);
         gen ^= 0x80000000u;
     }
     __syncthreads();
 }
 
+// Inclusive prefix sum over the CTA's threads (three CTA barriers inside); out of line, one copy per width.
 template <typename U>
-__device__ __forceinline__ U block_inclusive_scan(U v, U* warp_sum) {
+__device__ __noinline__ U block_inclusive_scan(U v, U* warp_sum) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     U inc = v;
 #pragma unroll
@@ -173,7 +216,7 @@ __device__ __forceinline__ U block_inclusive_scan(U v, U* warp_sum) {
 
 // Given a 2048-bin histogram in shared memory, find the bin holding the k-th largest key (bins
 // counted from the top), the number of keys in higher bins and the bin's own count.
-__device__ __forceinline__ void find_threshold(FusedShared& sh, unsigned k) {
+__device__ __noinline__ void find_threshold(FusedShared& sh, unsigned k) {
     const int tid = threadIdx.x;
     constexpr int kPer = 8;            // 256 threads x 8 bins
     unsigned c[kPer];
@@ -250,7 +293,11 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
 template <typename T>
 __device__ __forceinline__ void side_work(const LayerParams& p, FusedShared& sh, int mode, int err0, bool ok,
                                           const ThreadGroup& tg) {
+#ifdef SZ_NO_SIDE
+    return;
+#endif
     if (mode == kModeAll || mode == kModeTpFused) {
+#pragma unroll 1
         for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
             if (err0 != 0) break;
             prepare_request<T, true>(p, b, sh.prep, tg);
@@ -259,9 +306,11 @@ __device__ __forceinline__ void side_work(const LayerParams& p, FusedShared& sh,
     if (!ok) return;
     if (mode != kModeTpA) emit_windows(p, sh, tg);
     // a CTA without candidates of request b still owes (-inf, 0) statistics for it
+#pragma unroll 1
     for (int i = tg.tid; i < p.batch * p.hq; i += tg.nthr) {
         const int b = i / p.hq, c = i - b * p.hq;
         bool mine = false;
+#pragma unroll 1
         for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
         if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
             p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
@@ -772,6 +821,7 @@ __device__ __forceinline__ void load_vote_batch(const LayerParams& p, const floa
 __device__ __forceinline__ void flush_hist(const LayerParams& p, FusedShared& sh, int b) {
     __syncthreads();
     unsigned* gh = p.hist + (size_t)b * kHistBins;
+#pragma unroll 1
     for (int i = threadIdx.x; i < kHistBins; i += kFusedThreads) {
         const unsigned c = sh.hist[i];
         if (c) { atomicAdd(gh + i, c); sh.hist[i] = 0u; }
@@ -828,6 +878,7 @@ __device__ __forceinline__ void vote_issue(const LayerParams& p, FusedShared& sh
         const unsigned char* src =
             reinterpret_cast<const unsigned char*>(p.logits + ((size_t)sh.plan.off[sg.b] + r0) * p.hq);
         const uint32_t dst = smem_u32(dyn + g.part_bytes);
+#pragma unroll 1
         for (uint32_t o = 0; o < row_total; o += 32768u)
             bulk_g2s(dst + o, src + o, min(32768u, row_total - o), bar);
     }
@@ -886,6 +937,7 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
             }
             __syncthreads();
             stamp(p, 20);
+            fstamp(p, 0);
             if (first) {
                 // softmax statistics of the request: merge every CTA's (max, sum exp) in two levels, each
                 // as a max pass followed by independent exponentials; head c then contributes
@@ -936,6 +988,7 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
                 __syncthreads();
             }
             stamp(p, 21);
+            fstamp(p, 1);
             if (g.bulk && nch <= 16) {
                 // Rows are unpadded: every thread starts at a different 16-byte chunk so that eight
                 // consecutive threads hit distinct banks (chunk counts that are not a power of two are
@@ -992,8 +1045,10 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
             }
         }
         stamp(p, 22);
+        fstamp(p, 2);
         if (with_hist) flush_hist(p, sh, sg.b);
         stamp(p, 23);
+        fstamp(p, 3);
     }
 }
 
@@ -1198,6 +1253,7 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
     const int k = p.top_k;
     // windows, dense requests and cached index sets: request b is handled by CTA grid-1 - b % grid (the
     // low-numbered CTAs prepare requests at the same time)
+#pragma unroll 1
     for (int b = (int)(gridDim.x - 1 - blockIdx.x); b < p.batch; b += gridDim.x) {
         const int n = sh.plan.n[b];
         const int flag = sh.plan.flag[b];
@@ -1210,11 +1266,14 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
         int* out_slots = p.sel_slots + (size_t)b * p.n_sel;
         int* out_pos = p.sel_pos + (size_t)b * p.n_sel;
         if (flag == TS_FLAG_DENSE) {                       // every token, position order (:329-330)
+#pragma unroll 1
             for (int i = tid; i < n; i += tg.nthr) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
             if (tid == 0) p.sel_count[b] = n;
             continue;
         }
+#pragma unroll 1
         for (int i = tid; i < p.n_init; i += tg.nthr) { out_pos[i] = i; out_slots[i] = checked_slot(p, row, i); }
+#pragma unroll 1
         for (int i = tid; i < p.n_local; i += tg.nthr) {   // (:438-444)
             const int pos = n - p.n_local + i;
             out_pos[p.n_init + k + i] = pos;
@@ -1223,6 +1282,7 @@ __device__ __forceinline__ void emit_windows(const LayerParams& p, FusedShared& 
         if (tid == 0) p.sel_count[b] = p.n_sel;
         if (flag == TS_FLAG_REUSE) {                       // cached positions (:419)
             const int* cache_pos = p.pos_cache + ((size_t)req * p.n_layers + p.layer) * k;
+#pragma unroll 1
             for (int i = tid; i < k; i += tg.nthr) {
                 const int pos = cache_pos[i];
                 out_pos[p.n_init + i] = pos;
@@ -1366,6 +1426,44 @@ __device__ __forceinline__ void emit_phase(const LayerParams& p, FusedShared& sh
 #include "step_tail.cuh"
 namespace ts {
 
+// Thread 0: which candidates this CTA owns (contiguous tiles), where their shared-memory copies start, and the
+// attention partials of every request.  `own_copies`: the scoring path fills the shared-memory copies.
+__device__ __forceinline__ void plan_ownership(const LayerParams& p, FusedShared& sh, bool ok, bool own_copies, int attn_rows,
+                                               bool attn) {
+    const int tt = p.tile_tokens;
+    int acc = 0;
+#pragma unroll 1
+    for (int b = 0; b < p.batch; ++b) { sh.tile_off[b] = acc; acc += (sh.plan.nc[b] + tt - 1) / tt; }
+    sh.tile_off[p.batch] = acc;
+    sh.tq = (unsigned)acc / gridDim.x;
+    sh.tr = (unsigned)acc % gridDim.x;
+    const int lo = (int)tile_lo(sh, blockIdx.x), hi = (int)tile_lo(sh, blockIdx.x + 1u);
+    int ns = 0, own_total = 0;
+#pragma unroll 1
+    for (int b = 0; b < p.batch && ok; ++b) {
+        const int a0 = max(lo, sh.tile_off[b]), a1 = min(hi, sh.tile_off[b + 1]);
+        if (a0 < a1) {
+            sh.seg[ns].b = b;
+            sh.seg[ns].t0 = (a0 - sh.tile_off[b]) * tt;
+            sh.seg[ns].t1 = min(sh.plan.nc[b], (a1 - sh.tile_off[b]) * tt);
+            // shared-memory copies of the own votes and pool rows, when the CTA's candidates are few enough
+            sh.seg_off[ns] = own_total;
+            own_total += (sh.seg[ns].t1 - sh.seg[ns].t0 + 3) & ~3;
+            ++ns;
+        }
+    }
+    sh.nseg = ns;
+    sh.own_in_smem = (own_copies && own_total <= kOwnCap) ? 1 : 0;
+    // attention partials: one per (request, CTA that has a share of the request's rows)
+    int pb = 0;
+#pragma unroll 1
+    for (int b = 0; b < p.batch; ++b) {
+        sh.pbase[b] = pb;
+        if (ok && attn) pb += static_share(p, sh, b, attn_rows).np;
+    }
+    sh.pbase[p.batch] = pb;
+}
+
 // ------------------------------------------------------------------------------------------
 // the kernel
 // ------------------------------------------------------------------------------------------
@@ -1396,12 +1494,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // ---- phase 0 ----
     stamp(p, 0);
     stamp(p, 52 + (p.layer & 1));
-    if (p.stamps && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        if (blockIdx.x == 0) { p.phase_ts[9] = t; p.phase_ts[10] = t; p.phase_ts[13] = ~0ull; p.phase_ts[14] = 0ull; }
-        else atomicMin(p.phase_ts + 11, t);
-    }
+    if (p.stamps) stamp_range_slow(p.phase_ts, 0);
     // The sticky error word is requested here and looked at only after the plan's own loads have been
     // issued, so that the two round trips overlap (CTAs that prepare a request need it at once).
     const int err0 = *(volatile int*)p.err;
@@ -1415,6 +1508,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // are in flight (side_work).  Otherwise the preparation (and, with the cache on, a grid barrier that
     // publishes the decisions) comes first.
     const bool side = (HKV > 0 && !DIRECT) && !need_flags_barrier && mode != kModeTpB && !p.diag_no_side;
+#ifndef SZ_NO_PREP
     if (mode != kModeTpB && !side) {
         for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
             if (err0 != 0) break;
@@ -1423,42 +1517,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
         }
         if (need_flags_barrier) grid_barrier(p, dead, bar_gen);
     }
+#endif
     // Flags: from the length guard alone when the selection cache is off (nothing to wait for).
     bool ok;
+#ifndef SZ_NO_PLAN
     if (need_flags_barrier || mode == kModeTpB) ok = build_plan<false>(p, sh.plan);
     else ok = build_plan<true>(p, sh.plan);
+#else
+    ok = true;
+#endif
     ok = ok && err0 == 0;
 
     // ---- ownership: contiguous tile range per CTA ----
     if (tid == 0) {
-        const int tt = p.tile_tokens;
-        int acc = 0;
-        for (int b = 0; b < p.batch; ++b) { sh.tile_off[b] = acc; acc += (sh.plan.nc[b] + tt - 1) / tt; }
-        sh.tile_off[p.batch] = acc;
-        const long long total = acc;
-        const int lo = (int)(total * blockIdx.x / gridDim.x), hi = (int)(total * (blockIdx.x + 1) / gridDim.x);
-        int ns = 0;
-        for (int b = 0; b < p.batch && ok; ++b) {
-            const int a0 = max(lo, sh.tile_off[b]), a1 = min(hi, sh.tile_off[b + 1]);
-            if (a0 < a1) {
-                sh.seg[ns].b = b;
-                sh.seg[ns].t0 = (a0 - sh.tile_off[b]) * tt;
-                sh.seg[ns].t1 = min(sh.plan.nc[b], (a1 - sh.tile_off[b]) * tt);
-                ++ns;
-            }
-        }
-        sh.nseg = ns;
-        // shared-memory copies of the own votes and pool rows, when the CTA's candidates are few enough
-        int own_total = 0;
-        for (int s = 0; s < ns; ++s) { sh.seg_off[s] = own_total; own_total += (sh.seg[s].t1 - sh.seg[s].t0 + 3) & ~3; }
-        sh.own_in_smem = (HKV > 0 && !DIRECT && mode != kModeTpB && own_total <= kOwnCap) ? 1 : 0;
-        // attention partials: one per (request, CTA that has a share of the request's rows)
-        int pb = 0;
-        for (int b = 0; b < p.batch; ++b) {
-            sh.pbase[b] = pb;
-            if (ok && p.attn_inline) pb += static_share(p, sh, b, AttnGeom<(HKV > 0 ? HKV : 1)>::kRows).np;
-        }
-        sh.pbase[p.batch] = pb;
+        plan_ownership(p, sh, ok, HKV > 0 && !DIRECT && mode != kModeTpB, 32, false);
         mbar_init(smem_u32(&sh.stage_bar), 1);
         if (HKV > 0) {
             for (int s = 0; s < kScoreStages; ++s) {
@@ -1479,105 +1551,96 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_select_kernel(const La
     // the same empty plan, so all of them skip the scoring phases and their barriers together.  In the
     // fused tensor-parallel form the ranks decide alike for the same reason.
     const bool nothing_to_score = sh.tile_off[p.batch] == 0;
-    // attention inside this kernel: decode steps with the tensor-core shapes (the host does not launch the
-    // attention kernels then)
-    const bool attn = (HKV > 0 && !DIRECT) && p.attn_inline != 0 && (mode == kModeAll || mode == kModeTpFused);
     if (side && (nothing_to_score || !ok)) side_work<T>(p, sh, mode, err0, ok, whole_cta());
     // The parts of the index sets that do not depend on votes are written now, off the kernel's tail.
     if (!side && ok && mode != kModeTpA) emit_windows(p, sh, whole_cta());
     if (nothing_to_score) {
-        if constexpr (HKV > 0 && !DIRECT) {
-            if (attn) {
-                // no request recomputes: the lists are the cached or the complete ones; attend to them
-                __syncthreads();
-                if (tid == 0) {
-                    mbar_init(smem_u32(&tail_scratch(sh).kv_bar), 1);
-                    tail_scratch(sh).fast = 0;
-                    tail_scratch(sh).fast_b = -1;
-                    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-                }
-                __syncthreads();
-                if (ok) resolve_and_attend<HKV>(p, sh, ring, true, dead);
-                grid_barrier(p, dead, bar_gen);
-                if (ok) merge_phase(p, sh);
-            }
-        }
         stamp(p, 8);
         return;
     }
-    if (mode != kModeTpB) {
-        // ---- phase 1: score ----
-        if (ok) {
-            if (!side) {
-                // a CTA without candidates of request b still owes (-inf, 0) statistics for it
-                for (int i = tid; i < p.batch * p.hq; i += kFusedThreads) {
-                    const int b = i / p.hq, c = i - b * p.hq;
-                    bool mine = false;
-                    for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
-                    if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
-                        p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
+    {
+        if (mode != kModeTpB) {
+            // ---- phase 1: score ----
+            if (ok) {
+                if (!side) {
+                    // a CTA without candidates of request b still owes (-inf, 0) statistics for it
+                    for (int i = tid; i < p.batch * p.hq; i += kFusedThreads) {
+                        const int b = i / p.hq, c = i - b * p.hq;
+                        bool mine = false;
+                        for (int s = 0; s < sh.nseg; ++s) mine |= sh.seg[s].b == b;
+                        if (sh.plan.flag[b] == TS_FLAG_RECOMPUTE && !mine)
+                            p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
+                    }
                 }
+#ifndef SZ_NO_SCORE
+                if constexpr (HKV > 0 && !DIRECT) score_phase_tma<T, HKV, (HKV > kBulkMinHkv)>(p, sh, ring, dead, side, mode, err0);
+                else
+#endif
+                if constexpr (HKV > 0) score_phase_direct<HKV>(p, sh);
+                else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
             }
-            if constexpr (HKV > 0 && !DIRECT) score_phase_tma<T, HKV, (HKV > kBulkMinHkv)>(p, sh, ring, dead, side, mode, err0);
-            else if constexpr (HKV > 0) score_phase_direct<HKV>(p, sh);
-            else score_phase_plain<T>(p, sh, reinterpret_cast<float*>(ring));
-        }
-        if (ok) vote_prefetch(p, sh, ring);
-        stamp(p, 2);
-        if (p.stamps && threadIdx.x == 0) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            atomicMin(p.phase_ts + 13, t);
-            atomicMax(p.phase_ts + 14, t);
-        }
-        grid_barrier(p, dead, bar_gen);
-        stamp(p, 3);
-        // ---- phase 2: votes ----
-        if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead, votes_raw);
-        stamp(p, 4);
-        if (mode == kModeTpA) return;
-        if (mode == kModeTpFused) tp_exchange_phase(p, sh, ring, ok && !pooled, dead);
-        stamp(p, 24);
-        if (pooled) {
+#ifndef SZ_NO_VP
+            if (ok) vote_prefetch(p, sh, ring);
+#endif
+            stamp(p, 2);
+            if (p.stamps) stamp_range_slow(p.phase_ts, 1);
             grid_barrier(p, dead, bar_gen);
+            stamp(p, 3);
+            // ---- phase 2: votes ----
+#ifndef SZ_NO_VOTE
+            if (ok) vote_phase(p, sh, ring, mode == kModeAll && !pooled, stage_parity, dead, votes_raw);
+#endif
+            stamp(p, 4);
+            if (mode == kModeTpA) return;
+#ifndef SZ_NO_TPX
+            if (mode == kModeTpFused) tp_exchange_phase(p, sh, ring, ok && !pooled, dead);
+#endif
+            stamp(p, 24);
+            if (pooled) {
+                grid_barrier(p, dead, bar_gen);
+    #ifndef SZ_NO_POOLED
+                if (ok) hist_phase(p, sh);
+#endif
+            }
+        } else {
+#ifndef SZ_NO_HISTB
             if (ok) hist_phase(p, sh);
+#endif
         }
-    } else {
-        if (ok) hist_phase(p, sh);
-    }
-    grid_barrier(p, dead, bar_gen);
-    stamp(p, 5);
-    if (pooled) {
-        // max-pooled votes: the general top-k path on the pooled vote vector; attention kernels follow
-        if (ok) filter_phase(p, sh);
-        stamp(p, 6);
         grid_barrier(p, dead, bar_gen);
-        stamp(p, 7);
-        if (ok) emit_phase(p, sh, ring);
-        stamp(p, 8);
-    } else {
-        // ---- phase 3: threshold bin, records, early request of the possible winners' rows ----
-        if (ok) classify_phase<HKV>(p, sh, ring, attn);
-        stamp(p, 6);
-        grid_barrier(p, dead, bar_gen);
-        stamp(p, 7);
-        // ---- phases 4 and 5: final set, attention over the CTA's rows ----
-        if (ok) resolve_and_attend<HKV>(p, sh, ring, attn, dead);
-        stamp(p, 8);
-        if (attn) {
+        stamp(p, 5);
+        if (pooled) {
+            // max-pooled votes: the general top-k path on the pooled vote vector; attention kernels follow
+#ifndef SZ_NO_POOLED
+            if (ok) filter_phase(p, sh);
+            stamp(p, 6);
             grid_barrier(p, dead, bar_gen);
-            stamp(p, 15);
-            // ---- phase 6: merge of the partials ----
-            if (ok) merge_phase(p, sh);
-            stamp(p, 16);
+            stamp(p, 7);
+            if (ok) emit_phase(p, sh, ring);
+#endif
+            stamp(p, 8);
+            return;
         }
+        // ---- phase 3: threshold bin, records, early request of the possible winners' rows ----
+        tail_init(p, sh);
+#ifndef SZ_NO_CLASSIFY
+        if (ok) classify_phase<HKV, false>(p, sh, ring);
+#endif
+        stamp(p, 6);
+        grid_barrier(p, dead, bar_gen);
+        stamp(p, 7);
     }
-    if (p.stamps && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        atomicMax(p.phase_ts + 12, t);
-    }
+    // ---- phase 4: final set (the attention kernels follow) ----
+#ifndef SZ_NO_RESOLVE
+    if (ok) resolve_and_attend<HKV, false>(p, sh, ring, dead);
+#endif
+    stamp(p, 8);
+    if (p.stamps) stamp_range_slow(p.phase_ts, 2);
 }
+
+}  // namespace ts
+#include "step_kernel.cuh"
+namespace ts {
 
 // ------------------------------------------------------------------------------------------
 // host side
@@ -1642,7 +1705,50 @@ static cudaError_t launch_fused_t(const LayerParams& p, const Launch& l, int mod
     return e;
 }
 
+// The lean layer-step kernel (step_kernel.cuh): cooperative, with programmatic serialization where accepted.
+template <int HKV>
+static cudaError_t launch_step_t(const LayerParams& p, const Launch& l, int tp_fused) {
+    const size_t smem = kFusedDynSmem;
+    static SmemConfig configured = {};
+    cudaError_t e0 = ensure_dynamic_smem(decode_step_kernel<HKV>, smem, configured);
+    if (e0 != cudaSuccess) return e0;
+    LayerParams pp = p;
+    int tf = tp_fused;
+    stage_begin(l, kStageSelect);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.grid);
+    cfg.blockDim = dim3(kFusedThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = l.stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    static bool overlap_ok = true;      // cleared the first time the runtime refuses the pair of attributes
+    cfg.numAttrs = overlap_ok ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, decode_step_kernel<HKV>, pp, tf);
+    if (e != cudaSuccess && cfg.numAttrs == 2) {
+        (void)cudaGetLastError();
+        overlap_ok = false;
+        cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, decode_step_kernel<HKV>, pp, tf);
+    }
+    stage_end(l);
+    return e;
+}
+
 cudaError_t launch_fused(const LayerParams& p, const Launch& l, int mode) {
+    if (p.attn_inline && (mode == kModeAll || mode == kModeTpFused)) {
+        const int tf = mode == kModeTpFused ? 1 : 0;
+        switch (p.hkv) {
+            case 1: return launch_step_t<1>(p, l, tf);
+            case 2: return launch_step_t<2>(p, l, tf);
+            case 4: return launch_step_t<4>(p, l, tf);
+            default: return launch_step_t<8>(p, l, tf);
+        }
+    }
     if (use_mma(l.dtype, l.flags, p.hkv, p.d, p.group)) {
         const bool direct = use_direct(l.flags, p.hkv);
         switch (p.hkv) {

@@ -75,10 +75,12 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         const uint4* vs = reinterpret_cast<const uint4*>(p.v_new) + (size_t)b * row_vec;
         uint4* kd = reinterpret_cast<uint4*>(p.k_pool) + (size_t)loc * row_vec;
         uint4* vd = reinterpret_cast<uint4*>(p.v_pool) + (size_t)loc * row_vec;
+#pragma unroll 1
         for (int i = tid; i < row_vec; i += tg.nthr) { kd[i] = ks[i]; vd[i] = vs[i]; }
     }
 
     // 2. clear this request's first-level histogram and candidate counter
+#pragma unroll 1
     for (int i = tid; i < kHistBins; i += tg.nthr) p.hist[(size_t)b * kHistBins + i] = 0u;
     if (tid == 0) p.cand_count[b] = 0u;
 
@@ -94,6 +96,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     const T* q = reinterpret_cast<const T*>(p.q) + (size_t)b * hd;
     T* qr = reinterpret_cast<T*>(p.q_rot) + (size_t)b * hd;
     const int half = p.d / 2;
+#pragma unroll 1
     for (int e = tid; e < p.hq * half; e += tg.nthr) {
         int h = e / half, i = e % half;
         if (p.q_prerot) {                                  // a prefill chunk's fingerprint: copy
@@ -118,6 +121,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         float dot = 0.f, qq = 0.f, cc = 0.f;
         const bool have = p.valid[(size_t)req * p.n_layers + p.layer] != 0;
         if (have) {
+#pragma unroll 1
             for (int e = tid; e < hd; e += 32) {
                 float a = to_f32<T>(qr[e]);
                 float c = to_f32<T>(fp[e]);
@@ -155,6 +159,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     tg.sync();
     if (p.query_cache && s_flag == TS_FLAG_RECOMPUTE) {    // query_fingerprints_cache[layer] = q (:416)
         T* fpw = reinterpret_cast<T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
+#pragma unroll 1
         for (int e = tid; e < hd; e += tg.nthr) fpw[e] = qr[e];
     }
 }
@@ -178,6 +183,7 @@ __device__ __forceinline__ void decide_request(const LayerParams& p, int b, Prep
     if (p.query_cache && s_flag == TS_FLAG_RECOMPUTE) {
         const T* qr = reinterpret_cast<const T*>(p.q_rot) + (size_t)b * hd;
         T* fpw = reinterpret_cast<T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
+#pragma unroll 1
         for (int e = tid; e < hd; e += blockDim.x) fpw[e] = qr[e];
     }
 }

@@ -31,23 +31,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: gives up after `limit` clock cycles (or as soon as the sticky error word is set), records
 // TS_ERR_DEVICE_TIMEOUT and lets the caller carry on (control flow stays uniform so no barrier is left
-// short of a participant).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead, int where,
-                                          long long limit = kWaitCycles) {
-    if (mbar_try_wait(bar, parity)) return;
-    if (dead) return;
+// short of a participant).  The polling loop is one out-of-line function: waits sit in many places and the
+// kernels' speed depends on how few instruction bytes they fetch.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* err, int where, long long limit) {
     const long long t0 = clock64();
     unsigned spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 1023u) == 0u) {
-#ifdef TS_DIAG_CONST_WAIT
-            if (clock64() - t0 > kWaitCycles) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); dead = true; return; }
-#else
-            if (clock64() - t0 > limit) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); dead = true; return; }
-#endif
-            if (*(volatile int*)err != 0) { dead = true; return; }
+            if (clock64() - t0 > limit) { set_error(err, TS_ERR_DEVICE_TIMEOUT, where); return true; }
+            if (*(volatile int*)err != 0) return true;
         }
     }
+    return false;
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead, int where,
+                                          long long limit = kWaitCycles) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (dead) return;
+    dead = mbar_wait_slow(bar, parity, err, where, limit);
 }
 __device__ __forceinline__ uint64_t l2_evict_first_policy() {
     uint64_t pol;

@@ -45,7 +45,7 @@ struct TailScratch {
     int row_rank[kAttnRowsMax];              // its list position (rotation angle); < 0: not attended
     int row_t[kAttnRowsMax];                 // candidate index of a possible winner staged early
     unsigned row_v[kAttnRowsMax];            // its vote bits
-    float2 cs_q[64];                         // (cos, sin) of the query position
+    float inv_freq[64];                      // rotation frequencies of the attention positions
     unsigned rec_sure[kMaxGrid];
     unsigned rec_off[kMaxGrid];
     unsigned long long kv_bar;               // mbarrier of the staged K/V rows
@@ -71,15 +71,10 @@ template <int HKV> struct AttnGeom {
 };
 __device__ __forceinline__ int attn_part_bytes(int warps_busy, int group) { return warps_busy * group * (128 + 2) * 4; }
 
-// CTA that owns tile T when `total` tiles are dealt out in contiguous ranges [total*c/G, total*(c+1)/G).
-__device__ __forceinline__ int tile_owner(long long T, long long total, int grid) {
-    return (int)(((T + 1) * grid - 1) / total);
-}
 // First and last CTA that own candidates of request b (nc[b] > 0).
 __device__ __forceinline__ void owner_range(const LayerParams& p, const FusedShared& sh, int b, int& c0, int& c1) {
-    const long long total = sh.tile_off[p.batch];
-    c0 = tile_owner(sh.tile_off[b], total, p.grid);
-    c1 = tile_owner(sh.tile_off[b + 1] - 1, total, p.grid);
+    c0 = tile_owner(sh, (unsigned)sh.tile_off[b]);
+    c1 = tile_owner(sh, (unsigned)sh.tile_off[b + 1] - 1u);
 }
 
 // Rows of request b's list that do not depend on this step's votes, and how many CTAs share them.
@@ -129,6 +124,19 @@ __device__ __forceinline__ void static_row(const LayerParams& p, const FusedShar
     else pos = n - p.n_local + (list_idx - p.n_init - p.top_k);
 }
 
+// Called by all threads before the first use of the tail's scratch.
+__device__ __forceinline__ void tail_init(const LayerParams& p, FusedShared& sh) {
+    TailScratch& ts = tail_scratch(sh);
+    __syncthreads();                                   // the area's previous users are done
+    if (threadIdx.x >= 64 && threadIdx.x < 128 && p.attn_inline) ts.inv_freq[threadIdx.x - 64] = p.attn_inv_freq[threadIdx.x - 64];
+    if (threadIdx.x == 0) {
+        ts.fast = 0; ts.fast_static = 0; ts.fast_pot = 0; ts.fast_b = -1;
+        mbar_init(smem_u32(&ts.kv_bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+}
+
 // ------------------------------------------------------------------------------------------
 // phase 3
 // ------------------------------------------------------------------------------------------
@@ -138,19 +146,15 @@ __device__ __forceinline__ float own_vote(const LayerParams& p, const FusedShare
     return sh.own_in_smem ? votes_s[sh.seg_off[s] + (t - sh.seg[s].t0)] : __ldcg(votes_g + t);
 }
 
-template <int HKV>
-__device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool attn) {
+template <int HKV, bool ATTN>
+__device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn) {
+    constexpr bool attn = ATTN;
     using AG = AttnGeom<(HKV > 0 ? HKV : 1)>;
     const int tid = threadIdx.x;
     TailScratch& ts = tail_scratch(sh);
     const float* votes_s = own_votes(dyn);
     const int* slot_s = own_slots(dyn);
-    if (tid == 0) {
-        ts.fast = 0; ts.fast_static = 0; ts.fast_pot = 0; ts.fast_b = -1;
-        mbar_init(smem_u32(&ts.kv_bar), 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
+    fstamp(p, 4);
     // The first segment's request: this CTA's share of its window rows can be staged together with the
     // possible winners.  Their pool rows are looked up now (the loads travel with the histogram's).
     int st_cnt = 0, st_slot = 0, st_list = -1;
@@ -168,6 +172,7 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
             }
         }
     }
+#pragma unroll 1
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
         const float* votes_g = p.votes_final + sh.plan.off[sg.b];
@@ -182,11 +187,14 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
 #pragma unroll
         for (int i = 0; i < kHistBins / kFusedThreads; ++i) sh.hist[tid + kFusedThreads * i] = hreg[i];
         __syncthreads();
+        fstamp(p, 5);
         find_threshold(sh, (unsigned)p.top_k);
+        fstamp(p, 6);
         const unsigned b1 = (unsigned)sh.res_bin;
         if (tid == 0) { sh.seg_b1[s] = sh.res_bin; sh.seg_above[s] = sh.res_above; sh.seg_cnt[s] = sh.res_cnt; }
         // pass 1: sure winners and members of the bin among the own candidates
         unsigned sure = 0, eq = 0;
+#pragma unroll 1
         for (int t = own0; t < own1; ++t) {
             const unsigned bin = vote_bin(own_vote(p, sh, votes_s, votes_g, s, t));
             sure += bin > b1;
@@ -195,6 +203,7 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
         const unsigned long long packed = block_inclusive_scan(((unsigned long long)sure << 32) | eq, sh.warp_sum64);
         if (tid == kFusedThreads - 1) { sh.tmp_u[0] = (unsigned)(packed >> 32); sh.tmp_u[1] = (unsigned)packed; }
         __syncthreads();
+        fstamp(p, 7);
         const unsigned sure_tot = sh.tmp_u[0], eq_tot = sh.tmp_u[1];
         const bool overflow = eq_tot > (unsigned)kRecInline;
         SelRecord* rec = p.records + (size_t)sg.b * p.grid + blockIdx.x;
@@ -210,6 +219,7 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
         unsigned m_at = (unsigned)packed - eq;                                   // members in front of this thread's
         unsigned p_at = (unsigned)(packed >> 32) - sure + m_at;                  // possible winners in front of it
         uint2* list = p.cand + sh.plan.off[sg.b] + sh.tmp_u[2];
+#pragma unroll 1
         for (int t = own0; t < own1; ++t) {
             const float v = own_vote(p, sh, votes_s, votes_g, s, t);
             const unsigned bin = vote_bin(v);
@@ -231,8 +241,9 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
             if (tid == 0) { ts.fast = 1; ts.fast_static = st_cnt; ts.fast_pot = (int)(sure_tot + eq_tot); ts.fast_b = sg.b; }
         }
         __syncthreads();
+        fstamp(p, 8);
     }
-    if constexpr (HKV > 0) {
+    if constexpr (ATTN) {
         // request the staged rows: they land while the CTA waits at the next grid barrier
         if (ts.fast) {
             const int rows = ts.fast_static + ts.fast_pot;
@@ -247,6 +258,14 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
             }
         }
     }
+    if constexpr (ATTN) {
+        // the staged request's query is read right after the barrier: bring it close
+        if (ts.fast && tid < p.hq * 2) {
+            const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q) + ((size_t)ts.fast_b * p.hq * 256) + (size_t)tid * 128;
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(qrow));
+        }
+    }
+    fstamp(p, 9);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -268,24 +287,39 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
     owner_range(p, sh, sg.b, c0, c1);
     const int nown = c1 - c0 + 1;
     const SelRecord* recs = p.records + (size_t)sg.b * p.grid + c0;
-    // headers, and the overflow list's length
+    fstamp(p, 10);
+    // All records of the request in one round trip: 16 eight-byte words each, the first one the header; the
+    // members are kept in registers until the header prefix says where they go.
+    constexpr int kRecWords = 16;
+    constexpr int kPerThread = (kMaxGrid * kRecWords + kFusedThreads - 1) / kFusedThreads;     // 8
+    uint2 w[kPerThread];
     unsigned ovf = 0;
-    if (tid < nown) {
-        // a CTA inside the range may own no tile at all (fewer tiles than CTAs): it wrote no record
-        const long long total = sh.tile_off[p.batch];
-        const int c = c0 + tid;
-        const long long lo = max(total * c / p.grid, (long long)sh.tile_off[sg.b]);
-        const long long hi = min(total * (c + 1) / p.grid, (long long)sh.tile_off[sg.b + 1]);
-        uint2 h = make_uint2(0u, 0u);
-        if (lo < hi) h = __ldcg(reinterpret_cast<const uint2*>(recs + tid));
-        ts.rec_sure[tid] = h.x;
-        ts.rec_off[tid] = h.y;
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int idx = tid + kFusedThreads * u;
+        w[u] = make_uint2(0u, 0u);
+        if (idx < nown * kRecWords) w[u] = __ldcg(reinterpret_cast<const uint2*>(recs) + idx);
     }
     if (tid == kFusedThreads - 1) ovf = __ldcg(p.cand_count + sg.b);
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int idx = tid + kFusedThreads * u;
+        if (idx < nown * kRecWords && (idx & (kRecWords - 1)) == 0) {
+            // a CTA inside the range may own no tile at all (fewer tiles than CTAs): it wrote no record
+            const int r = idx / kRecWords;
+            const unsigned c = (unsigned)(c0 + r);
+            const int lo = max((int)tile_lo(sh, c), sh.tile_off[sg.b]);
+            const int hi = min((int)tile_lo(sh, c + 1u), sh.tile_off[sg.b + 1]);
+            ts.rec_sure[r] = lo < hi ? w[u].x : 0u;
+            ts.rec_off[r] = lo < hi ? w[u].y : 0u;
+        }
+    }
     __syncthreads();
+    fstamp(p, 11);
     if (tid < 32) {
         // exclusive prefix of the inline member counts; sure winners of the CTAs in front
         unsigned carry = 0, sb = 0;
+#pragma unroll 1
         for (int base = 0; base < nown; base += 32) {
             const int i = base + tid;
             const unsigned nm = i < nown ? ts.rec_off[i] : 0u;
@@ -309,18 +343,23 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
     }
     if (tid == kFusedThreads - 1) ts.n_ovf = ovf;
     __syncthreads();
+    fstamp(p, 12);
     const unsigned n_inl = ts.n_inl, n_ovf = ts.n_ovf, n_c = n_inl + n_ovf;
     // members: the inline ones always fit the staging area; the list's part when there is room
-    for (int i = tid; i < nown * kRecInline; i += kFusedThreads) {
-        const int r = i / kRecInline, m = i - r * kRecInline;
-        if ((unsigned)m < ts.rec_sure[r]) cand_s[ts.rec_off[r] + m] = __ldcg(&recs[r].members[m]);
+#pragma unroll
+    for (int u = 0; u < kPerThread; ++u) {
+        const int idx = tid + kFusedThreads * u;
+        const int r = idx / kRecWords, m = (idx & (kRecWords - 1)) - 1;
+        if (idx < nown * kRecWords && m >= 0 && (unsigned)m < ts.rec_sure[r]) cand_s[ts.rec_off[r] + m] = w[u];
     }
     const uint2* cand_g = p.cand + sh.plan.off[sg.b];
     const bool staged = n_c <= cand_cap;
     if (staged)
+#pragma unroll 1
         for (unsigned i = tid; i < n_ovf; i += kFusedThreads) cand_s[n_inl + i] = __ldcg(cand_g + i);
     __syncthreads();
     auto get_cand = [&](unsigned i) -> uint2 { return (i < n_inl || staged) ? cand_s[i] : __ldcg(cand_g + (i - n_inl)); };
+    fstamp(p, 13);
 
     Resolved r;
     r.b1 = (unsigned)sh.seg_b1[s];
@@ -333,6 +372,7 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
         if (tid < (int)n_c) {
             const unsigned long long key = cand_key(cand_s[tid]);
             unsigned larger = 0;
+#pragma unroll 1
             for (unsigned j = 0; j < n_c; ++j) larger += cand_key(cand_s[j]) > key;
             if (larger == k1 - 1) ts.key_at = key;
         }
@@ -348,9 +388,11 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
         for (int lv = 0; lv < 5; ++lv) {
             if (k_rem >= active) break;                    // everything still active is taken
             __syncthreads();
+#pragma unroll 1
             for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
             __syncthreads();
             const unsigned long long dmask = (1ull << widths[lv]) - 1ull;
+#pragma unroll 1
             for (unsigned i = tid; i < n_c; i += kFusedThreads) {
                 const unsigned long long key = cand_key(get_cand(i));
                 if ((key & mask_above) == prefix) atomicAdd(&sh.hist[(unsigned)((key >> shifts[lv]) & dmask)], 1u);
@@ -363,8 +405,10 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
             active = sh.res_cnt;
         }
     }
+    fstamp(p, 14);
     // selected members in front of this CTA's range
     unsigned before = 0;
+#pragma unroll 1
     for (unsigned i = tid; i < n_c; i += kFusedThreads) {
         const uint2 c = get_cand(i);
         if ((int)c.x < sg.t0 && (cand_key(c) & mask_above) >= prefix) ++before;
@@ -376,6 +420,7 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
     r.prefix = prefix;
     r.mask = mask_above;
     r.before = ts.sure_before + sh.tmp_u[3];
+    fstamp(p, 15);
     return r;
 }
 
@@ -405,6 +450,7 @@ __device__ __forceinline__ void emit_segment(const LayerParams& p, FusedShared& 
         const int st = ts.fast_static, np = ts.fast_pot;
         if (tid < 32) {
             unsigned carry = 0;
+#pragma unroll 1
             for (int base = 0; base < np; base += 32) {
                 const int i = base + tid;
                 const bool sel = i < np && vote_selected(r, ts.row_t[st + i], ts.row_v[st + i]);
@@ -435,12 +481,14 @@ __device__ __forceinline__ void emit_segment(const LayerParams& p, FusedShared& 
         int own0, own1, per;
         own_range(sg.t0, sg.t1, own0, own1, per);
         unsigned mine = 0;
+#pragma unroll 1
         for (int t = own0; t < own1; ++t)
             mine += vote_selected(r, t, __float_as_uint(own_vote(p, sh, votes_s, votes_g, s, t)));
         const unsigned long long packed = block_inclusive_scan((unsigned long long)mine, sh.warp_sum64);
         if (tid == kFusedThreads - 1) { sh.tmp_u[0] = r.before; sh.tmp_u[1] = (unsigned)packed; }
         __syncthreads();
         unsigned rank = r.before + (unsigned)packed - mine;
+#pragma unroll 1
         for (int t = own0; t < own1; ++t) {
             if (!vote_selected(r, t, __float_as_uint(own_vote(p, sh, votes_s, votes_g, s, t)))) continue;
             if (rank < (unsigned)k) {
@@ -465,65 +513,81 @@ __device__ __forceinline__ void emit_segment(const LayerParams& p, FusedShared& 
 // ------------------------------------------------------------------------------------------
 // phase 5: attention over staged rows
 // ------------------------------------------------------------------------------------------
+// sin and cos of a non-negative angle of up to a few thousand radians: two-constant reduction to [-pi, pi]
+// (2*pi = 6.2831854820251465 - 1.7484555e-7 in fp32 pieces), then the special-function unit (absolute error
+// below 1e-6, far inside the attention tolerance; the library's sincosf would cost hundreds of instruction
+// bytes at each place it is used).
+__device__ __forceinline__ void sincos_reduced(float a, float& sn, float& cn) {
+    const float n = rintf(a * 0.15915494309189535f);
+    float r = fmaf(n, -6.2831854820251465f, a);
+    r = fmaf(n, 1.7484555e-7f, r);
+    sn = __sinf(r);
+    cn = __cosf(r);
+}
+
+constexpr int kQStride = 136;            // floats per head of the staged rotated query (8 floats of padding: bank spread)
+
 // Rotation rows of the staged rows' list positions, in the order the lanes of the multiplying warps read them:
 // positions in tiles of eight; inside a tile the (cos, sin) of frequency i = 16s + 8u + 2t + w of position g
 // sits in float2 (((s*2+u)*8 + g)*4 + t)*2 + w.
 __device__ __forceinline__ void fill_rotation_rows(const LayerParams& p, const TailScratch& ts, float2* cs, int rows) {
+#pragma unroll 1
     for (int idx = threadIdx.x; idx < rows * 64; idx += kFusedThreads) {
         const int r = idx >> 6, i = idx & 63;
         const int rank = max(ts.row_rank[r], 0);
         float sn, cn;
-        sincosf(__fmul_rn((float)rank, p.attn_inv_freq[i]), &sn, &cn);
+        sincos_reduced(__fmul_rn((float)rank, ts.inv_freq[i]), sn, cn);
         const int tile = r >> 3, g = r & 7;
         const int s = i >> 4, u = (i >> 3) & 1, t = (i >> 1) & 3, w = i & 1;
         cs[(tile * 256 + ((s * 2 + u) * 8 + g) * 4 + t) * 2 + w] = make_float2(cn, sn);
     }
 }
 
-// One warp: 16 staged rows x one KV head.  Partial (max, sum) and unnormalised output of the head group go to
-// part_o [G][128] / part_ml [G] in shared memory.  Arithmetic as attend_split_tc_kernel (attend.cu): rotated
-// query and keys split into bf16 high and low parts, three mma.sync per k-step, softmax in base 2.
+// The request's query rotated at position count-1, fp32, [hq][kQStride] in shared memory.
+__device__ __forceinline__ void fill_rotated_query(const LayerParams& p, const TailScratch& ts, const __nv_bfloat16* q_b, int count,
+                                                   float* q_s) {
+#pragma unroll 1
+    for (int idx = threadIdx.x; idx < p.hq * 64; idx += kFusedThreads) {
+        const int h = idx >> 6, i = idx & 63;
+        float sn, cn;
+        sincos_reduced(__fmul_rn((float)(count - 1), ts.inv_freq[i]), sn, cn);
+        const float x1 = __bfloat162float(q_b[h * 128 + i]), x2 = __bfloat162float(q_b[h * 128 + i + 64]);
+        q_s[h * kQStride + i] = x1 * cn - x2 * sn;
+        q_s[h * kQStride + i + 64] = x2 * cn + x1 * sn;
+    }
+}
+
+// One warp: S^T of 16 staged rows x one KV head's query heads.  Arithmetic as attend_split_tc_kernel
+// (attend.cu): rotated query and keys split into bf16 high and low parts, three mma.sync per k-step.  The
+// loops are kept rolled: this code runs once per launch and its cost is the instruction bytes it fetches.
 template <int HKV>
-__device__ __forceinline__ void attend_block(const LayerParams& p, const TailScratch& ts, const unsigned char* sm_k,
-                                             const unsigned char* sm_v, const float4* sm_cs, int wb, int kv, int rows,
-                                             const __nv_bfloat16* q_b, float* part_o, float2* part_ml) {
+__device__ __forceinline__ void attend_scores(const LayerParams& p, const unsigned char* sm_k, const float4* sm_cs,
+                                              const float* q_s, int wb, int kv, float (&sc)[2][4]) {
     using AG = AttnGeom<HKV>;
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = p.group;
-    // ---- query fragments ----
-    uint32_t qh[8][2], ql[8][2];
-    {
-        const __nv_bfloat16* q = q_b + (size_t)(kv * G + min(g, G - 1)) * 128;
-        uint32_t w[8][2];
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-#pragma unroll
-            for (int u = 0; u < 2; ++u) w[ks][u] = *reinterpret_cast<const uint32_t*>(q + 16 * ks + 8 * u + 2 * t);
-#pragma unroll
-        for (int s = 0; s < 4; ++s)
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const float4 cs = *reinterpret_cast<const float4*>(ts.cs_q + 16 * s + 8 * u + 2 * t);
-                const float x1a = __uint_as_float(w[s][u] << 16), x1b = __uint_as_float(w[s][u] & 0xFFFF0000u);
-                const float x2a = __uint_as_float(w[s + 4][u] << 16), x2b = __uint_as_float(w[s + 4][u] & 0xFFFF0000u);
-                const bool on = g < G;
-                split_bf16x2(on ? x1a * cs.x - x2a * cs.y : 0.f, on ? x1b * cs.z - x2b * cs.w : 0.f, qh[s][u], ql[s][u]);
-                split_bf16x2(on ? x2a * cs.x + x1a * cs.y : 0.f, on ? x2b * cs.z + x1b * cs.w : 0.f, qh[s + 4][u], ql[s + 4][u]);
-            }
-    }
-    // ---- S^T = Q_rot . K_rot^T ----
-    float sc[2][4];
+    const bool on = g < G;
+    const float* qh = q_s + (size_t)(kv * G + min(g, G - 1)) * kQStride;
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) sc[j][i] = 0.f;
     const int lrow = lane & 7, lsel = lane >> 3;
+#pragma unroll 1
+    for (int s = 0; s < 4; ++s) {
+        // A fragments of k-steps s and s+4 (rows 8..15 of A are unused: zero)
+        uint32_t ah[2][2], al[2][2];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-        const float4* cst = sm_cs + (size_t)(wb * 2 + j) * 256;
+        for (int k2 = 0; k2 < 2; ++k2)
 #pragma unroll
-        for (int s = 0; s < 4; ++s) {
+            for (int u = 0; u < 2; ++u) {
+                const float2 x = *reinterpret_cast<const float2*>(qh + 16 * (s + 4 * k2) + 8 * u + 2 * t);
+                split_bf16x2(on ? x.x : 0.f, on ? x.y : 0.f, ah[k2][u], al[k2][u]);
+            }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const float4* cst = sm_cs + (size_t)(wb * 2 + j) * 256;
             uint32_t r[4];
             const int doff = 16 * s + (lsel & 1) * 8 + (lsel >> 1) * 64;
             ldmatrix_x4(r, smem_u32(sm_k) + (wb * 16 + 8 * j + lrow) * AG::kRowS + kv * 256 + doff * 2);
@@ -538,16 +602,25 @@ __device__ __forceinline__ void attend_block(const LayerParams& p, const TailScr
             }
 #pragma unroll
             for (int k2 = 0; k2 < 2; ++k2) {
-                const int ks = s + 4 * k2;
-                const uint32_t ah[4] = {qh[ks][0], 0u, qh[ks][1], 0u};
-                const uint32_t al[4] = {ql[ks][0], 0u, ql[ks][1], 0u};
-                mma_bf16_16816(sc[j], ah, bh[k2][0], bh[k2][1]);
-                mma_bf16_16816(sc[j], ah, bl[k2][0], bl[k2][1]);
-                mma_bf16_16816(sc[j], al, bh[k2][0], bh[k2][1]);
+                const uint32_t a_hi[4] = {ah[k2][0], 0u, ah[k2][1], 0u};
+                const uint32_t a_lo[4] = {al[k2][0], 0u, al[k2][1], 0u};
+                mma_bf16_16816(sc[j], a_hi, bh[k2][0], bh[k2][1]);
+                mma_bf16_16816(sc[j], a_hi, bl[k2][0], bl[k2][1]);
+                mma_bf16_16816(sc[j], a_lo, bh[k2][0], bh[k2][1]);
             }
         }
     }
-    // ---- softmax over the block's rows (head = accumulator row g; a quad shares it) ----
+}
+
+// Softmax numerators of the block (base 2) and O^T = V^T . P^T into part_o [G][128], (max, sum) into part_ml [G].
+template <int HKV>
+__device__ __forceinline__ void attend_values(const LayerParams& p, const TailScratch& ts, const unsigned char* sm_v, int wb,
+                                              int kv, int rows, const float (&sc)[2][4], float* part_o, float2* part_ml) {
+    using AG = AttnGeom<HKV>;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = p.group;
+    const int lrow = lane & 7;
     float x[2][2], mx = -INFINITY;
 #pragma unroll
     for (int j = 0; j < 2; ++j)
@@ -567,7 +640,7 @@ __device__ __forceinline__ void attend_block(const LayerParams& p, const TailScr
     for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            pe[j][u] = (x[j][u] == -INFINITY) ? 0.f : exp2f(x[j][u] - mx);
+            pe[j][u] = (x[j][u] == -INFINITY) ? 0.f : ex2_ftz(fmaxf(x[j][u] - mx, -126.f));
             lsum += pe[j][u];
         }
     lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
@@ -575,8 +648,7 @@ __device__ __forceinline__ void attend_block(const LayerParams& p, const TailScr
     uint32_t ph[2], pl[2];
     split_bf16x2(pe[0][0], pe[0][1], ph[0], pl[0]);
     split_bf16x2(pe[1][0], pe[1][1], ph[1], pl[1]);
-    // ---- O^T = V^T . P^T ----
-#pragma unroll
+#pragma unroll 1
     for (int db = 0; db < 8; ++db) {
         uint32_t a[4];
         ldmatrix_x4_trans(a, smem_u32(sm_v) + (wb * 16 + ((lane >> 4) & 1) * 8 + lrow) * AG::kRowS + kv * 256 +
@@ -597,41 +669,37 @@ __device__ __forceinline__ void attend_block(const LayerParams& p, const TailScr
 }
 
 // The rows of one (request, CTA): `st_cnt` rows that never depended on votes starting at static row st0,
-// then `own_cnt` winners of this CTA starting at list index own0.  `staged`: the first round's rows are
-// already on their way (requested by classify_phase).  Writes partial `pslot` of the request.
+// then `own_cnt` winners of this CTA starting at list index own0.  `staged`: all rows are already on their
+// way (requested by classify_phase) and listed in the scratch.  Writes partial `pslot` of the request.
 template <int HKV>
 __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared& sh, unsigned char* dyn, int b, int pslot,
                                               int st0, int st_cnt, int own0, int own_cnt, bool staged, uint32_t& kv_parity,
                                               bool& dead) {
     using AG = AttnGeom<HKV>;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x, warp = tid >> 5;
     TailScratch& ts = tail_scratch(sh);
     const int G = p.group, hq = p.hq;
     unsigned char* sm_k = dyn;
     unsigned char* sm_v = dyn + AG::kRows * AG::kRowS;
     float2* cs = reinterpret_cast<float2*>(dyn + AG::kCsOff);
-    float* part = reinterpret_cast<float*>(dyn + AG::kPartOff);       // [warps busy][G][130]
+    float* part = reinterpret_cast<float*>(dyn + AG::kPartOff);       // [warps busy][G][130]; first the rotated query
     const uint32_t bar = smem_u32(&ts.kv_bar);
-    const int n = sh.plan.n[b];
-    const int count = min(n, p.n_sel);
+    const int count = min(sh.plan.n[b], p.n_sel);
     const __nv_bfloat16* q_b = reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)b * hq * 128;
     float* g_o = p.part_o + (size_t)pslot * hq * 128;
     float2* g_ml = p.part_ml + (size_t)pslot * hq;
     const int total = st_cnt + own_cnt;
     if (total == 0) {
+#pragma unroll 1
         for (int h = tid; h < hq; h += kFusedThreads) g_ml[h] = make_float2(-INFINITY, 0.f);
         return;
     }
-    // (cos, sin) of the query position count-1
-    if (tid < 64) {
-        float sn, cn;
-        sincosf(__fmul_rn((float)(count - 1), p.attn_inv_freq[tid]), &sn, &cn);
-        ts.cs_q[tid] = make_float2(cn, sn);
-    }
     const int* rtt_row = p.rtt + (long long)sh.plan.req[b] * p.rtt_stride;
+#pragma unroll 1
     for (int r0 = 0; r0 < total; r0 += AG::kRows) {
         const int rows = min(AG::kRows, total - r0);
-        if (!(staged && r0 == 0)) {
+        const int rows16 = (rows + 15) / 16 * 16;
+        if (!staged) {
             // look the round's rows up and request them
             __syncthreads();                               // the previous round's readers are done
             if (tid < rows) {
@@ -664,7 +732,7 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
             }
         }
         // rows of the last, partly filled block: zeros, so that 0-weight products stay finite
-        const int rows16 = (rows + 15) / 16 * 16;
+#pragma unroll 1
         for (int i = rows * (AG::kRowB / 16) + tid; i < rows16 * (AG::kRowB / 16); i += kFusedThreads) {
             const int r = i / (AG::kRowB / 16), c = i - r * (AG::kRowB / 16);
             *reinterpret_cast<uint4*>(sm_k + r * AG::kRowS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -672,16 +740,22 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
         }
         if (tid >= rows && tid < rows16) ts.row_rank[tid] = -1;
         __syncthreads();
+        fstamp(p, 17);
         fill_rotation_rows(p, ts, cs, rows16);
+        fill_rotated_query(p, ts, q_b, count, part);
         __syncthreads();
+        fstamp(p, 18);
         mbar_wait(bar, kv_parity, p.err, dead, 5, p.wait_cycles);
         kv_parity ^= 1u;
+        fstamp(p, 19);
         const int nblk = rows16 / 16;
         const int wb = warp / HKV, kv = warp % HKV;
+        float sc[2][4];
+        if (wb < nblk) attend_scores<HKV>(p, sm_k, reinterpret_cast<const float4*>(cs), part, wb, kv, sc);
+        __syncthreads();                                   // the rotated query has been read: its place takes the partials
         float* my_o = part + (size_t)warp * G * 130;
-        if (wb < nblk)
-            attend_block<HKV>(p, ts, sm_k, sm_v, reinterpret_cast<const float4*>(cs), wb, kv, rows, q_b, my_o,
-                              reinterpret_cast<float2*>(my_o + G * 128));
+        if (wb < nblk) attend_values<HKV>(p, ts, sm_v, wb, kv, rows, sc, my_o, reinterpret_cast<float2*>(my_o + G * 128));
+        fstamp(p, 20);
         __syncthreads();
         // merge the blocks of the round (and, from the second round on, the partial written so far):
         // per head the new (max, sum) and the weights of the pieces, then the weighted outputs
@@ -692,16 +766,18 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
             const int h = tid, kvh = h / G, gg = h - kvh * G;
             const float2 prev = more ? g_ml[h] : make_float2(-INFINITY, 0.f);
             float mm = prev.x;
+#pragma unroll 1
             for (int w = 0; w < nblk; ++w)
                 mm = fmaxf(mm, reinterpret_cast<const float2*>(part + (size_t)(w * HKV + kvh) * G * 130 + G * 128)[gg].x);
-            const float wp = (prev.x == -INFINITY) ? 0.f : exp2f(prev.x - mm);
+            const float wp = (prev.x == -INFINITY) ? 0.f : ex2_ftz(fmaxf(prev.x - mm, -126.f));
             float ll = prev.y * wp;
             s_w[h * kW + AG::kBlocks] = wp;
+#pragma unroll 1
             for (int w = 0; w < AG::kBlocks; ++w) {
                 float wgt = 0.f;
                 if (w < nblk) {
                     const float2 ml = reinterpret_cast<const float2*>(part + (size_t)(w * HKV + kvh) * G * 130 + G * 128)[gg];
-                    wgt = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - mm);
+                    wgt = (ml.x == -INFINITY) ? 0.f : ex2_ftz(fmaxf(ml.x - mm, -126.f));
                     ll += ml.y * wgt;
                 }
                 s_w[h * kW + w] = wgt;
@@ -710,11 +786,13 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
             s_w[hq * kW + 2 * h + 1] = ll;
         }
         __syncthreads();
+#pragma unroll 1
         for (int idx = tid; idx < hq * 128; idx += kFusedThreads) {
             const int h = idx >> 7, e = idx & 127;
             const int kvh = h / G, gg = h - kvh * G;
             const float wp = s_w[h * kW + AG::kBlocks];
             float acc = wp > 0.f ? g_o[idx] * wp : 0.f;
+#pragma unroll 1
             for (int w = 0; w < nblk; ++w) {
                 const float wgt = s_w[h * kW + w];
                 if (wgt > 0.f) acc += part[(size_t)(w * HKV + kvh) * G * 130 + gg * 128 + e] * wgt;
@@ -722,13 +800,16 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
             g_o[idx] = acc;
         }
         if (tid < hq) g_ml[tid] = make_float2(s_w[hq * kW + 2 * tid], s_w[hq * kW + 2 * tid + 1]);
+        fstamp(p, 21);
+        staged = false;                                    // only the first round can have been requested early
     }
     __syncthreads();
 }
 
 // Phases 4 and 5 for everything this CTA holds.
-template <int HKV>
-__device__ __forceinline__ void resolve_and_attend(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool attn, bool& dead) {
+template <int HKV, bool ATTN>
+__device__ __forceinline__ void resolve_and_attend(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool& dead) {
+    constexpr bool attn = ATTN;
     using AG = AttnGeom<(HKV > 0 ? HKV : 1)>;
     TailScratch& ts = tail_scratch(sh);
     // members are staged where the rotation rows and the partial outputs go later (behind the K/V rows, which
@@ -736,33 +817,35 @@ __device__ __forceinline__ void resolve_and_attend(const LayerParams& p, FusedSh
     uint2* cand_s = reinterpret_cast<uint2*>(dyn + (attn ? AG::kCsOff : 0));
     const unsigned cand_cap = attn ? (unsigned)((AG::kCsBytes + attn_part_bytes(AG::kWarpsBusy, p.group)) / 8)
                                    : (unsigned)((kFusedDynSmem - 2 * kOwnCap * 4) / 8);
+#pragma unroll 1
     for (int s = 0; s < sh.nseg; ++s) {
         const Resolved r = resolve_segment(p, sh, s, cand_s, cand_cap);
         emit_segment(p, sh, dyn, s, r, ts.fast != 0 && s == 0);
+        fstamp(p, 16);
     }
-    if constexpr (HKV > 0) {
-        if (!attn) return;
+    if constexpr (ATTN) {
         uint32_t kv_parity = 0;
         // the staged row set first (its rows are already in flight), then every other request this CTA has a part in
-        for (int pass = 0; pass < 2; ++pass) {
-            for (int b = 0; b < p.batch; ++b) {
-                const bool is_fast = ts.fast != 0 && b == ts.fast_b;
-                if ((pass == 0) != is_fast) continue;
-                const StaticShare ss = static_share(p, sh, b, AG::kRows);
-                const int me = share_index(p, ss);
-                if (me < 0) continue;
-                const int st0 = me * ss.chunk, st_cnt = max(0, min(ss.total, st0 + ss.chunk) - st0);
-                int own0 = 0, own_cnt = 0;
-                for (int s = 0; s < sh.nseg; ++s)
-                    if (sh.seg[s].b == b) { own0 = (int)sh.seg_above[s]; own_cnt = (int)sh.seg_cnt[s]; }
-                const int pslot = sh.pbase[b] + me;
-                if (is_fast) {
-                    // staged rows: the static ones, then the possible winners (those not selected carry rank -1)
-                    attend_rowset<HKV>(p, sh, dyn, b, pslot, st0, ts.fast_static + ts.fast_pot, 0, 0, true, kv_parity, dead);
-                } else {
-                    attend_rowset<HKV>(p, sh, dyn, b, pslot, st0, st_cnt, own0, own_cnt, false, kv_parity, dead);
-                }
+        const int nb = p.batch;
+#pragma unroll 1
+        for (int it = 0; it < 2 * nb; ++it) {
+            const int pass = it >= nb ? 1 : 0, b = it - pass * nb;
+            const bool is_fast = ts.fast != 0 && b == ts.fast_b;
+            if ((pass == 0) != is_fast) continue;
+            const StaticShare ss = static_share(p, sh, b, AG::kRows);
+            const int me = share_index(p, ss);
+            if (me < 0) continue;
+            int st0 = me * ss.chunk, st_cnt = max(0, min(ss.total, st0 + ss.chunk) - st0);
+            int own0 = 0, own_cnt = 0;
+#pragma unroll 1
+            for (int s = 0; s < sh.nseg; ++s)
+                if (sh.seg[s].b == b) { own0 = (int)sh.seg_above[s]; own_cnt = (int)sh.seg_cnt[s]; }
+            if (is_fast) {
+                // staged rows: the static ones, then the possible winners (those not selected carry rank -1)
+                st_cnt = ts.fast_static + ts.fast_pot;
+                own_cnt = 0;
             }
+            attend_rowset<HKV>(p, sh, dyn, b, sh.pbase[b] + me, st0, st_cnt, own0, own_cnt, is_fast, kv_parity, dead);
         }
     }
 }
@@ -776,6 +859,8 @@ __device__ __forceinline__ void merge_phase(const LayerParams& p, FusedShared& s
     float* s_acc = reinterpret_cast<float*>(sh.hist);          // [16 warps][32]
     float* s_red = s_acc + 16 * 32;                              // [2][16]
     const int items = p.batch * hq * 4;
+    fstamp(p, 22);
+#pragma unroll 1
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int b = item / (hq * 4), rem = item - b * hq * 4;
         const int h = rem >> 2, qd = rem & 3;
@@ -784,12 +869,13 @@ __device__ __forceinline__ void merge_phase(const LayerParams& p, FusedShared& s
         const float2* ml = p.part_ml + (size_t)sh.pbase[b] * hq + h;
         const float* o = p.part_o + ((size_t)sh.pbase[b] * hq + h) * 128 + qd * 32 + lane;
         float mm = -INFINITY, ll = 0.f, acc = 0.f;
-        for (int c0 = 0; c0 < np; c0 += kFusedThreads) {
-            // (max, sum) of up to 512 partials, and this warp's share of their outputs, requested together
+#pragma unroll 1
+        for (int c0 = 0; c0 < np; c0 += 16 * 10) {
+            // (max, sum) of up to 160 partials, and this warp's share of their outputs, requested together
             const int c = c0 + tid;
             float2 mine = make_float2(-INFINITY, 0.f);
-            if (c < np) mine = __ldcg(ml + (size_t)c * hq);
-            constexpr int kPer = kFusedThreads / 16;          // 32 partials per warp and round
+            if (c < np && tid < 16 * 10) mine = __ldcg(ml + (size_t)c * hq);
+            constexpr int kPer = 10;                          // partials per warp and round: one round for grids up to 160
             float xo[kPer];
 #pragma unroll
             for (int u = 0; u < kPer; ++u) {
@@ -800,6 +886,7 @@ __device__ __forceinline__ void merge_phase(const LayerParams& p, FusedShared& s
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) m2 = fmaxf(m2, __shfl_xor_sync(0xffffffffu, m2, off));
             __syncthreads();
+            fstamp(p, 23);
             if (lane == 0) s_red[warp] = m2;
             __syncthreads();
             float mn = mm;
@@ -840,6 +927,7 @@ __device__ __forceinline__ void merge_phase(const LayerParams& p, FusedShared& s
         }
         __syncthreads();
     }
+    fstamp(p, 24);
 }
 
 }  // namespace ts
