@@ -74,6 +74,9 @@ def parse_args():
                          "through ts_extend_chunk instead of the decode step")
     ap.add_argument("--flags", type=int, default=0, help="further TS_CFG_* diagnostic bits for the engine")
     ap.add_argument("--no-check", action="store_true", help="skip the untimed check against the CPU oracle")
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="benchmark configuration: 2 the headline (default), 3 ragged Qwen2 batch, 4 selection-cache "
+                         "stress, 5 one-million-token batch under tensor parallelism")
     ap.add_argument("--seed", type=int, default=2024)
     return ap.parse_args()
 
@@ -260,6 +263,123 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_config4(args):
+    """Selection-cache stress (the fourth benchmark configuration): the headline layer shape at 65536 context
+    tokens, decode queries following q_t = rho*q_(t-1) + sqrt(1-rho^2)*eps_t per layer, rho in {0.80, 0.95, 0.99} x
+    threshold in {0.85, 0.90, 0.95}, 512 steps each.  Per pair: reuse rate, microseconds per layer for steps that
+    recompute and for steps that reuse (least squares over the per-token times, a token's layers decide
+    independently), and whether every decision equals the CPU oracle's replay of the same fixed-order fp32 cosine
+    (the replay needs the query sequence only; decisions within 1e-5 of the threshold in fp64 are counted apart)."""
+    import numpy as np
+    from oracle import tokenselect_oracle as orc
+    from tokenselect_b200 import TokenSelectConfig, TokenSelectEngine
+    from tokenselect_b200 import build as _build
+    _build.build_library()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    ctx, layers, steps = (args.ctx if args.ctx != 131072 else 65536), args.layers, (args.steps if args.steps != 256 else 512)
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    rows = ctx + steps + 64
+    perm = torch.randperm(rows, generator=g, device=dev).to(torch.int32)
+    max_ctx = ctx + steps + 8
+    rtt = torch.zeros(2, max_ctx, dtype=torch.int32, device=dev)
+    rtt[1] = perm[:max_ctx]
+    planted = torch.randperm(ctx - N_INIT - N_LOCAL, generator=g, device=dev)[: ctx // 100] + N_INIT
+    planted_rows = perm[planted].long()
+    k_pools, v_pools = [], []
+    for _ in range(layers):
+        u = torch.randn(HKV, D, generator=g, device=dev)
+        k, v = make_layer_data(g, dev, rows, ctx, HKV, planted_rows, u / u.norm(dim=-1, keepdim=True))
+        k_pools.append(k)
+        v_pools.append(v)
+    ks = torch.randn(steps, layers, 1, HKV * D, generator=g, device=dev).to(torch.bfloat16)
+    vs = torch.randn(steps, layers, 1, HKV * D, generator=g, device=dev).to(torch.bfloat16)
+    eps = torch.randn(steps, layers, HQ * D, generator=g, device=dev)
+    ridx = torch.tensor([1], dtype=torch.int32, device=dev)
+    lens_all = torch.arange(ctx + 1, ctx + 1 + steps, dtype=torch.int32, device=dev).view(-1, 1)
+    locs_all = perm[ctx: ctx + steps].view(-1, 1).contiguous()
+    out = torch.empty(1, HQ * D, dtype=torch.bfloat16, device=dev)
+    pairs, launches_total, ms_total = [], 0, 0.0
+    sampler = ClockSampler(0)
+    sampler.start()
+    for rho in (0.80, 0.95, 0.99):
+        qs = torch.empty_like(eps)
+        qs[0] = eps[0]
+        for t in range(1, steps):
+            qs[t] = rho * qs[t - 1] + (1.0 - rho * rho) ** 0.5 * eps[t]
+        qs_b = qs.to(torch.bfloat16).contiguous()
+        q_rot = orc.rotate_scoring_query(qs_b.cpu().view(steps, layers, HQ, D), N_LOCAL, ROPE_BASE, 1.0)
+        q_rot = q_rot.float().numpy().reshape(steps, layers, HQ * D)
+        for theta in (0.85, 0.90, 0.95):
+            cfg = TokenSelectConfig(rope_base=ROPE_BASE, max_n_tokens=max_ctx, top_k=TOP_K, n_init=N_INIT, n_local=N_LOCAL,
+                                    n_layers=layers, num_q_heads=HQ, num_kv_heads=HKV, head_dim=D, max_reqs=2, max_batch=1,
+                                    max_total_tokens=max_ctx, query_cache=True, similarity_threshold=theta)
+            eng = TokenSelectEngine(cfg, device=dev)
+            eng.reset_request(1)
+            flags = torch.zeros(steps, layers, dtype=torch.int32, device=dev)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            c0 = eng.launch_count
+            torch.cuda.synchronize()
+            for t in range(steps):
+                ev[t].record()
+                for li in range(layers):
+                    eng.decode_layer(li, qs_b[t, li:li + 1], ks[t, li], vs[t, li], locs_all[t], k_pools[li], v_pools[li], rtt,
+                                     ridx, lens_all[t], out=out, debug={"flags": flags[t, li:li + 1]})
+            ev[steps].record()
+            torch.cuda.synchronize()
+            eng.raise_on_device_error()
+            launches_total += eng.launch_count - c0
+            tok_ms = np.array([ev[t].elapsed_time(ev[t + 1]) for t in range(steps)])
+            ms_total += float(tok_ms.sum())
+            got = flags.cpu().numpy()
+            # replay on the CPU: fixed-order fp32 cosine against the query of the layer's last recompute
+            th32 = np.float32(theta)
+            cache = np.zeros((layers, HQ * D), dtype=np.float32)
+            valid = np.zeros(layers, dtype=bool)
+            want = np.zeros_like(got)
+            near = np.zeros_like(got, dtype=bool)
+            for t in range(steps):
+                terms = orc.cosine_terms_fixed_order_batch(q_rot[t], cache)
+                den = (np.sqrt(terms[:, 1]) * np.sqrt(terms[:, 2])).astype(np.float32)
+                cos = np.where(den == 0, np.float32(0), (terms[:, 0] / np.where(den == 0, np.float32(1), den)).astype(np.float32))
+                cos64 = (q_rot[t].astype(np.float64) * cache).sum(1) / np.maximum(
+                    np.linalg.norm(q_rot[t].astype(np.float64), axis=1) * np.linalg.norm(cache.astype(np.float64), axis=1), 1e-300)
+                rec = ~valid | (cos < th32)
+                near[t] = valid & (np.abs(cos64 - theta) < 1e-5)
+                want[t] = np.where(rec, 1, 2)                  # TS_FLAG_RECOMPUTE / TS_FLAG_REUSE
+                cache[rec] = q_rot[t][rec]
+                valid |= rec
+            wrong = int(((got != want) & ~near).sum())
+            r = (got == 1).sum(axis=1).astype(np.float64)      # recomputing layers per token
+            a = np.stack([r, layers - r], axis=1)
+            coef, *_ = np.linalg.lstsq(a, tok_ms * 1e3, rcond=None)
+            retr, reuses = eng.counters(1)
+            pairs.append({"rho": rho, "threshold": theta, "decisions": int(got.size), "reuse_rate": float((got == 2).mean()),
+                          "counters": {"retrievals": int(retr), "reuses": int(reuses)},
+                          "decisions_exact": wrong == 0, "decisions_differing": wrong,
+                          "decisions_within_1e-5_of_threshold": int(near.sum()),
+                          "tok_s": steps / (tok_ms.sum() * 1e-3), "us_per_layer": float(tok_ms.sum() * 1e3 / (steps * layers)),
+                          "us_per_layer_recompute": float(coef[0]), "us_per_layer_reuse": float(coef[1])})
+            eng.close()
+    clocks = sampler.stop()
+    mid = next(x for x in pairs if x["rho"] == 0.95 and x["threshold"] == 0.90)
+    line = {
+        "metric": METRIC, "value": mid["tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": 0,
+        "ms_per_step": 1e3 / mid["tok_s"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"config 4: selection-cache stress, llama3-8b layer shape, bs=1, ctx={ctx}, {layers} layers, {steps} "
+                               f"steps per (rho, threshold) pair, AR(1) decode queries, top_k={TOP_K}, n_init={N_INIT}, "
+                               f"n_local={N_LOCAL}; value = the (rho 0.95, threshold 0.90) pair",
+                   "launch": "kernels launched from the host (one call per layer, flags read back per call)"},
+        "us_per_layer": mid["us_per_layer"], "pairs": pairs,
+        "all_decisions_exact": all(x["decisions_exact"] for x in pairs),
+        "gpu_launches": int(launches_total), "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+    if not line["all_decisions_exact"]:
+        raise SystemExit(3)
+
+
 def tensor_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -404,6 +524,9 @@ def main():
     args = parse_args()
     if args.prefill:
         run_prefill(args)
+        return
+    if args.config == 4 and args.impl == "ours":
+        run_config4(args)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -143,18 +143,11 @@ __device__ __forceinline__ void vote_phase_lean(const LayerParams& p, FusedShare
 }
 
 template <int HKV>
-__global__ void __launch_bounds__(kFusedThreads, 1) decode_step_kernel(const __grid_constant__ LayerParams gp, const int tp_fused) {
+__global__ void __launch_bounds__(kFusedThreads, 1) decode_step_kernel(const LayerParams p, const int tp_fused) {
     using T = __nv_bfloat16;
     extern __shared__ __align__(128) unsigned char ring[];
     __shared__ FusedShared sh;
-    // The parameters are copied to shared memory once and read from there: each phase touches other fields, and
-    // a first touch of a kernel parameter is a miss of the constant cache, which is cold at every launch.
-    __shared__ __align__(16) LayerParams sp;
     const int tid = threadIdx.x;
-    if (tid < (int)(sizeof(LayerParams) / 4))
-        reinterpret_cast<uint32_t*>(&sp)[tid] = reinterpret_cast<const uint32_t*>(&gp)[tid];
-    __syncthreads();
-    const LayerParams& p = sp;
     bool dead = false;
     // Launched with programmatic serialization where the runtime accepts it: the CTAs may be placed while the
     // previous kernel drains; nothing is read or written before it has finished.

@@ -124,6 +124,13 @@ __device__ __forceinline__ void static_row(const LayerParams& p, const FusedShar
     else pos = n - p.n_local + (list_idx - p.n_init - p.top_k);
 }
 
+// Diagnostic: an address that is not aligned as its access needs is recorded (9000 + site) instead of used.
+__device__ __forceinline__ bool aligned_or_report(const LayerParams& p, const void* a, unsigned mask, int site) {
+    if ((reinterpret_cast<unsigned long long>(a) & mask) == 0ull) return true;
+    set_error(p.err, TS_ERR_INTERNAL, 9000 + site);
+    return false;
+}
+
 // Called by all threads before the first use of the tail's scratch.
 __device__ __forceinline__ void tail_init(const LayerParams& p, FusedShared& sh) {
     TailScratch& ts = tail_scratch(sh);
@@ -258,13 +265,6 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
             }
         }
     }
-    if constexpr (ATTN) {
-        // the staged request's query is read right after the barrier: bring it close
-        if (ts.fast && tid < p.hq * 2) {
-            const unsigned char* qrow = reinterpret_cast<const unsigned char*>(p.q) + ((size_t)ts.fast_b * p.hq * 256) + (size_t)tid * 128;
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(qrow));
-        }
-    }
     fstamp(p, 9);
 }
 
@@ -288,32 +288,19 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
     const int nown = c1 - c0 + 1;
     const SelRecord* recs = p.records + (size_t)sg.b * p.grid + c0;
     fstamp(p, 10);
-    // All records of the request in one round trip: 16 eight-byte words each, the first one the header; the
-    // members are kept in registers until the header prefix says where they go.
-    constexpr int kRecWords = 16;
-    constexpr int kPerThread = (kMaxGrid * kRecWords + kFusedThreads - 1) / kFusedThreads;     // 8
-    uint2 w[kPerThread];
+    // headers, and the overflow list's length
     unsigned ovf = 0;
-#pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
-        const int idx = tid + kFusedThreads * u;
-        w[u] = make_uint2(0u, 0u);
-        if (idx < nown * kRecWords) w[u] = __ldcg(reinterpret_cast<const uint2*>(recs) + idx);
+    if (tid < nown) {
+        // a CTA inside the range may own no tile at all (fewer tiles than CTAs): it wrote no record
+        const unsigned c = (unsigned)(c0 + tid);
+        const int lo = max((int)tile_lo(sh, c), sh.tile_off[sg.b]);
+        const int hi = min((int)tile_lo(sh, c + 1u), sh.tile_off[sg.b + 1]);
+        uint2 h = make_uint2(0u, 0u);
+        if (lo < hi) h = __ldcg(reinterpret_cast<const uint2*>(recs + tid));
+        ts.rec_sure[tid] = h.x;
+        ts.rec_off[tid] = h.y;
     }
     if (tid == kFusedThreads - 1) ovf = __ldcg(p.cand_count + sg.b);
-#pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
-        const int idx = tid + kFusedThreads * u;
-        if (idx < nown * kRecWords && (idx & (kRecWords - 1)) == 0) {
-            // a CTA inside the range may own no tile at all (fewer tiles than CTAs): it wrote no record
-            const int r = idx / kRecWords;
-            const unsigned c = (unsigned)(c0 + r);
-            const int lo = max((int)tile_lo(sh, c), sh.tile_off[sg.b]);
-            const int hi = min((int)tile_lo(sh, c + 1u), sh.tile_off[sg.b + 1]);
-            ts.rec_sure[r] = lo < hi ? w[u].x : 0u;
-            ts.rec_off[r] = lo < hi ? w[u].y : 0u;
-        }
-    }
     __syncthreads();
     fstamp(p, 11);
     if (tid < 32) {
@@ -346,11 +333,10 @@ __device__ __forceinline__ Resolved resolve_segment(const LayerParams& p, FusedS
     fstamp(p, 12);
     const unsigned n_inl = ts.n_inl, n_ovf = ts.n_ovf, n_c = n_inl + n_ovf;
     // members: the inline ones always fit the staging area; the list's part when there is room
-#pragma unroll
-    for (int u = 0; u < kPerThread; ++u) {
-        const int idx = tid + kFusedThreads * u;
-        const int r = idx / kRecWords, m = (idx & (kRecWords - 1)) - 1;
-        if (idx < nown * kRecWords && m >= 0 && (unsigned)m < ts.rec_sure[r]) cand_s[ts.rec_off[r] + m] = w[u];
+#pragma unroll 1
+    for (int i = tid; i < nown * kRecInline; i += kFusedThreads) {
+        const int r = i / kRecInline, m = i - r * kRecInline;
+        if ((unsigned)m < ts.rec_sure[r]) cand_s[ts.rec_off[r] + m] = __ldcg(&recs[r].members[m]);
     }
     const uint2* cand_g = p.cand + sh.plan.off[sg.b];
     const bool staged = n_c <= cand_cap;

@@ -300,11 +300,11 @@ class TokenSelectEngine:
         a.req_pool_indices, a.seq_lens = req_pool_indices.data_ptr(), seq_lens.data_ptr()
         a.out = out.data_ptr()
         a.tp_votes, a.tp_cos = _ptr(self.tp_votes), _ptr(self.tp_cos)
-        if debug is not None:
-            a.dbg_sel_slots = debug["slots"].data_ptr()
-            a.dbg_sel_pos = debug["positions"].data_ptr()
-            a.dbg_sel_count = debug["count"].data_ptr()
-            a.dbg_flags = debug["flags"].data_ptr()
+        if debug is not None:                      # any subset of the four inspection outputs
+            a.dbg_sel_slots = _ptr(debug.get("slots"))
+            a.dbg_sel_pos = _ptr(debug.get("positions"))
+            a.dbg_sel_count = _ptr(debug.get("count"))
+            a.dbg_flags = _ptr(debug.get("flags"))
         a.stream = self._stream()
         return a
 
