@@ -380,6 +380,232 @@ def run_config4(args):
         raise SystemExit(3)
 
 
+def run_batch_config(args, which):
+    """Configurations 3 and 5: a BATCH of long requests decoded together, under tensor parallelism by KV head
+    when launched on several GPUs (votes summed inside the selection kernel over NVLink peer memory).
+
+    3: Qwen2-7B attention shape (28 query / 4 KV heads, 28 layers), 16 concurrent requests with lengths
+       log-uniform in [16384, 262144] from a seed; requests finish and new ones join their slots at staggered
+       steps (their selection-cache state is reset as for a new request id).  TP 1, 2 or 4.
+    5: Llama-3-8B shape, 4 requests of 1048576 tokens, top_k 4096, n_local 1024.  TP 4 or 8 with all 32 layers
+       resident; TP 2 holds 16 layers and cycles them (a layer streams far more than L2 from HBM whichever
+       pool it reads, so the per-layer time is that of distinct layers) -- stated in the line.
+
+    One step = one decoded token for every request of the batch through all layers; value = tokens/s of the
+    whole batch.  Before the timed region one layer step is checked against the CPU oracle's tensor-parallel
+    emulation for the shortest request of the batch (every rank must hold the same row list for ALL requests)."""
+    import math
+    import random
+    import torch.distributed as dist
+    from tokenselect_b200 import TokenSelectConfig, TokenSelectEngine
+    from tokenselect_b200 import build as _build
+    _build.build_library()
+    rank = int(os.environ.get("RANK", "0"))
+    tp = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    if tp > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if which == 3:
+        hq_all, hkv_all, layers, top_k, n_local, base, bs, n_spare = 28, 4, 28, TOP_K, N_LOCAL, 1e6, 16, 4
+        rng = random.Random(args.seed)
+        lens0 = [int(math.exp(rng.uniform(math.log(16384), math.log(262144)))) for _ in range(bs + n_spare)]
+        steps = args.steps if args.steps != 256 else 24
+        name = "config 3: qwen2-7b-shape ragged continuous batch"
+    else:
+        hq_all, hkv_all, layers, top_k, n_local, base, bs, n_spare = 32, 8, 32, 4096, 1024, ROPE_BASE, 4, 0
+        lens0 = [args.ctx if args.ctx != 131072 else 1048576] * bs
+        steps = args.steps if args.steps != 256 else 8
+        name = "config 5: llama3-8b-shape one-million-token batch"
+    if args.layers != LAYERS:
+        layers = args.layers
+    if hkv_all % tp != 0:
+        raise SystemExit("the KV heads must divide over the ranks")
+    hq, hkv = hq_all // tp, hkv_all // tp
+    n_sel = N_INIT + top_k + n_local
+    total_steps = args.warmup + steps
+    n_req = bs + n_spare
+    # resident layers: everything when it fits in ~150 GB per GPU, else a cycled subset
+    row_total = sum(lens0) + n_req * (total_steps + 8)
+    bytes_per_layer = 2 * row_total * hkv * D * 2
+    resident = max(1, min(layers, int(150e9 // bytes_per_layer)))
+    g = torch.Generator(device=dev).manual_seed(args.seed)           # same slot map on every rank
+    perm = torch.randperm(row_total, generator=g, device=dev).to(torch.int32)
+    max_ctx = max(lens0) + total_steps + 8
+    rtt = torch.zeros(n_req, max_ctx, dtype=torch.int32, device=dev)
+    at = 0
+    for r, n in enumerate(lens0):
+        rtt[r, : n + total_steps + 8] = perm[at: at + n + total_steps + 8]
+        at += n + total_steps + 8
+    gr = torch.Generator(device=dev).manual_seed(args.seed + 17 * (rank + 1))
+    k_pools, v_pools = [], []
+    for _ in range(resident):
+        k = torch.empty(row_total, hkv, D, dtype=torch.bfloat16, device=dev)
+        v = torch.empty(row_total, hkv, D, dtype=torch.bfloat16, device=dev)
+        ch = torch.randperm(D, generator=gr, device=dev)[:4]
+        for r0 in range(0, row_total, 1 << 20):                      # in slices: the fp32 temporaries stay small
+            r1 = min(row_total, r0 + (1 << 20))
+            t = torch.randn(r1 - r0, hkv, D, generator=gr, device=dev)
+            t[:, :, ch] *= 8
+            k[r0:r1] = t.to(torch.bfloat16)
+            t = torch.randn(r1 - r0, hkv, D, generator=gr, device=dev)
+            t[:, :, ch] *= 8
+            v[r0:r1] = t.to(torch.bfloat16)
+        k_pools.append(k)
+        v_pools.append(v)
+    qs = torch.randn(total_steps, layers, bs, hq * D, generator=gr, device=dev).to(torch.bfloat16)
+    ks = torch.randn(total_steps, layers, bs, hkv * D, generator=gr, device=dev).to(torch.bfloat16)
+    vs = torch.randn(total_steps, layers, bs, hkv * D, generator=gr, device=dev).to(torch.bfloat16)
+    # schedule: which request slot every batch position holds at every step, and the slot's length then
+    slot_of = list(range(bs))
+    cur_len = list(lens0)
+    sched = []
+    spare = list(range(bs, n_req))
+    for t in range(total_steps):
+        if which == 3 and t > 0 and t % 8 == 0 and spare:            # two requests finish, two join their positions
+            for j in range(2):
+                if spare:
+                    pos = (2 * (t // 8 - 1) + j) % bs
+                    slot_of[pos] = spare.pop(0)
+        lens_t = []
+        for pos in range(bs):
+            cur_len[slot_of[pos]] += 1
+            lens_t.append(cur_len[slot_of[pos]])
+        sched.append((list(slot_of), lens_t))
+    ridx_all = torch.tensor([s[0] for s in sched], dtype=torch.int32, device=dev)
+    lens_all = torch.tensor([s[1] for s in sched], dtype=torch.int32, device=dev)
+    locs_all = torch.stack([rtt[ridx_all[t].long(), (lens_all[t] - 1).long()] for t in range(total_steps)]).contiguous()
+    outs = torch.empty(bs, hq * D, dtype=torch.bfloat16, device=dev)
+    cfg = TokenSelectConfig(rope_base=base, max_n_tokens=max_ctx, top_k=top_k, n_init=N_INIT, n_local=n_local,
+                            n_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=D, max_reqs=n_req, max_batch=bs,
+                            max_total_tokens=sum(sorted(lens0)[-bs:]) + bs * (total_steps + 8), tp_rank=rank, tp_size=tp,
+                            tp_fused=not args.tp_split)
+    eng = TokenSelectEngine(cfg, device=dev)
+    for r in range(n_req):
+        eng.reset_request(r)
+    ve = eng.vote_elems_for([max_ctx] * bs, N_INIT, n_local)
+
+    def step(t):
+        if t > 0:
+            for pos in range(bs):                                    # a new request id in the position: fresh state
+                if sched[t][0][pos] != sched[t - 1][0][pos]:
+                    eng.reset_request(sched[t][0][pos])
+        for li in range(layers):
+            eng.decode_layer(li, qs[t, li], ks[t, li], vs[t, li], locs_all[t], k_pools[li % resident], v_pools[li % resident],
+                             rtt, ridx_all[t], lens_all[t], out=outs, vote_elems=ve)
+
+    # ---- untimed check of one layer step against the oracle (shortest request; all requests for rank agreement) ----
+    check = None
+    if not args.no_check:
+        from oracle import tokenselect_oracle as orc
+        dbg = eng.new_debug_buffers(bs)
+        out = eng.decode_layer(0, qs[0, 0], ks[0, 0], vs[0, 0], locs_all[0], k_pools[0], v_pools[0], rtt, ridx_all[0],
+                               lens_all[0], debug=dbg)
+        torch.cuda.synchronize()
+        eng.raise_on_device_error()
+
+        def gather(x):
+            if tp == 1:
+                return [x]
+            parts = [torch.empty_like(x) for _ in range(tp)]
+            dist.all_gather(parts, x.contiguous())
+            return parts
+        all_slots = gather(dbg["slots"])
+        pos_b = min(range(bs), key=lambda i: sched[0][1][i])
+        n_b, slot_b = sched[0][1][pos_b], sched[0][0][pos_b]
+        rows_b = rtt[slot_b, :n_b].long()
+        k_sub = [x.cpu() for x in gather(k_pools[0][rows_b].contiguous())]          # the request's rows, position order
+        v_sub = [x.cpu() for x in gather(v_pools[0][rows_b].contiguous())]
+        q_sub = [x.cpu() for x in gather(qs[0, 0, pos_b].contiguous())]
+        o_sub = [x.cpu() for x in gather(out[pos_b].contiguous())]
+        if rank == 0:
+            check = {"ranks_agree": all(torch.equal(all_slots[0], x) for x in all_slots), "request_tokens": n_b}
+            ocfg = orc.OracleConfig(1, hq_all, hkv_all, D, N_INIT, n_local, top_k, base)
+            q_full = torch.cat([x.view(hq, D) for x in q_sub], dim=0)
+            k_full = torch.cat(k_sub, dim=1)
+            _, want_pos, info = orc.DecodeOracle(ocfg, tp_ranks=tp).select(0, 1, q_full, k_full, torch.arange(n_b, dtype=torch.int32), n_b)
+            got_pos = dbg["positions"][pos_b].cpu()
+            ok, why = orc.index_sets_match(got_pos[N_INIT:N_INIT + top_k].numpy() - N_INIT,
+                                           want_pos[N_INIT:N_INIT + top_k].numpy() - N_INIT,
+                                           info["votes"].double().numpy(), top_k)
+            check["oracle_match"], check["oracle_detail"] = bool(ok), why
+            err = 0.0
+            for r in range(tp):
+                ref = orc.sparse_attention(q_sub[r].view(hq, D), k_sub[r], v_sub[r], got_pos[:n_sel].long(), D ** -0.5, base, 1.0,
+                                           0.0, torch.float64).reshape(-1)
+                err = max(err, (o_sub[r].double() - ref).abs().max().item())
+            check["attn_max_abs_err"] = err
+            check["ok"] = bool(check["ranks_agree"] and ok and err <= 2e-2)
+        flag = torch.tensor([1 if (rank != 0 or check["ok"]) else 0], device=dev)
+        if tp > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            if rank == 0:
+                print(json.dumps({"tp_check": check, "n_gpus": tp, "error": "correctness check failed"}), flush=True)
+            raise SystemExit(3)
+
+    def barrier():
+        if tp > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for t in range(args.warmup):
+        step(t)
+    barrier()
+    eng.raise_on_device_error()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    c0 = eng.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for t in range(args.warmup, total_steps):
+        step(t)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    launches = eng.launch_count - c0
+    eng.raise_on_device_error()
+    if tp > 1:
+        tt = torch.tensor([ms], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    if rank == 0:
+        n_mid = [n + args.warmup + steps // 2 for n in sched[args.warmup][1]]
+        layer_bytes = 0
+        for n in n_mid:
+            nc = n - N_INIT - n_local
+            layer_bytes += nc * hkv * D * 2 + nc * 4 + hq * D * 2 + n_sel * 4 + 2 * n_sel * hkv * D * 2 + n_sel * 4 + 2 * hq * D * 2
+        us_layer = 1e3 * ms / (steps * layers)
+        peak, peak_kind = hbm_peak()
+        line = {
+            "metric": METRIC, "value": bs * steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": tp, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{name}, bs={bs}, lengths {min(lens0)}..{max(lens0)} (sum {sum(sched[args.warmup][1])}), {layers} layers "
+                                   f"({resident} resident{', cycled' if resident < layers else ''}), top_k={top_k}, n_init={N_INIT}, "
+                                   f"n_local={n_local}, page size 1, permuted pool rows",
+                       "parallelism": (f"tp{tp} by KV head, votes summed "
+                                       f"{'in the kernel over NVLink peer memory' if eng.fused_tp else 'by NCCL all-reduce'}")
+                       if tp > 1 else "single GPU",
+                       "l2": "inputs larger than L2: every layer streams its own keys", "launch": "kernels launched from the host"},
+            "us_per_layer": us_layer,
+            "roofline": {"bound": "hbm", "kernel": "decode_step_kernel", "achieved": layer_bytes / (us_layer * 1e-6) / 1e9,
+                         "peak": peak, "unit": "GB/s", "frac": layer_bytes / (us_layer * 1e-6) / 1e9 / peak, "peak_source": peak_kind,
+                         "bytes_per_launch": layer_bytes, "us_per_launch": us_layer, "traffic": None,
+                         "note": "per rank: algorithmic bytes of one layer step of the whole batch over the time of a layer step "
+                                 "(one launch)"},
+            "gpu_launches": int(launches), "clocks": clocks,
+        }
+        if check is not None:
+            line["tp_check"] = check
+        print(json.dumps(line), flush=True)
+    if tp > 1:
+        dist.destroy_process_group()
+
+
 def tensor_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -527,6 +753,9 @@ def main():
         return
     if args.config == 4 and args.impl == "ours":
         run_config4(args)
+        return
+    if args.config in (3, 5) and args.impl == "ours":
+        run_batch_config(args, args.config)
         return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -134,3 +134,97 @@ def test_engine_refuses_to_run_without_a_gpu():
 def test_vote_prefix_bound():
     assert TokenSelectEngine.vote_elems_for([131072], 128, 512) == (131072 - 640 + 127) // 128 * 128
     assert TokenSelectEngine.vote_elems_for([100, 700, 641], 128, 512) == 128 + 128
+
+
+def test_installers_patch_stand_in_serving_classes():
+    """The three patch groups (patcher/token_retrieval.py:452-472, :475-568, :868-883) applied to stand-ins with
+    the attributes the reference reads: the patched runner builds the per-runner state from model_config and
+    the patch() knobs, the patched metadata binds request ids to slots and carries the engine, the patched
+    attention classes route DECODE and EXTEND to it.  No GPU: a recording engine stands in for the CUDA one."""
+    import types
+    from tokenselect_b200 import patcher
+    patcher.patch(rope_base=5e5, max_n_tokens=4096, top_k=256, n_init=16, n_local=64)
+    calls = []
+
+    class FakeEngine:
+        def __init__(self, cfg):
+            self.cfg = cfg
+            self.bound = []
+
+        def bind_requests(self, rids, slots):
+            self.bound.append((list(rids), list(slots)))
+
+        def decode_layer(self, layer, q, k, v, loc, kp, vp, rtt, ridx, lens, vote_elems=None):
+            calls.append(("decode", layer, tuple(q.shape)))
+            return torch.zeros_like(q)
+
+        def extend_chunk(self, layer, q, k, v, loc, kp, vp, rtt, req, seq_len, out=None):
+            calls.append(("extend", layer, q.shape[0], req, seq_len))
+            out.zero_()
+            return out
+
+        @staticmethod
+        def vote_elems_for(lens, n_init, n_local):
+            return 0
+
+    class ModelConfig:
+        num_hidden_layers, head_dim, num_attention_heads = 2, 128, 8
+
+        @staticmethod
+        def get_num_kv_heads(tp_size):
+            return 2 // tp_size
+
+    class ModelRunner:
+        def __init__(self, **kw):
+            self.model_config, self.tp_size, self.tp_rank, self.dtype = ModelConfig(), 1, 0, torch.bfloat16
+            self.req_to_token_pool = patcher.ReqToTokenPool(4, 512, device="cpu")
+            self.token_to_kv_pool = patcher.TokenToKVPool(1024, torch.bfloat16, 2, 128, 2, device="cpu")
+            self.max_total_num_tokens = 1024
+
+    class InputMetadata(patcher.InputMetadata):
+        @classmethod
+        def from_schedule_batch(cls, model_runner, batch, forward_mode):
+            return cls(forward_mode=forward_mode, batch_size=len(batch.reqs), req_pool_indices=batch.req_pool_indices,
+                       seq_lens=batch.seq_lens, req_to_token_pool=model_runner.req_to_token_pool,
+                       token_to_kv_pool=model_runner.token_to_kv_pool, out_cache_loc=batch.out_cache_loc)
+
+    mr_mod, fbi_mod, rot_mod = types.SimpleNamespace(ModelRunner=ModelRunner), types.SimpleNamespace(InputMetadata=InputMetadata), \
+        types.SimpleNamespace(get_rope=lambda *a, **k: object())
+    patcher.patch_model_runner(mr_mod, engine_factory=FakeEngine)
+    patcher.patch_input_metadata(fbi_mod)
+    patcher.patch_rotary_embedding(rot_mod)
+    assert rot_mod.get_rope(128, 128, 4096, 1e6) is None
+    runner = mr_mod.ModelRunner()
+    cfg = runner.req_to_token_retriever.config
+    assert (cfg.n_layers, cfg.num_q_heads, cfg.num_kv_heads, cfg.head_dim) == (2, 8, 2, 128)
+    assert (cfg.top_k, cfg.n_init, cfg.n_local, cfg.max_n_tokens, cfg.max_reqs) == (256, 16, 64, 4096, 4)
+
+    class Attn:                                            # the serving stack's RadixAttention
+        tp_q_head_num, tp_k_head_num, tp_v_head_num, head_dim, qk_head_dim, v_head_dim, layer_id = 8, 2, 2, 128, 128, 128, 1
+
+        def __call__(self, q, k, v, md):
+            return self.forward(q, k, v, md)
+
+    class SelfAttn:                                        # the model's attention module
+        q_size, kv_size = 8 * 128, 2 * 128
+
+        def __init__(self):
+            self.attn = Attn()
+            self.qkv_proj = lambda h: (torch.cat([h, h[:, :512]], dim=-1), None)
+            self.o_proj = lambda a: (a, None)
+
+    model = types.SimpleNamespace(model=types.SimpleNamespace(layers=[types.SimpleNamespace(self_attn=SelfAttn())]))
+    patcher.patch_attention(model)
+    req = types.SimpleNamespace(rid="r-17", prefix_indices=[])
+    batch = types.SimpleNamespace(reqs=[req], req_pool_indices=torch.tensor([3], dtype=torch.int32),
+                                  seq_lens=torch.tensor([700], dtype=torch.int32),
+                                  out_cache_loc=torch.tensor([5], dtype=torch.int32))
+    md = fbi_mod.InputMetadata.from_schedule_batch(runner, batch, patcher.ForwardMode.DECODE)
+    assert md.token_retriever is runner.req_to_token_retriever.engine and md.token_retriever.bound == [(["r-17"], [3])]
+    out = model.model.layers[0].self_attn.forward(None, torch.zeros(1, 1024, dtype=torch.bfloat16), md)
+    assert out.shape == (1, 1024) and calls[-1] == ("decode", 1, (1, 1024))
+    batch.out_cache_loc = torch.arange(600, dtype=torch.int32)
+    md = fbi_mod.InputMetadata.from_schedule_batch(runner, batch, patcher.ForwardMode.EXTEND)
+    out = model.model.layers[0].self_attn.forward(None, torch.zeros(600, 1024, dtype=torch.bfloat16), md)
+    assert out.shape == (600, 1024)
+    assert calls[-2:] == [("extend", 1, 512, 3, 512), ("extend", 1, 88, 3, 600)]      # chunks of 512 (:716-724, :917)

@@ -158,10 +158,13 @@ __device__ __forceinline__ unsigned grid_barrier_generation(const LayerParams& p
 }
 // The arrival and the bounded poll, out of line (one copy for the kernel's five barriers).  Returns true
 // when the wait was given up.
-__device__ __noinline__ bool grid_barrier_poll(unsigned* bar, int* err, long long limit, unsigned gen, bool skip_wait) {
-    const unsigned expected = gridDim.x;
-    const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (expected - 1u)) : 1u;
-    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(bar), "r"(add) : "memory");
+__device__ __noinline__ bool grid_barrier_poll(unsigned* bar, int* err, long long limit, unsigned gen, bool skip_wait,
+                                                bool arrive = true) {
+    if (arrive) {
+        const unsigned expected = gridDim.x;
+        const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (expected - 1u)) : 1u;
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(bar), "r"(add) : "memory");
+    }
     if (skip_wait) return true;
     const long long t0 = clock64();
     unsigned spins = 0, v;
@@ -181,6 +184,23 @@ __device__ __forceinline__ void grid_barrier(const LayerParams& p, bool& dead, u
     __syncthreads();
     if (threadIdx.x == 0) {
         dead = grid_barrier_poll(p.grid_bar, p.err, p.wait_cycles, gen, dead);
+        gen ^= 0x80000000u;
+    }
+    __syncthreads();
+}
+
+// The same barrier in two halves, for work that should start once this CTA's results are published but need
+// not hold the other CTAs up: arrive (after a CTA barrier, thread 0), do the work, then wait.
+__device__ __forceinline__ void grid_barrier_arrive(const LayerParams& p) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned add = (blockIdx.x == 0) ? (0x80000000u - (gridDim.x - 1u)) : 1u;
+        asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p.grid_bar), "r"(add) : "memory");
+    }
+}
+__device__ __forceinline__ void grid_barrier_wait(const LayerParams& p, bool& dead, unsigned& gen) {
+    if (threadIdx.x == 0) {
+        dead = grid_barrier_poll(p.grid_bar, p.err, p.wait_cycles, gen, dead, false);
         gen ^= 0x80000000u;
     }
     __syncthreads();

@@ -247,7 +247,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_step_kernel(const Lay
         if (ok) classify_phase<HKV, true>(p, sh, ring);
 #endif
         stamp(p, 6);
-        grid_barrier(p, dead, bar_gen);
+        grid_barrier_arrive(p);
+        if (ok) issue_staged_rows<HKV>(p, sh, ring);
+        grid_barrier_wait(p, dead, bar_gen);
         stamp(p, 7);
     }
 #ifndef SZL_RESOLVE

@@ -250,22 +250,29 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
         __syncthreads();
         fstamp(p, 8);
     }
-    if constexpr (ATTN) {
-        // request the staged rows: they land while the CTA waits at the next grid barrier
-        if (ts.fast) {
-            const int rows = ts.fast_static + ts.fast_pot;
-            const uint32_t kbase = smem_u32(dyn), vbase = kbase + AG::kRows * AG::kRowS;
-            const uint32_t bar = smem_u32(&ts.kv_bar);
-            asm volatile("fence.proxy.async;" ::: "memory");
-            if (tid == 0) mbar_expect_tx(bar, (uint32_t)rows * 2u * AG::kRowB);
-            if (tid < rows) {
-                const int slot = ts.row_slot[tid];
-                bulk_g2s(kbase + tid * AG::kRowS, reinterpret_cast<const unsigned char*>(p.k_pool) + (size_t)slot * AG::kRowB, AG::kRowB, bar);
-                bulk_g2s(vbase + tid * AG::kRowS, reinterpret_cast<const unsigned char*>(p.v_pool) + (size_t)slot * AG::kRowB, AG::kRowB, bar);
-            }
+    fstamp(p, 9);
+}
+
+// Requests the rows classify_phase staged.  Called after the CTA has ARRIVED at the grid barrier that follows
+// the classification (the copy engine takes ~35 ns per row copy to issue; the other CTAs need not wait for that)
+// and before it waits there: the rows land during the wait.
+template <int HKV>
+__device__ __forceinline__ void issue_staged_rows(const LayerParams& p, FusedShared& sh, unsigned char* dyn) {
+    using AG = AttnGeom<HKV>;
+    const int tid = threadIdx.x;
+    TailScratch& ts = tail_scratch(sh);
+    if (ts.fast) {
+        const int rows = ts.fast_static + ts.fast_pot;
+        const uint32_t kbase = smem_u32(dyn), vbase = kbase + AG::kRows * AG::kRowS;
+        const uint32_t bar = smem_u32(&ts.kv_bar);
+        asm volatile("fence.proxy.async;" ::: "memory");
+        if (tid == 0) mbar_expect_tx(bar, (uint32_t)rows * 2u * AG::kRowB);
+        if (tid < rows) {
+            const int slot = ts.row_slot[tid];
+            bulk_g2s(kbase + tid * AG::kRowS, reinterpret_cast<const unsigned char*>(p.k_pool) + (size_t)slot * AG::kRowB, AG::kRowB, bar);
+            bulk_g2s(vbase + tid * AG::kRowS, reinterpret_cast<const unsigned char*>(p.v_pool) + (size_t)slot * AG::kRowB, AG::kRowB, bar);
         }
     }
-    fstamp(p, 9);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -543,12 +550,15 @@ __device__ __forceinline__ void fill_rotated_query(const LayerParams& p, const T
     }
 }
 
-// One warp: S^T of 16 staged rows x one KV head's query heads.  Arithmetic as attend_split_tc_kernel
-// (attend.cu): rotated query and keys split into bf16 high and low parts, three mma.sync per k-step.  The
-// loops are kept rolled: this code runs once per launch and its cost is the instruction bytes it fetches.
+// One warp: S^T of 16 staged rows x one KV head's query heads on mma.sync, rows in groups of eight (the N of
+// the instruction); a group without rows is skipped.  The rotated query and keys (fp32) go into the tensor
+// cores as fp16: 11 significant bits, i.e. a logit error of a few 1e-4 at these shapes -- an order of magnitude
+// inside what the bf16 output rounding already costs -- for ONE instruction per k-step (the bf16 high/low
+// split of attend.cu needs three; this path is bound by the tensor pipe's rate for mma.sync).  Values beyond
+// the fp16 range saturate.  The loops are kept rolled: this code runs once per launch.
 template <int HKV>
 __device__ __forceinline__ void attend_scores(const LayerParams& p, const unsigned char* sm_k, const float4* sm_cs,
-                                              const float* q_s, int wb, int kv, float (&sc)[2][4]) {
+                                              const float* q_s, int wb, int kv, int rows, float (&sc)[2][4]) {
     using AG = AttnGeom<HKV>;
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -560,39 +570,39 @@ __device__ __forceinline__ void attend_scores(const LayerParams& p, const unsign
 #pragma unroll
         for (int i = 0; i < 4; ++i) sc[j][i] = 0.f;
     const int lrow = lane & 7, lsel = lane >> 3;
+    const int ngroups = min(2, (rows - wb * 16 + 7) >> 3);        // groups of eight rows this block really has
 #pragma unroll 1
     for (int s = 0; s < 4; ++s) {
         // A fragments of k-steps s and s+4 (rows 8..15 of A are unused: zero)
-        uint32_t ah[2][2], al[2][2];
+        uint32_t af[2][2];
 #pragma unroll
         for (int k2 = 0; k2 < 2; ++k2)
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
                 const float2 x = *reinterpret_cast<const float2*>(qh + 16 * (s + 4 * k2) + 8 * u + 2 * t);
-                split_bf16x2(on ? x.x : 0.f, on ? x.y : 0.f, ah[k2][u], al[k2][u]);
+                af[k2][u] = pack_f16x2_sat(on ? x.x : 0.f, on ? x.y : 0.f);
             }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            const float4* cst = sm_cs + (size_t)(wb * 2 + j) * 256;
-            uint32_t r[4];
-            const int doff = 16 * s + (lsel & 1) * 8 + (lsel >> 1) * 64;
-            ldmatrix_x4(r, smem_u32(sm_k) + (wb * 16 + 8 * j + lrow) * AG::kRowS + kv * 256 + doff * 2);
-            uint32_t bh[2][2], bl[2][2];               // [k-step s | s+4][b0 | b1]
+            if (j < ngroups) {
+                const float4* cst = sm_cs + (size_t)(wb * 2 + j) * 256;
+                uint32_t r[4];
+                const int doff = 16 * s + (lsel & 1) * 8 + (lsel >> 1) * 64;
+                ldmatrix_x4(r, smem_u32(sm_k) + (wb * 16 + 8 * j + lrow) * AG::kRowS + kv * 256 + doff * 2);
+                uint32_t bf[2][2];                         // [k-step s | s+4][b0 | b1]
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const float4 cs = cst[((s * 2 + u) * 8 + g) * 4 + t];
-                const float x1a = __uint_as_float(r[u] << 16), x1b = __uint_as_float(r[u] & 0xFFFF0000u);
-                const float x2a = __uint_as_float(r[2 + u] << 16), x2b = __uint_as_float(r[2 + u] & 0xFFFF0000u);
-                split_bf16x2(x1a * cs.x - x2a * cs.y, x1b * cs.z - x2b * cs.w, bh[0][u], bl[0][u]);
-                split_bf16x2(x2a * cs.x + x1a * cs.y, x2b * cs.z + x1b * cs.w, bh[1][u], bl[1][u]);
-            }
+                for (int u = 0; u < 2; ++u) {
+                    const float4 cs = cst[((s * 2 + u) * 8 + g) * 4 + t];
+                    const float x1a = __uint_as_float(r[u] << 16), x1b = __uint_as_float(r[u] & 0xFFFF0000u);
+                    const float x2a = __uint_as_float(r[2 + u] << 16), x2b = __uint_as_float(r[2 + u] & 0xFFFF0000u);
+                    bf[0][u] = pack_f16x2_sat(x1a * cs.x - x2a * cs.y, x1b * cs.z - x2b * cs.w);
+                    bf[1][u] = pack_f16x2_sat(x2a * cs.x + x1a * cs.y, x2b * cs.z + x1b * cs.w);
+                }
 #pragma unroll
-            for (int k2 = 0; k2 < 2; ++k2) {
-                const uint32_t a_hi[4] = {ah[k2][0], 0u, ah[k2][1], 0u};
-                const uint32_t a_lo[4] = {al[k2][0], 0u, al[k2][1], 0u};
-                mma_bf16_16816(sc[j], a_hi, bh[k2][0], bh[k2][1]);
-                mma_bf16_16816(sc[j], a_hi, bl[k2][0], bl[k2][1]);
-                mma_bf16_16816(sc[j], a_lo, bh[k2][0], bh[k2][1]);
+                for (int k2 = 0; k2 < 2; ++k2) {
+                    const uint32_t a4[4] = {af[k2][0], 0u, af[k2][1], 0u};
+                    mma_f16_16816(sc[j], a4, bf[k2][0], bf[k2][1]);
+                }
             }
         }
     }
@@ -737,7 +747,7 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
         const int nblk = rows16 / 16;
         const int wb = warp / HKV, kv = warp % HKV;
         float sc[2][4];
-        if (wb < nblk) attend_scores<HKV>(p, sm_k, reinterpret_cast<const float4*>(cs), part, wb, kv, sc);
+        if (wb < nblk) attend_scores<HKV>(p, sm_k, reinterpret_cast<const float4*>(cs), part, wb, kv, rows, sc);
         __syncthreads();                                   // the rotated query has been read: its place takes the partials
         float* my_o = part + (size_t)warp * G * 130;
         if (wb < nblk) attend_values<HKV>(p, ts, sm_v, wb, kv, rows, sc, my_o, reinterpret_cast<float2*>(my_o + G * 128));

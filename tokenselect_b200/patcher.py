@@ -99,7 +99,7 @@ class ReqToTokenRetriever:
     def __init__(self, num_layers, head_dim, num_heads, num_kv_heads, max_num_tokens, dtype,
                  max_reqs: int = 8, max_batch: int = 8, max_total_tokens: Optional[int] = None,
                  sm_scale: Optional[float] = None, logit_cap: float = 0.0, tp_rank: int = 0,
-                 tp_size: int = 1, process_group=None, device=None):
+                 tp_size: int = 1, process_group=None, device=None, engine_factory=None):
         if TOP_K < 0:
             raise RuntimeError("call patch(...) before building the model runner")
         cfg = TokenSelectConfig(
@@ -109,7 +109,11 @@ class ReqToTokenRetriever:
             num_q_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, dtype=dtype,
             sm_scale=sm_scale, logit_cap=logit_cap, max_reqs=max_reqs, max_batch=max_batch,
             max_total_tokens=max_total_tokens, tp_rank=tp_rank, tp_size=tp_size)
-        self.engine = TokenSelectEngine(cfg, device=device, process_group=process_group)
+        self.config = cfg
+        if engine_factory is not None:
+            self.engine = engine_factory(cfg)
+        else:
+            self.engine = TokenSelectEngine(cfg, device=device, process_group=process_group)
 
     def get_token_retriever(self, req_ids: Sequence[object], req_pool_indices: Sequence[int]) -> TokenSelectEngine:
         """New request id in a slot -> fresh state for that slot (:147-163)."""
@@ -209,3 +213,97 @@ class RadixAttention:
 
     def __call__(self, q, k, v, input_metadata):
         return self.forward(q, k, v, input_metadata)
+
+
+# ---------------------------------------------------------------------------------------------
+# Installers: the three patch groups of the reference, applied to whatever classes a serving stack
+# hands in.  The reference imports SGLang 0.2.13 and patches its classes in place (:452-472, :475-568,
+# :868-883); that package is not a dependency here, so the installers take the module objects (or
+# stand-ins with the same attributes) as arguments.  ``install()`` looks the real modules up.
+# ---------------------------------------------------------------------------------------------
+def patched_meta_attention_forward(self, positions, hidden_states, input_metadata):
+    """Attention module forward without its own rotary embedding (:856-866): q and k reach the patched
+    ``RadixAttention.forward`` un-rotated; the rotation happens inside the selection and attention kernels."""
+    qkv, _ = self.qkv_proj(hidden_states)
+    q, k, v = qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
+    attn_output = self.attn(q, k, v, input_metadata)
+    output, _ = self.o_proj(attn_output)
+    return output
+
+
+def patch_attention(model):
+    """Equivalent of ``patch_attention`` (:700, :868-876): every layer's attention module loses its rotary
+    step and its ``attn`` object gets the patched forward.  Returns the model."""
+    for layer in model.model.layers:
+        layer.self_attn.__class__.forward = patched_meta_attention_forward
+        layer.self_attn.attn.__class__.forward = patched_radix_attention_forward
+    return model
+
+
+def patch_rotary_embedding(rotary_embedding_module):
+    """``get_rope`` returns None, as at :878-881: the model must not rotate q and k itself."""
+    def patched_rotary_embedding_get_rope(*args, **kwargs):
+        return None
+    rotary_embedding_module.get_rope = patched_rotary_embedding_get_rope
+    return rotary_embedding_module
+
+
+def patch_model_runner(model_runner_module, engine_factory=None):
+    """Equivalent of ``patch_model_runner`` (:452-472): ``ModelRunner`` is replaced by a subclass whose
+    constructor also builds the per-runner ``req_to_token_retriever`` from ``model_config`` (layers, head_dim,
+    attention heads and this rank's KV heads) and the ``patch()`` knobs.  ``engine_factory`` replaces the CUDA
+    engine in tests without a GPU."""
+    base = model_runner_module.ModelRunner
+
+    class PatchedModelRunner(base):
+        def __init__(self, **kwargs):
+            super().__init__(**kwargs)
+            mc = self.model_config
+            tp_size = getattr(self, "tp_size", 1)
+            self.req_to_token_retriever = ReqToTokenRetriever(
+                mc.num_hidden_layers, mc.head_dim, mc.num_attention_heads // tp_size, mc.get_num_kv_heads(tp_size),
+                MAX_N_TOKENS, self.dtype,
+                max_reqs=int(self.req_to_token_pool.req_to_token.shape[0]),
+                max_batch=int(getattr(self, "max_running_requests", 8) or 8),
+                max_total_tokens=int(getattr(self, "max_total_num_tokens", 0)) or None,
+                tp_rank=getattr(self, "tp_rank", 0), tp_size=tp_size, engine_factory=engine_factory)
+
+    model_runner_module.ModelRunner = PatchedModelRunner
+    return PatchedModelRunner
+
+
+def patch_input_metadata(forward_batch_info_module):
+    """Equivalent of ``patch_input_metadata`` (:475-568): ``InputMetadata.from_schedule_batch`` additionally
+    binds the batch's request ids to their request slots (a new id in a slot gets fresh selection state,
+    :147-163) and carries the runner's engine as ``token_retriever``.  No third-party attention wrappers are
+    planned and no sequence lengths are copied to the host (:570-625 is not needed: the kernels read
+    ``req_to_token`` directly)."""
+    base = forward_batch_info_module.InputMetadata
+
+    class PatchedInputMetadata(base):
+        token_retriever = None
+
+        @classmethod
+        def from_schedule_batch(cls, model_runner, batch, forward_mode):
+            ret = super().from_schedule_batch(model_runner, batch, forward_mode)
+            slots = batch.req_pool_indices.tolist() if hasattr(batch.req_pool_indices, "tolist") else list(batch.req_pool_indices)
+            ret.token_retriever = model_runner.req_to_token_retriever.get_token_retriever(
+                [r.rid for r in batch.reqs], slots)
+            ret.req_pool_indices_cpu = slots
+            if getattr(forward_mode, "name", str(forward_mode)) != "DECODE":
+                ret.extend_prefix_lens_cpu = [len(r.prefix_indices) for r in batch.reqs]
+            return ret
+
+    forward_batch_info_module.InputMetadata = PatchedInputMetadata
+    return PatchedInputMetadata
+
+
+def install():
+    """Apply the three patch groups to an installed SGLang (the reference pins 0.2.13, README.md:42).  Raises
+    ImportError when it is absent."""
+    import sglang.srt.model_executor.forward_batch_info as fbi
+    import sglang.srt.model_executor.model_runner as mr
+    from sglang.srt.layers import rotary_embedding as rot       # noqa: F401  (location in 0.2.13: vllm's module)
+    patch_input_metadata(fbi)
+    patch_model_runner(mr)
+    patch_rotary_embedding(rot)
