@@ -862,12 +862,15 @@ def main():
                 dist.destroy_process_group()
             raise SystemExit(3)
 
+    launches_per_token = 3 * layers
     for i in range(args.warmup):
+        c0 = eng.launch_count
         step(i)
+        launches_per_token = eng.launch_count - c0                  # counted by the library, one per kernel launch
     barrier()
     eng.raise_on_device_error()
 
-    # Single GPU: the 3 x layers launches of a token are captured once as a CUDA graph (the calls enqueue on
+    # Single GPU: the launches of a token (one per layer where the layer-step kernel applies, else three) are captured once as a CUDA graph (the calls enqueue on
     # the capturing stream, nothing in them synchronises or allocates) and replayed per token; the token's
     # inputs are first copied into the buffers the graph was captured on.  Under tensor parallelism this holds
     # for the form that exchanges votes inside the kernel (the NCCL form has host-driven collectives between
@@ -878,7 +881,6 @@ def main():
     sq, sk, sv = sqkv[..., :hq * D], sqkv[..., hq * D:(hq + hkv) * D], sqkv[..., (hq + hkv) * D:]
     smeta = torch.zeros(2, dtype=torch.int32, device=dev)           # pool row of the new token, sequence length
     sloc, slens = smeta[0:1], smeta[1:2]
-    launches_per_token = 3 * layers
     graph = None
     if use_graph:
         qkv_all = torch.cat([qs, ks, vs], dim=-1).contiguous()       # [steps, layers, 1, d_in]
@@ -1031,11 +1033,15 @@ def main():
     if rank == 0:
         ab = algorithmic_bytes(ctx + args.warmup + args.steps // 2, hq, hkv, D)
         peak, peak_kind = hbm_peak()
-        # dominant kernel: the fused selection kernel (under tensor parallelism: its two parts)
+        # dominant kernel: one launch per layer means the layer-step kernel did the whole layer (selection,
+        # attention, merge), and its algorithmic bytes are the layer's; otherwise the selection kernel (under the
+        # NCCL form of tensor parallelism: its two parts) and the selection's bytes
+        one_launch = launches_per_token == layers
         score_ms, score_n = stages["select"]
         score_ms += stages["select_tp_b"][0]
         score_us = 1e3 * score_ms / max(score_n, 1)
-        achieved = ab["select"] / (score_us * 1e-6) / 1e9 if score_n else None
+        kernel_bytes = ab["layer"] if one_launch else ab["select"]
+        achieved = kernel_bytes / (score_us * 1e-6) / 1e9 if score_n else None
         us_layer = 1e3 * ms / (args.steps * layers)
         per_stage_us = {k: round(1e3 * v[0] / max(v[1], 1), 3) for k, v in stages.items() if v[1]}
         line = {
@@ -1055,11 +1061,12 @@ def main():
                                "frac_of_measured_copy": ab["layer"] / (us_layer * 1e-6) / 1e9 / peak,
                                "frac_of_8tbs": ab["layer"] / (us_layer * 1e-6) / 1e9 / 8000.0},
             "kernel_us": per_stage_us,
-            "roofline": {"bound": "hbm", "kernel": "fused_select_kernel", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "decode_step_kernel" if one_launch else "fused_select_kernel",
+                         "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
-                         "peak_source": peak_kind, "bytes_per_launch": ab["select"],
+                         "peak_source": peak_kind, "bytes_per_launch": kernel_bytes,
                          "us_per_launch": score_us,
-                         "traffic": (ab["select"] * SELECT_DRAM_BYTES_PER_ALGORITHMIC_BYTE) if tp == 1 else None,
+                         "traffic": (kernel_bytes * SELECT_DRAM_BYTES_PER_ALGORITHMIC_BYTE) if tp == 1 else None,
                          "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel "
                                             "at this shape under ncu (a separate run), scaled by the algorithmic bytes "
                                             "of this run's sequence length; not measured in this run")

@@ -24,49 +24,65 @@ def _ar1_queries(seed, steps, hq, d, rho, dtype):
     return q.to(dtype)
 
 
-@pytest.mark.parametrize("dtype,rho,theta", [(BF16, 0.95, 0.9), (BF16, 0.8, 0.85), (F32, 0.99, 0.95)],
-                         ids=["bf16_rho95", "bf16_rho80", "fp32_rho99"])
+_PAIRS = [(rho, theta) for rho in (0.80, 0.95, 0.99) for theta in (0.85, 0.90, 0.95)]
+
+
+@pytest.mark.parametrize("dtype,rho,theta",
+                         [(F32 if (rho, theta) in ((0.99, 0.95), (0.80, 0.90)) else BF16, rho, theta) for rho, theta in _PAIRS],
+                         ids=[f"rho{int(r * 100)}_theta{int(t * 100)}" for r, t in _PAIRS])
 def test_selection_cache_decisions_are_bit_exact(dtype, rho, theta):
     """Reuse / recompute decisions per (request, layer, step) equal the oracle's replay of the same
-    fixed-order fp32 cosine; the sequence grows by one token per step; two layers keep separate state."""
+    fixed-order fp32 cosine, for every (rho, threshold) pair of the cache-stress configuration; the sequence
+    grows by one token per step; two layers keep separate state.  A query sequence with a step inside the 1e-5
+    band around the threshold (where fp32 and fp64 may disagree) is replaced by the next seed's, never skipped."""
     hq, hkv, d, n_init, n_local, k, base = 8, 2, 128, 16, 64, 256, 5e5
     n0, steps, layers = 1200, 20, 2
     case = synth.make_layer_case(55, n0 + steps, hq, hkv, d, n_init, n_local, base, dtype=dtype)
-    qs = _ar1_queries(56, steps, hq, d, rho, dtype)
     eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, dtype, n_layers=layers, max_ctx=n0 + steps + 8,
                          query_cache=True, similarity_threshold=theta)
-    o = orc.DecodeOracle(gu.oracle_config(eng))
     _, kp, vp, rtt, ridx, _ = gu.case_tensors(case)
-    eng.reset_request(case.req_pool_idx)
-    o.reset_request(case.req_pool_idx)
-    reuse = 0
-    checked = 0
-    for t in range(steps):
-        lens = torch.tensor([n0 + t])
-        for layer in range(layers):
-            q = (qs[t] if layer == 0 else -qs[t].flip(0))[None].contiguous()
-            out, res = gu.run_gpu(eng, layer, q, kp, vp, rtt, ridx, lens)
-            ref = o.decode_layer(layer, q, None, None, None, kp, vp, rtt, ridx, lens)
-            cos = ref["info"][0].get("cos")
-            if cos is not None and abs(cos - theta) < 1e-5:
-                pytest.skip("a step fell inside the 1e-5 band around the threshold; pick another seed")
-            assert int(res["flags"][0]) == ref["flags"][0], f"step {t} layer {layer}: cos={cos}"
-            checked += 1
-            if ref["flags"][0] == orc.FLAG_REUSE:
-                reuse += 1
-                assert torch.equal(res["positions"][0, : eng.cfg.n_sel].long(), ref["positions"][0])
-            else:
-                gu.check_selection(eng, res, 0, ref["positions"][0], ref["info"][0]["votes"], n0 + t)
-                # keep both caches on the same index set even if a tie-band index differs
-                o.cache[(case.req_pool_idx, layer)].topk_positions = \
-                    res["positions"][0, n_init: n_init + k].long().clone()
-            want = orc.sparse_attention(q.view(hq, d), kp, vp, res["slots"][0, : eng.cfg.n_sel], d ** -0.5, base,
-                                        1.0, 0.0, torch.float64).reshape(-1)
-            assert (out[0].double() - want).abs().max().item() <= (2e-2 if dtype == BF16 else 1e-5)
-    retr, skips = eng.counters(case.req_pool_idx)
-    assert retr == checked == o.retrieval_count[case.req_pool_idx]
-    assert skips == reuse == o.skip_count[case.req_pool_idx]
-    if rho >= 0.95:
+
+    def run(seed):
+        qs = _ar1_queries(seed, steps, hq, d, rho, dtype)
+        o = orc.DecodeOracle(gu.oracle_config(eng))
+        eng.reset_request(case.req_pool_idx)
+        o.reset_request(case.req_pool_idx)
+        reuse = checked = 0
+        for t in range(steps):
+            lens = torch.tensor([n0 + t])
+            for layer in range(layers):
+                q = (qs[t] if layer == 0 else -qs[t].flip(0))[None].contiguous()
+                out, res = gu.run_gpu(eng, layer, q, kp, vp, rtt, ridx, lens)
+                ref = o.decode_layer(layer, q, None, None, None, kp, vp, rtt, ridx, lens)
+                cos = ref["info"][0].get("cos")
+                if cos is not None and abs(cos - theta) < 1e-5:
+                    return None                                # inside the band: try the next seed
+                assert int(res["flags"][0]) == ref["flags"][0], f"seed {seed} step {t} layer {layer}: cos={cos}"
+                checked += 1
+                if ref["flags"][0] == orc.FLAG_REUSE:
+                    reuse += 1
+                    assert torch.equal(res["positions"][0, : eng.cfg.n_sel].long(), ref["positions"][0])
+                else:
+                    gu.check_selection(eng, res, 0, ref["positions"][0], ref["info"][0]["votes"], n0 + t)
+                    # keep both caches on the same index set even if a tie-band index differs
+                    o.cache[(case.req_pool_idx, layer)].topk_positions = \
+                        res["positions"][0, n_init: n_init + k].long().clone()
+                want = orc.sparse_attention(q.view(hq, d), kp, vp, res["slots"][0, : eng.cfg.n_sel], d ** -0.5, base,
+                                            1.0, 0.0, torch.float64).reshape(-1)
+                assert (out[0].double() - want).abs().max().item() <= (2e-2 if dtype == BF16 else 1e-5)
+        retr, skips = eng.counters(case.req_pool_idx)
+        assert retr == checked == o.retrieval_count[case.req_pool_idx]
+        assert skips == reuse == o.skip_count[case.req_pool_idx]
+        return reuse, qs
+
+    done = None
+    for seed in range(56, 64):
+        done = run(seed)
+        if done is not None:
+            break
+    assert done is not None, "eight query sequences in a row had a step inside the 1e-5 band"
+    reuse, qs = done
+    if rho >= 0.95 and theta <= 0.9:
         assert reuse > 0, "expected some reuse at this correlation"
     # a new request in the slot starts from scratch
     eng.reset_request(case.req_pool_idx)

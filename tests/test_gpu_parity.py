@@ -33,6 +33,11 @@ SHAPES = [
     ("direct_llama_tp4", 8, 2, 128, 3000, 16, 64, 256, 5e5, BF16, {"score_path": "direct"}),
     ("direct_llama_tp8", 4, 1, 128, 5000, 16, 64, 256, 5e5, BF16, {"score_path": "direct"}),
     ("plain_bf16", 8, 2, 128, 2048, 16, 64, 256, 5e5, BF16, {"plain_score": True}),
+    # the general selection kernel followed by the stand-alone attention kernels (TS_CFG_SPLIT_ATTEND) at shapes
+    # that default to the single layer-step kernel
+    ("split_attend_llama_tp1", 32, 8, 128, 8192, 128, 512, 1024, 5e5, BF16, {"extra_flags": 256}),
+    ("split_attend_qwen_tp4", 7, 1, 128, 3001, 16, 64, 300, 1e6, BF16, {"extra_flags": 256}),
+    ("softcap_bf16", 8, 2, 128, 1500, 16, 64, 256, 5e5, BF16, {"logit_cap": 30.0}),
     ("fp32_check", 32, 8, 128, 8192, 128, 512, 1024, 5e5, F32, {}),
     ("fp32_d64_mha", 4, 4, 64, 1024, 8, 32, 128, 1e4, F32, {}),
     ("softcap_fp32", 8, 2, 128, 1500, 16, 64, 256, 5e5, F32, {"logit_cap": 30.0}),

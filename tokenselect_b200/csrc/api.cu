@@ -339,8 +339,6 @@ int ts_create(const ts_config* cfg, ts_handle** out) {
     if (cudaMalloc(&h->arena, h->arena_bytes) != cudaSuccess) { delete h; return TS_ERR_CUDA; }
     layout(cfg, h->num_sms, h);
     h->base.wait_cycles = h->wait_cycles;
-    h->base.diag_no_side = (cfg->flags & 64u) ? 1 : 0;
-    h->base.diag_plain_hist = (cfg->flags & 128u) ? 1 : 0;
     const LayerParams& p = h->base;
     const int half = cfg->head_dim / 2;
     cudaError_t e = cudaMemset(h->arena, 0, h->arena_bytes);

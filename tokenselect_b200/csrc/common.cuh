@@ -21,7 +21,7 @@ constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stag
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
 constexpr int kFlagPad = 256;          // per-CTA flags per (parity, source rank) in the tensor-parallel flag pad
 constexpr int kMaxTp = 8;
-constexpr int kFusedDynSmem = 196608; // dynamic shared memory of the selection kernel (5 stages of 34 KB; the tail needs more)
+constexpr int kFusedDynSmem = 196608;    // dynamic shared memory of the selection kernels (5 stages of 34 KB; the tail needs more)
 constexpr int kAttnThreads = 256;
 constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
 
@@ -96,7 +96,6 @@ struct LayerParams {
     unsigned long long* counters;  // [max_reqs, 2] retrievals, reuses
     int* err;                  // [2] sticky (code, detail)
     long long wait_cycles;     // bound of every device-side wait, in SM clock cycles
-    int diag_no_side, diag_plain_hist;
     // attention inside the selection kernel
     int attn_inline;               // 1: phases 5 and 6 run in the selection kernel, no attention kernels follow
     struct SelRecord* records;     // [max_batch, grid] what each CTA found for each request (phase 3)

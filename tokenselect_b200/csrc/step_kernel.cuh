@@ -60,37 +60,32 @@ __device__ __forceinline__ void vote_phase_lean(const LayerParams& p, FusedShare
             __syncthreads();
             fstamp(p, 0);
             if (first) {
-                // softmax statistics of the request: every CTA's (max, sum exp) merged in two levels; head c then
-                // contributes exp2(x*log2e + bias_c) with bias_c = shift - (M_c*log2e + log2 L_c)
-                const int nsl = min(kFusedThreads / hq, 16);          // slices per head
-                const int sl = tid / hq, c = tid - sl * hq;
-                float2* lvl = reinterpret_cast<float2*>(sh.idx);       // [nsl][hq] scratch
-                if (sl < nsl) {
-                    float m = -INFINITY, l = 0.f;
+                // softmax statistics of the request: every CTA's (max, sum exp); sixteen consecutive lanes share a
+                // head, each takes every sixteenth CTA, a butterfly joins them; head c then contributes
+                // exp2(x*log2e + bias_c) with bias_c = shift - (M_c*log2e + log2 L_c)
+                auto join = [](float& m, float& l, float mo, float lo) {
+                    const float mn = fmaxf(m, mo);
+                    if (mn > -INFINITY)
+                        l = l * ex2_ftz(fmaxf((m - mn) * kLog2e, -126.f)) + lo * ex2_ftz(fmaxf((mo - mn) * kLog2e, -126.f));
+                    m = mn;
+                };
 #pragma unroll 1
-                    for (int i = sl; i < p.grid; i += nsl) {
-                        const float2 v = part_s[i * hq + c];
-                        if (v.x > -INFINITY) {
-                            const float mn = fmaxf(m, v.x);
-                            l = l * ex2_ftz(fmaxf((m - mn) * kLog2e, -126.f)) + v.y * ex2_ftz(fmaxf((v.x - mn) * kLog2e, -126.f));
-                            m = mn;
+                for (int h0 = 0; h0 < hq; h0 += kFusedThreads / 16) {
+                    const int h = h0 + (tid >> 4), sl = tid & 15;
+                    float m = -INFINITY, l = 0.f;
+                    if (h < hq) {
+#pragma unroll 1
+                        for (int i = sl; i < p.grid; i += 16) {
+                            const float2 v = part_s[i * hq + h];
+                            join(m, l, v.x, v.y);
                         }
                     }
-                    lvl[sl * hq + c] = make_float2(m, l);
-                }
-                __syncthreads();
-                if (tid < hq) {
-                    float m = -INFINITY, l = 0.f;
-#pragma unroll 1
-                    for (int i = 0; i < nsl; ++i) {
-                        const float2 v = lvl[i * hq + tid];
-                        if (v.x > -INFINITY) {
-                            const float mn = fmaxf(m, v.x);
-                            l = l * ex2_ftz(fmaxf((m - mn) * kLog2e, -126.f)) + v.y * ex2_ftz(fmaxf((v.x - mn) * kLog2e, -126.f));
-                            m = mn;
-                        }
+#pragma unroll
+                    for (int o = 8; o >= 1; o >>= 1) {
+                        const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo = __shfl_xor_sync(0xffffffffu, l, o);
+                        join(m, l, mo, lo);
                     }
-                    sh.s_m[tid] = kVoteShift - (m * kLog2e + log2f(l));
+                    if (sl == 0 && h < hq) sh.s_m[h] = kVoteShift - (m * kLog2e + log2f(l));
                 }
                 __syncthreads();
             }
@@ -172,22 +167,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_step_kernel(const Lay
 #pragma unroll 1
         for (int b = blockIdx.x; b < p.batch; b += gridDim.x) {
             if (err0 != 0) break;
-#ifndef SZL_PREP
             prepare_request<T, true>(p, b, sh.prep, whole_cta());
-#endif
         }
         grid_barrier(p, dead, bar_gen);
     }
-#ifndef SZL_PLAN
     bool ok = side ? build_plan<true>(p, sh.plan) : build_plan<false>(p, sh.plan);
-#else
-    bool ok = true;
-#endif
     ok = ok && err0 == 0;
     if (tid == 0) {
-#ifndef SZL_OWN
         plan_ownership(p, sh, ok, true, AttnGeom<HKV>::kRows, true);
-#endif
         mbar_init(smem_u32(&sh.stage_bar), 1);
 #pragma unroll 1
         for (int s = 0; s < kScoreStages; ++s) {
@@ -202,12 +189,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_step_kernel(const Lay
     float* votes_raw = tp_fused ? p.peer_votes[(sh.epoch & 1u) * kMaxTp + p.tp_rank] : p.votes;
     stamp(p, 1);
     const bool nothing_to_score = sh.tile_off[p.batch] == 0;
-#ifndef SZL_SIDEW
     if (side && (nothing_to_score || !ok)) side_work<T>(p, sh, mode, err0, ok, whole_cta());
-#endif
-#ifndef SZL_EW
     if (!side && ok) emit_windows(p, sh, whole_cta());
-#endif
     if (!nothing_to_score) {
         if (ok) {
             if (!side) {
@@ -221,46 +204,37 @@ __global__ void __launch_bounds__(kFusedThreads, 1) decode_step_kernel(const Lay
                         p.partials[(size_t)b * p.part_stride + (size_t)blockIdx.x * p.hq + c] = make_float2(-INFINITY, 0.f);
                 }
             }
-#ifndef SZL_SCORE
             score_phase_tma<T, HKV, (HKV > kBulkMinHkv)>(p, sh, ring, dead, side, mode, err0);
-#endif
             vote_prefetch(p, sh, ring);
         }
         stamp(p, 2);
         if (p.stamps) stamp_range_slow(p.phase_ts, 1);
         grid_barrier(p, dead, bar_gen);
         stamp(p, 3);
-#ifndef SZL_VOTE
         if (ok) vote_phase_lean(p, sh, ring, !tp_fused, stage_parity, dead, votes_raw);
-#endif
         stamp(p, 4);
-#ifndef SZL_TPX
         if (tp_fused) tp_exchange_phase(p, sh, ring, ok, dead);
-#endif
         stamp(p, 24);
         grid_barrier(p, dead, bar_gen);
         stamp(p, 5);
     }
     tail_init(p, sh);
     if (!nothing_to_score) {
-#ifndef SZL_CLASSIFY
         if (ok) classify_phase<HKV, true>(p, sh, ring);
-#endif
         stamp(p, 6);
         grid_barrier_arrive(p);
-        if (ok) issue_staged_rows<HKV>(p, sh, ring);
+        if (ok) {
+            issue_staged_rows<HKV>(p, sh, ring);
+            early_prepare<HKV>(p, sh, ring);
+        }
         grid_barrier_wait(p, dead, bar_gen);
         stamp(p, 7);
     }
-#ifndef SZL_RESOLVE
     if (ok) resolve_and_attend<HKV, true>(p, sh, ring, dead);
-#endif
     stamp(p, 8);
     grid_barrier(p, dead, bar_gen);
     stamp(p, 15);
-#ifndef SZL_MERGE
     if (ok) merge_phase(p, sh);
-#endif
     stamp(p, 16);
     if (p.stamps) stamp_range_slow(p.phase_ts, 2);
 }

@@ -26,7 +26,7 @@
 
 namespace ts {
 
-constexpr int kRecInline = 15;               // members of the threshold bin a record holds itself
+constexpr int kRecInline = 12;               // members of the threshold bin a record holds itself
 constexpr unsigned kRecOverflow = 0x80000000u;
 constexpr int kAttnRowsMax = 64;             // rows one attention round stages in shared memory
 constexpr int kMaxGrid = 256;
@@ -35,7 +35,7 @@ constexpr int kDirectRankMax = 128;          // members ranked by direct compari
 struct alignas(128) SelRecord {
     unsigned sure;                           // winners above the threshold bin in this CTA's range
     unsigned n_members;                      // members of the bin in the range (| kRecOverflow: in the global list)
-    uint2 members[kRecInline];               // (candidate index, vote bits)
+    uint2 members[15];                       // (candidate index, vote bits); the first kRecInline are used
 };
 static_assert(sizeof(SelRecord) == 128, "one record is one 128-byte line");
 
@@ -124,20 +124,13 @@ __device__ __forceinline__ void static_row(const LayerParams& p, const FusedShar
     else pos = n - p.n_local + (list_idx - p.n_init - p.top_k);
 }
 
-// Diagnostic: an address that is not aligned as its access needs is recorded (9000 + site) instead of used.
-__device__ __forceinline__ bool aligned_or_report(const LayerParams& p, const void* a, unsigned mask, int site) {
-    if ((reinterpret_cast<unsigned long long>(a) & mask) == 0ull) return true;
-    set_error(p.err, TS_ERR_INTERNAL, 9000 + site);
-    return false;
-}
-
 // Called by all threads before the first use of the tail's scratch.
 __device__ __forceinline__ void tail_init(const LayerParams& p, FusedShared& sh) {
     TailScratch& ts = tail_scratch(sh);
     __syncthreads();                                   // the area's previous users are done
     if (threadIdx.x >= 64 && threadIdx.x < 128 && p.attn_inline) ts.inv_freq[threadIdx.x - 64] = p.attn_inv_freq[threadIdx.x - 64];
     if (threadIdx.x == 0) {
-        ts.fast = 0; ts.fast_static = 0; ts.fast_pot = 0; ts.fast_b = -1;
+        ts.fast = 0; ts.fast_static = 0; ts.fast_pot = 0; ts.fast_b = -1; ts.pad = 0u;
         mbar_init(smem_u32(&ts.kv_bar), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -185,17 +178,9 @@ __device__ __forceinline__ void classify_phase(const LayerParams& p, FusedShared
         const float* votes_g = p.votes_final + sh.plan.off[sg.b];
         int own0, own1, per;
         own_range(sg.t0, sg.t1, own0, own1, per);
-        // the request's histogram
-        unsigned hreg[kHistBins / kFusedThreads];
-#pragma unroll
-        for (int i = 0; i < kHistBins / kFusedThreads; ++i)
-            hreg[i] = __ldcg(p.hist + (size_t)sg.b * kHistBins + tid + kFusedThreads * i);
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < kHistBins / kFusedThreads; ++i) sh.hist[tid + kFusedThreads * i] = hreg[i];
-        __syncthreads();
+        // the bin of the k-th vote, from the request's histogram
         fstamp(p, 5);
-        find_threshold(sh, (unsigned)p.top_k);
+        find_threshold_global(sh, p.hist + (size_t)sg.b * kHistBins, (unsigned)p.top_k);
         fstamp(p, 6);
         const unsigned b1 = (unsigned)sh.res_bin;
         if (tid == 0) { sh.seg_b1[s] = sh.res_bin; sh.seg_above[s] = sh.res_above; sh.seg_cnt[s] = sh.res_cnt; }
@@ -273,6 +258,33 @@ __device__ __forceinline__ void issue_staged_rows(const LayerParams& p, FusedSha
             bulk_g2s(vbase + tid * AG::kRowS, reinterpret_cast<const unsigned char*>(p.v_pool) + (size_t)slot * AG::kRowB, AG::kRowB, bar);
         }
     }
+}
+
+// Where the threshold bin's members are staged when the attention's inputs are prepared early: behind the
+// partial outputs, running into the shared-memory copies of the CTA's own votes and pool rows (no longer
+// needed once the possible winners are staged).
+template <int HKV>
+__device__ __forceinline__ int early_cand_offset(const LayerParams& p) {
+    using AG = AttnGeom<HKV>;
+    return (AG::kPartOff + attn_part_bytes(AG::kWarpsBusy, p.group) + 15) & ~15;
+}
+
+template <int HKV> __device__ __forceinline__ void attend_prepare(const LayerParams& p, FusedShared& sh, unsigned char* dyn, int b,
+                                                                  int rows, int cs_rows, int tid0, int nthr);
+
+// While the CTA waits at the grid barrier after the classification: everything the attention over the staged
+// rows needs except the winners' final list positions (rotated query, zeros in unused rows, rotation rows of the
+// window rows).  Only when the members of all records are sure to fit their alternative staging place.
+template <int HKV>
+__device__ __forceinline__ void early_prepare(const LayerParams& p, FusedShared& sh, unsigned char* dyn) {
+    TailScratch& ts = tail_scratch(sh);
+    if (ts.fast == 0 || sh.nseg != 1) return;     // (a second segment would still read the own-vote copies)
+    int c0, c1;
+    owner_range(p, sh, ts.fast_b, c0, c1);
+    const int room = (kFusedDynSmem - early_cand_offset<HKV>(p)) / 8;
+    if ((c1 - c0 + 1) * kRecInline > room) return;
+    attend_prepare<HKV>(p, sh, dyn, ts.fast_b, ts.fast_static + ts.fast_pot, ts.fast_static, 0, kFusedThreads);
+    if (threadIdx.x == 0) ts.pad = 1u;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -523,9 +535,10 @@ constexpr int kQStride = 136;            // floats per head of the staged rotate
 // Rotation rows of the staged rows' list positions, in the order the lanes of the multiplying warps read them:
 // positions in tiles of eight; inside a tile the (cos, sin) of frequency i = 16s + 8u + 2t + w of position g
 // sits in float2 (((s*2+u)*8 + g)*4 + t)*2 + w.
-__device__ __forceinline__ void fill_rotation_rows(const LayerParams& p, const TailScratch& ts, float2* cs, int rows) {
+__device__ __forceinline__ void fill_rotation_rows(const LayerParams& p, const TailScratch& ts, float2* cs, int row0, int row1,
+                                                   int tid0 = 0, int nthr = kFusedThreads) {
 #pragma unroll 1
-    for (int idx = threadIdx.x; idx < rows * 64; idx += kFusedThreads) {
+    for (int idx = row0 * 64 + (int)threadIdx.x - tid0; idx < row1 * 64; idx += nthr) {
         const int r = idx >> 6, i = idx & 63;
         const int rank = max(ts.row_rank[r], 0);
         float sn, cn;
@@ -538,9 +551,9 @@ __device__ __forceinline__ void fill_rotation_rows(const LayerParams& p, const T
 
 // The request's query rotated at position count-1, fp32, [hq][kQStride] in shared memory.
 __device__ __forceinline__ void fill_rotated_query(const LayerParams& p, const TailScratch& ts, const __nv_bfloat16* q_b, int count,
-                                                   float* q_s) {
+                                                   float* q_s, int tid0 = 0, int nthr = kFusedThreads) {
 #pragma unroll 1
-    for (int idx = threadIdx.x; idx < p.hq * 64; idx += kFusedThreads) {
+    for (int idx = (int)threadIdx.x - tid0; idx < p.hq * 64; idx += nthr) {
         const int h = idx >> 6, i = idx & 63;
         float sn, cn;
         sincos_reduced(__fmul_rn((float)(count - 1), ts.inv_freq[i]), sn, cn);
@@ -548,6 +561,32 @@ __device__ __forceinline__ void fill_rotated_query(const LayerParams& p, const T
         q_s[h * kQStride + i] = x1 * cn - x2 * sn;
         q_s[h * kQStride + i + 64] = x2 * cn + x1 * sn;
     }
+}
+
+// What the attention over a round's staged rows needs besides the rows' final list positions: zeros in the
+// unused rows of the last, partly filled block (0-weight products must stay finite), "not attended" marks for
+// them, the rotated query, and (from row `cs_rows` down) the rotation rows of positions already known.  Run
+// by the threads tid0 .. tid0 + nthr - 1.
+template <int HKV>
+__device__ __forceinline__ void attend_prepare(const LayerParams& p, FusedShared& sh, unsigned char* dyn, int b, int rows,
+                                               int cs_rows, int tid0, int nthr) {
+    using AG = AttnGeom<HKV>;
+    const int t = (int)threadIdx.x - tid0;
+    TailScratch& ts = tail_scratch(sh);
+    unsigned char* sm_k = dyn;
+    unsigned char* sm_v = dyn + AG::kRows * AG::kRowS;
+    const int rows16 = (rows + 15) / 16 * 16;
+#pragma unroll 1
+    for (int i = rows * (AG::kRowB / 16) + t; i < rows16 * (AG::kRowB / 16); i += nthr) {
+        const int r = i / (AG::kRowB / 16), c = i - r * (AG::kRowB / 16);
+        *reinterpret_cast<uint4*>(sm_k + r * AG::kRowS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(sm_v + r * AG::kRowS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (t >= rows && t < rows16) ts.row_rank[t] = -1;
+    const int count = min(sh.plan.n[b], p.n_sel);
+    fill_rotated_query(p, ts, reinterpret_cast<const __nv_bfloat16*>(p.q) + (size_t)b * p.hq * 128, count,
+                       reinterpret_cast<float*>(dyn + AG::kPartOff), tid0, nthr);
+    if (cs_rows > 0) fill_rotation_rows(p, ts, reinterpret_cast<float2*>(dyn + AG::kCsOff), 0, cs_rows, tid0, nthr);
 }
 
 // One warp: S^T of 16 staged rows x one KV head's query heads on mma.sync, rows in groups of eight (the N of
@@ -669,8 +708,8 @@ __device__ __forceinline__ void attend_values(const LayerParams& p, const TailSc
 // way (requested by classify_phase) and listed in the scratch.  Writes partial `pslot` of the request.
 template <int HKV>
 __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared& sh, unsigned char* dyn, int b, int pslot,
-                                              int st0, int st_cnt, int own0, int own_cnt, bool staged, uint32_t& kv_parity,
-                                              bool& dead) {
+                                              int st0, int st_cnt, int own0, int own_cnt, bool staged, bool prepared,
+                                              uint32_t& kv_parity, bool& dead) {
     using AG = AttnGeom<HKV>;
     const int tid = threadIdx.x, warp = tid >> 5;
     TailScratch& ts = tail_scratch(sh);
@@ -727,18 +766,15 @@ __device__ __forceinline__ void attend_rowset(const LayerParams& p, FusedShared&
                          AG::kRowB, bar);
             }
         }
-        // rows of the last, partly filled block: zeros, so that 0-weight products stay finite
-#pragma unroll 1
-        for (int i = rows * (AG::kRowB / 16) + tid; i < rows16 * (AG::kRowB / 16); i += kFusedThreads) {
-            const int r = i / (AG::kRowB / 16), c = i - r * (AG::kRowB / 16);
-            *reinterpret_cast<uint4*>(sm_k + r * AG::kRowS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(sm_v + r * AG::kRowS + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+        if (prepared && r0 == 0) {
+            // the caller zeroed the unused rows, rotated the query and filled the static rows' rotation rows
+            // while the final set was being settled; only the winners' rotation rows are left
+            fill_rotation_rows(p, ts, cs, ts.fast_static, rows16);
+        } else {
+            attend_prepare<HKV>(p, sh, dyn, b, rows, 0, 0, kFusedThreads);
+            __syncthreads();
+            fill_rotation_rows(p, ts, cs, 0, rows16);
         }
-        if (tid >= rows && tid < rows16) ts.row_rank[tid] = -1;
-        __syncthreads();
-        fstamp(p, 17);
-        fill_rotation_rows(p, ts, cs, rows16);
-        fill_rotated_query(p, ts, q_b, count, part);
         __syncthreads();
         fstamp(p, 18);
         mbar_wait(bar, kv_parity, p.err, dead, 5, p.wait_cycles);
@@ -811,8 +847,17 @@ __device__ __forceinline__ void resolve_and_attend(const LayerParams& p, FusedSh
     // members are staged where the rotation rows and the partial outputs go later (behind the K/V rows, which
     // may already be arriving); the inline members of all records (at most kMaxGrid * kRecInline) always fit
     uint2* cand_s = reinterpret_cast<uint2*>(dyn + (attn ? AG::kCsOff : 0));
-    const unsigned cand_cap = attn ? (unsigned)((AG::kCsBytes + attn_part_bytes(AG::kWarpsBusy, p.group)) / 8)
-                                   : (unsigned)((kFusedDynSmem - 2 * kOwnCap * 4) / 8);
+    unsigned cand_cap = attn ? (unsigned)((AG::kCsBytes + attn_part_bytes(AG::kWarpsBusy, p.group)) / 8)
+                             : (unsigned)((kFusedDynSmem - 2 * kOwnCap * 4) / 8);
+    const bool prepared = ATTN && ts.fast != 0 && ts.pad == 1u;
+    if constexpr (ATTN) {
+        if (prepared) {
+            // the attention's inputs were prepared before the barrier, where the members would be staged: they go
+            // behind the partial outputs instead (into the shared-memory copies of the own votes, done with here)
+            cand_s = reinterpret_cast<uint2*>(dyn + early_cand_offset<HKV>(p));
+            cand_cap = (unsigned)((kFusedDynSmem - early_cand_offset<HKV>(p)) / 8);
+        }
+    }
 #pragma unroll 1
     for (int s = 0; s < sh.nseg; ++s) {
         const Resolved r = resolve_segment(p, sh, s, cand_s, cand_cap);
@@ -841,7 +886,8 @@ __device__ __forceinline__ void resolve_and_attend(const LayerParams& p, FusedSh
                 st_cnt = ts.fast_static + ts.fast_pot;
                 own_cnt = 0;
             }
-            attend_rowset<HKV>(p, sh, dyn, b, sh.pbase[b] + me, st0, st_cnt, own0, own_cnt, is_fast, kv_parity, dead);
+            attend_rowset<HKV>(p, sh, dyn, b, sh.pbase[b] + me, st0, st_cnt, own0, own_cnt, is_fast, is_fast && prepared, kv_parity,
+                               dead);
         }
     }
 }
