@@ -299,6 +299,12 @@ def run_config4(args):
     lens_all = torch.arange(ctx + 1, ctx + 1 + steps, dtype=torch.int32, device=dev).view(-1, 1)
     locs_all = perm[ctx: ctx + steps].view(-1, 1).contiguous()
     out = torch.empty(1, HQ * D, dtype=torch.bfloat16, device=dev)
+    meta_all = torch.cat([locs_all, lens_all], dim=1).contiguous()
+    sqkv = torch.empty(layers, 1, (HQ + 2 * HKV) * D, dtype=torch.bfloat16, device=dev)
+    sq, sk, sv = sqkv[..., :HQ * D], sqkv[..., HQ * D:(HQ + HKV) * D], sqkv[..., (HQ + HKV) * D:]
+    smeta = torch.zeros(2, dtype=torch.int32, device=dev)           # pool row of the new token, sequence length
+    sloc, slens = smeta[0:1], smeta[1:2]
+    sflags = torch.zeros(layers, dtype=torch.int32, device=dev)
     pairs, launches_total, ms_total = [], 0, 0.0
     sampler = ClockSampler(0)
     sampler.start()
@@ -308,6 +314,7 @@ def run_config4(args):
         for t in range(1, steps):
             qs[t] = rho * qs[t - 1] + (1.0 - rho * rho) ** 0.5 * eps[t]
         qs_b = qs.to(torch.bfloat16).contiguous()
+        qkv_all = torch.cat([qs_b.view(steps, layers, 1, HQ * D), ks, vs], dim=-1).contiguous()
         q_rot = orc.rotate_scoring_query(qs_b.cpu().view(steps, layers, HQ, D), N_LOCAL, ROPE_BASE, 1.0)
         q_rot = q_rot.float().numpy().reshape(steps, layers, HQ * D)
         for theta in (0.85, 0.90, 0.95):
@@ -318,17 +325,34 @@ def run_config4(args):
             eng.reset_request(1)
             flags = torch.zeros(steps, layers, dtype=torch.int32, device=dev)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            # one CUDA graph per token, as in the headline run: the token's inputs are copied into the captured
+            # buffers, the layers' decisions land in a captured buffer and are copied out after the replay
+            sqkv.copy_(qkv_all[0])
+            smeta.copy_(meta_all[0])
+            for li in range(layers):                                  # eager once: kernel attributes, then a fresh state
+                eng.decode_layer(li, sq[li], sk[li], sv[li], sloc, k_pools[li], v_pools[li], rtt, ridx, slens, out=out,
+                                 debug={"flags": sflags[li:li + 1]})
+            torch.cuda.synchronize()
+            eng.reset_request(1)
             c0 = eng.launch_count
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for li in range(layers):
+                    eng.decode_layer(li, sq[li], sk[li], sv[li], sloc, k_pools[li], v_pools[li], rtt, ridx, slens, out=out,
+                                     debug={"flags": sflags[li:li + 1]})
+            per_token = eng.launch_count - c0
             torch.cuda.synchronize()
             for t in range(steps):
                 ev[t].record()
-                for li in range(layers):
-                    eng.decode_layer(li, qs_b[t, li:li + 1], ks[t, li], vs[t, li], locs_all[t], k_pools[li], v_pools[li], rtt,
-                                     ridx, lens_all[t], out=out, debug={"flags": flags[t, li:li + 1]})
+                sqkv.copy_(qkv_all[t], non_blocking=True)
+                smeta.copy_(meta_all[t], non_blocking=True)
+                graph.replay()
+                flags[t].copy_(sflags, non_blocking=True)
             ev[steps].record()
             torch.cuda.synchronize()
             eng.raise_on_device_error()
-            launches_total += eng.launch_count - c0
+            launches_total += per_token * steps
+            del graph
             tok_ms = np.array([ev[t].elapsed_time(ev[t + 1]) for t in range(steps)])
             ms_total += float(tok_ms.sum())
             got = flags.cpu().numpy()
@@ -370,7 +394,7 @@ def run_config4(args):
         "config": {"workload": f"config 4: selection-cache stress, llama3-8b layer shape, bs=1, ctx={ctx}, {layers} layers, {steps} "
                                f"steps per (rho, threshold) pair, AR(1) decode queries, top_k={TOP_K}, n_init={N_INIT}, "
                                f"n_local={N_LOCAL}; value = the (rho 0.95, threshold 0.90) pair",
-                   "launch": "kernels launched from the host (one call per layer, flags read back per call)"},
+                   "launch": "one CUDA graph replay per token (inputs copied in, the layers' decisions copied out)"},
         "us_per_layer": mid["us_per_layer"], "pairs": pairs,
         "all_decisions_exact": all(x["decisions_exact"] for x in pairs),
         "gpu_launches": int(launches_total), "clocks": clocks,
@@ -480,7 +504,7 @@ def run_batch_config(args, which):
     cfg = TokenSelectConfig(rope_base=base, max_n_tokens=max_ctx, top_k=top_k, n_init=N_INIT, n_local=n_local,
                             n_layers=layers, num_q_heads=hq, num_kv_heads=hkv, head_dim=D, max_reqs=n_req, max_batch=bs,
                             max_total_tokens=sum(sorted(lens0)[-bs:]) + bs * (total_steps + 8), tp_rank=rank, tp_size=tp,
-                            tp_fused=not args.tp_split)
+                            tp_fused=not args.tp_split, extra_flags=(32 if args.phase_times else 0) | args.flags)
     eng = TokenSelectEngine(cfg, device=dev)
     for r in range(n_req):
         eng.reset_request(r)
@@ -565,13 +589,45 @@ def run_batch_config(args, which):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
     launches = eng.launch_count - c0
     eng.raise_on_device_error()
+    if args.phase_times:
+        print_phase_times(eng, rank, tp)
+
+    # ---- the same steps with HOST buffers: a token's inputs (all layers' q | k | v) come from pinned memory, every
+    # layer's output goes back to pinned memory, and the host waits for it before the next token.  The appended rows
+    # are rewritten with the same contents and the lengths repeat, so the pass is a second run of the same steps.
+    d_in = (hq + 2 * hkv) * D
+    host_in = [x[args.warmup:].contiguous().cpu().pin_memory() for x in (qs, ks, vs)]          # [steps, layers, bs, *]
+    dev_in = [torch.empty_like(x[0]) for x in (qs, ks, vs)]
+    outs_dev = torch.empty(layers, bs, hq * D, dtype=torch.bfloat16, device=dev)
+    outs_host = torch.empty(layers, bs, hq * D, dtype=torch.bfloat16).pin_memory()
+    for r in range(n_req):
+        eng.reset_request(r)
+    barrier()
+    e0.record()
+    for i, t in enumerate(range(args.warmup, total_steps)):
+        if t > 0:
+            for pos in range(bs):
+                if sched[t][0][pos] != sched[t - 1][0][pos]:
+                    eng.reset_request(sched[t][0][pos])
+        for dst, src in zip(dev_in, host_in):
+            dst.copy_(src[i], non_blocking=True)
+        for li in range(layers):
+            eng.decode_layer(li, dev_in[0][li], dev_in[1][li], dev_in[2][li], locs_all[t],
+                             k_pools[li % resident], v_pools[li % resident], rtt, ridx_all[t], lens_all[t], out=outs_dev[li],
+                             vote_elems=ve)
+        outs_host.copy_(outs_dev, non_blocking=True)
+        torch.cuda.synchronize()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    eng.raise_on_device_error()
     if tp > 1:
-        tt = torch.tensor([ms], device=dev)
+        tt = torch.tensor([ms, ms_e2e], device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = float(tt.item())
+        ms, ms_e2e = float(tt[0].item()), float(tt[1].item())
     if rank == 0:
         n_mid = [n + args.warmup + steps // 2 for n in sched[args.warmup][1]]
         layer_bytes = 0
@@ -597,6 +653,8 @@ def run_batch_config(args, which):
                          "bytes_per_launch": layer_bytes, "us_per_launch": us_layer, "traffic": None,
                          "note": "per rank: algorithmic bytes of one layer step of the whole batch over the time of a layer step "
                                  "(one launch)"},
+            "e2e": {"value": bs * steps / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": layers * bs * d_in * 2,
+                    "d2h_bytes_per_step": layers * bs * hq * D * 2},
             "gpu_launches": int(launches), "clocks": clocks,
         }
         if check is not None:
@@ -642,7 +700,7 @@ def run_prefill(args):
     out = torch.empty(chunk, HQ * D, dtype=torch.bfloat16, device=dev)
     cfg = TokenSelectConfig(rope_base=ROPE_BASE, max_n_tokens=ctx + 8, top_k=TOP_K, n_init=N_INIT, n_local=N_LOCAL,
                             n_layers=layers, num_q_heads=HQ, num_kv_heads=HKV, head_dim=D, max_reqs=2, max_batch=1,
-                            max_total_tokens=ctx + 8, prefill_chunk=chunk)
+                            max_total_tokens=ctx + 8, prefill_chunk=chunk, extra_flags=args.flags)
     eng = TokenSelectEngine(cfg, device=dev)
     n_chunks = (ctx + chunk - 1) // chunk
 
@@ -686,12 +744,35 @@ def run_prefill(args):
                                f"top_k={TOP_K}, n_init={N_INIT}, n_local={N_LOCAL}, page size 1, permuted pool rows"},
         "us_per_chunk_layer": 1e3 * ms / (n_chunks * layers),
         "kernel_us_last_chunks": {k: round(1e3 * v[0] / v[1], 2) for k, v in stages.items()},
-        "roofline": {"bound": "tensor", "kernel": "extend_attend_tc5_kernel", "achieved": flops / (att_us * 1e-6) / 1e12,
+        "roofline": {"bound": "tensor", "kernel": "extend_attend_tc5_kernel" if args.flags & (16 | 512) else
+                     "extend_attend_tc5_pair_kernel", "achieved": flops / (att_us * 1e-6) / 1e12,
                      "peak": peak, "unit": "TFLOP/s", "frac": flops / (att_us * 1e-6) / 1e12 / peak, "peak_source": src,
                      "flops_per_launch": flops, "us_per_launch": att_us, "traffic": None},
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
+
+
+def print_phase_times(eng, rank, tp):
+    """The last launch's phase stamps of CTA 0 (TS_CFG_PHASE_STAMPS), to stderr."""
+    ts = eng.debug_read(3, 128, torch.int64).tolist()
+    # stamp indices of the selection kernel: 0 start, 1 plan, 2 scoring done, 3 barrier passed, 4 votes done,
+    # 24 exchange done, 5 barrier passed, 6 classified (records out, rows requested), 7 barrier passed,
+    # 8 set final + own rows attended, 15 barrier passed, 16 partials merged
+    marks = [("plan", 0, 1), ("score", 1, 2), ("barrier 1", 2, 3), ("vote", 3, 4), ("exchange", 4, 24),
+             ("barrier 2", 24, 5), ("classify", 5, 6), ("barrier 3", 6, 7), ("resolve+attend", 7, 8),
+             ("barrier 4", 8, 15), ("merge", 15, 16)]
+    split = {n: (ts[j] - ts[i]) / 1e3 for n, i, j in marks if ts[i] > 0 and ts[j] > 0}
+    if tp > 1 and eng.fused_tp:
+        split["exchange: signal sent"] = (ts[26] - ts[4]) / 1e3
+        split["exchange: flags"] = (ts[25] - ts[4]) / 1e3
+        split["exchange: sum"] = (ts[24] - ts[25]) / 1e3
+    print(f"[rank {rank}] selection kernel phases (us): {split}", file=sys.stderr, flush=True)
+    t0 = ts[0]
+    print(f"[rank {rank}] raw stamps (us after the kernel's start, by index): "
+          f"{ {i: round((t - t0) / 1e3, 2) for i, t in enumerate(ts) if t > 0 and abs(t - t0) < 1e9} }; "
+          f"threshold-bin members of the last launch: {eng.debug_read(4, 1, torch.int32).tolist()}",
+          file=sys.stderr, flush=True)
 
 
 def correctness_check(eng, dist, rank, tp, q, k_new, v_new, loc, k_pool, v_pool, rtt, ridx, lens, n_tokens):
@@ -1012,24 +1093,7 @@ def main():
     eng.raise_on_device_error()
 
     if args.phase_times:
-        ts = eng.debug_read(3, 128, torch.int64).tolist()
-        # stamp indices of the selection kernel: 0 start, 1 plan, 2 scoring done, 3 barrier passed, 4 votes done,
-        # 24 exchange done, 5 barrier passed, 6 classified (records out, rows requested), 7 barrier passed,
-        # 8 set final + own rows attended, 15 barrier passed, 16 partials merged
-        marks = [("plan", 0, 1), ("score", 1, 2), ("barrier 1", 2, 3), ("vote", 3, 4), ("exchange", 4, 24),
-                 ("barrier 2", 24, 5), ("classify", 5, 6), ("barrier 3", 6, 7), ("resolve+attend", 7, 8),
-                 ("barrier 4", 8, 15), ("merge", 15, 16)]
-        split = {n: (ts[j] - ts[i]) / 1e3 for n, i, j in marks if ts[i] > 0 and ts[j] > 0}
-        if tp > 1 and eng.fused_tp:
-            split["exchange: signal sent"] = (ts[26] - ts[4]) / 1e3
-            split["exchange: flags"] = (ts[25] - ts[4]) / 1e3
-            split["exchange: sum"] = (ts[24] - ts[25]) / 1e3
-        print(f"[rank {rank}] selection kernel phases (us): {split}", file=sys.stderr, flush=True)
-        t0 = ts[0]
-        print(f"[rank {rank}] raw stamps (us after the kernel's start, by index): "
-              f"{ {i: round((t - t0) / 1e3, 2) for i, t in enumerate(ts) if t > 0 and abs(t - t0) < 1e9} }; "
-              f"threshold-bin members of the last launch: {eng.debug_read(4, 1, torch.int32).tolist()}",
-              file=sys.stderr, flush=True)
+        print_phase_times(eng, rank, tp)
     if rank == 0:
         ab = algorithmic_bytes(ctx + args.warmup + args.steps // 2, hq, hkv, D)
         peak, peak_kind = hbm_peak()

@@ -51,8 +51,9 @@ def _check_request(eng, res, b, q_b, kp, vp, rtt_row, n, out_b, o, layer, slot):
     assert (out_b.double() - want).abs().max().item() <= 2e-2
 
 
-@pytest.mark.parametrize("scale", [16, 1], ids=["lengths_div16", "full_lengths"])
-def test_ragged_continuous_batch_qwen_shape(scale):
+@pytest.mark.parametrize("scale,flags", [(16, 0), (16, 1024), (1, 0)],
+                         ids=["lengths_div16", "lengths_div16_inline_attention", "full_lengths"])
+def test_ragged_continuous_batch_qwen_shape(scale, flags):
     """16 requests, lengths log-uniform in [16384, 262144] / scale from a seed; three scheduler steps in
     which requests finish and new ones join the freed slots (their cache state is reset).  Every request of
     every step is checked against the oracle at the reduced lengths; at full lengths the first and last
@@ -76,7 +77,7 @@ def test_ragged_continuous_batch_qwen_shape(scale):
         rtt[r, :n + 3] = perm[at: at + n + 3]
         at += n + 3
     eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, BF16, n_layers=2, max_ctx=max_ctx, max_reqs=max_reqs,
-                         max_batch=bs, max_total=sum(sorted(lens)[-bs:]) + 64, query_cache=True)
+                         max_batch=bs, max_total=sum(sorted(lens)[-bs:]) + 64, query_cache=True, extra_flags=flags)
     qs = torch.randn(3, max_reqs, hq * d, generator=g, device=dev).to(BF16)
     q_rot0 = orc.rotate_scoring_query(qs[0].cpu().view(max_reqs, hq, d), n_local, base, 1.0).float().to(dev)
     for r, n in enumerate(lens):

@@ -104,16 +104,19 @@ def _multi_request(seed, lens, hq, hkv, d, dtype, pool_rows, max_ctx, max_reqs, 
     return q, k_pool, v_pool, rtt
 
 
-@pytest.mark.parametrize("dtype", [BF16, F32], ids=["bf16", "fp32"])
-def test_ragged_batch_with_dense_requests(dtype):
+@pytest.mark.parametrize("dtype,flags", [(BF16, 0), (BF16, 1024), (F32, 0)], ids=["bf16", "bf16_inline_attention", "fp32"])
+def test_ragged_batch_with_dense_requests(dtype, flags):
     """Requests of different lengths in one call, some below the guard (attend to everything), at
-    the guard boundary (N == n_sel and N == n_sel + 1), and one shorter than n_init."""
+    the guard boundary (N == n_sel and N == n_sel + 1), and one shorter than n_init.  Batches take the
+    selection kernel followed by the attention kernels by default; TS_CFG_INLINE_ATTEND (1024) keeps the
+    attention inside the layer-step kernel."""
     hq, hkv, d, n_init, n_local, k, base = 8, 2, 128, 16, 64, 256, 5e5
     n_sel = n_init + k + n_local
     lens = [2000, n_sel, n_sel + 1, 5, 1177, 40]
     slots = [3, 0, 5, 1, 2, 4]
     q, kp, vp, rtt = _multi_request(7, lens, hq, hkv, d, dtype, 6000, 2100, 6, slots)
-    eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, dtype, max_ctx=2100, max_reqs=6, max_batch=6)
+    eng = gu.make_engine(hq, hkv, d, n_init, n_local, k, base, dtype, max_ctx=2100, max_reqs=6, max_batch=6,
+                         extra_flags=flags)
     ridx, sl = torch.tensor(slots), torch.tensor(lens)
     out, res = gu.run_gpu(eng, 0, q, kp, vp, rtt, ridx, sl)
     ref = orc.DecodeOracle(gu.oracle_config(eng)).decode_layer(0, q, None, None, None, kp, vp, rtt, ridx, sl)

@@ -231,6 +231,7 @@ int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l, bool 
     p.k_pool = a->k_pool; p.v_pool = a->v_pool; p.pool_rows = a->pool_rows;
     p.rtt = a->req_to_token; p.rtt_stride = a->req_to_token_stride;
     p.req_pool_indices = a->req_pool_indices; p.seq_lens = a->seq_lens; p.out = a->out;
+    p.flags_out = a->dbg_flags;
     if (h->cfg.tp_size > 1 && !fused_tp) {
         if (!a->tp_votes || !a->tp_cos) return TS_ERR_INVALID_ARG;
         p.votes = a->tp_votes;
@@ -265,8 +266,7 @@ int copy_debug(ts_handle* h, const ts_decode_args* a, const LayerParams& p, cuda
         e = cudaMemcpyAsync(a->dbg_sel_pos, p.sel_pos, nb * h->n_sel * 4, cudaMemcpyDeviceToDevice, s);
     if (a->dbg_sel_count && e == cudaSuccess)
         e = cudaMemcpyAsync(a->dbg_sel_count, p.sel_count, nb * 4, cudaMemcpyDeviceToDevice, s);
-    if (a->dbg_flags && e == cudaSuccess)
-        e = cudaMemcpyAsync(a->dbg_flags, p.flags, nb * 4, cudaMemcpyDeviceToDevice, s);
+    // (dbg_flags: written by the kernels themselves through LayerParams::flags_out)
     return e == cudaSuccess ? TS_OK : cuda_fail(h, e, "debug copy");
 }
 
@@ -455,6 +455,11 @@ int ts_decode_layer(ts_handle* h, const ts_decode_args* a) {
     LayerParams p; Launch l;
     int s = fill(h, a, p, l, fused_tp);
     if (s != TS_OK) return s;
+    // The layer-step kernel attends inside the CTAs that own the winners, which pays when a request's candidates
+    // span the whole grid.  In a batch every request spans a fraction of the grid only (a short one a CTA or two,
+    // which would then attend to all its winners alone), so batches take the selection kernel and the attention
+    // kernels, whose grid covers every (request, row block) -- unless TS_CFG_INLINE_ATTEND asks otherwise.
+    if (a->batch > 1 && !(h->cfg.flags & TS_CFG_INLINE_ATTEND)) p.attn_inline = 0;
     TS_TRY(launch_fused(p, l, fused_tp ? kModeTpFused : kModeAll), "select");
     if (!p.attn_inline) TS_TRY(launch_attend(p, l), "attend");
     return copy_debug(h, a, p, l.stream);

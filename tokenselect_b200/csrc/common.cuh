@@ -52,6 +52,7 @@ struct LayerParams {
     // workspace
     void* q_rot;               // [max_batch, hq*d] dtype: rotated scoring queries
     int* flags;                // [max_batch] TS_FLAG_*
+    int* flags_out;            // the caller's copy of the flags (inspection output), or null
     float* cos_terms;          // [max_batch, 4] (q.c, |q|^2, |c|^2, -)
     float* logits;             // [cand_capacity, hq]
     float2* partials;          // [max_batch, part_stride]: per-CTA (max, sum exp) as [grid, hq]

@@ -535,6 +535,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
 __device__ __forceinline__ float ex2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -782,6 +790,266 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
 }
 
 // ------------------------------------------------------------------------------------------------
+// 4a''. two softmax teams on alternating key blocks (the default)
+// ------------------------------------------------------------------------------------------------
+// One softmax team cannot keep up with the tensor pipe: its per-block chain (wait for S, tcgen05.ld, row
+// maximum through shared memory, 32 exponentials per thread, pack, tcgen05.st, arrive) runs with two warps per
+// scheduler and is bound by its own latencies.  Here two teams of 256 threads run that chain on alternating key
+// blocks -- team t takes blocks t, t + 2, ... -- each with its OWN online softmax (reference maximum, row sums)
+// and its OWN output accumulator, so the teams share no state; the two (reference, sum, output) triples of a row
+// are joined once at the end.  Tensor memory (all 512 columns):
+//   S[t][u]  128 x 64 fp32, columns 64 (2t + u), u = the team's block count mod 2;  P (packed bf16, 32 columns)
+//            is written over the start of the S buffer it was computed from
+//   O[t]     128 x 128 fp32, columns 256 + 128 t
+// The issuing thread keeps the tensor pipe two key blocks ahead of the softmax: S(b + 2) = Q.K_(b+2)^T is issued
+// before it waits for P(b).  MMAs execute in issue order, so S(b + 2) lands on the buffer of block b - 2 only
+// after P(b - 2).V has read it.
+struct Tc5PairSmem {
+    unsigned char q[128 * 256];                 // 2 halves x [128 rows][128 B]
+    unsigned char k[kKvStages][kTile * 256];    // 2 halves x [64 keys][128 B]
+    unsigned char v[kKvStages][kTile * 256];
+    float rowmax[2][2][2][128];                 // [team][buffer][column half][row]
+    float fin[2][3][128];                       // [team][reference maximum, row sum of column half 0, of half 1][row]
+    uint64_t qbar, full[kKvStages], s_done[2][2], o_done[2][2], p_ready[2][2];
+    uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const ExtendParams e) {
+    constexpr int W = 32;                                    // S columns per thread
+    constexpr int OW = 64;                                   // O columns per thread
+    constexpr uint32_t kPairO = 256;
+    extern __shared__ unsigned char tc5_dyn[];
+    Tc5PairSmem& sm = *reinterpret_cast<Tc5PairSmem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int qt = blockIdx.x, h = blockIdx.y, kv = h / e.group;
+    const int lq = e.chunk_len;
+    if (*(volatile int*)e.err != 0 || qt * 128 >= lq) return;
+    const int count = min(*e.sel_count, e.n_sel);
+    const int base_vis = count - lq;                         // query row r sees list entries j <= base_vis + r
+    const int kmax = min(count - 1, base_vis + qt * 128 + 127);
+    const int nblk = kmax / kTile + 1;
+    bool dead = false;
+
+    if (tid == 0) {
+        mbar_init(smem_u32(&sm.qbar), 1);
+        for (int s = 0; s < kKvStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
+        for (int t = 0; t < 2; ++t)
+            for (int u = 0; u < 2; ++u) {
+                mbar_init(smem_u32(&sm.s_done[t][u]), 1);
+                mbar_init(smem_u32(&sm.o_done[t][u]), 1);
+                mbar_init(smem_u32(&sm.p_ready[t][u]), 8);   // the team's eight warps
+            }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *(volatile uint32_t*)&sm.tmem_base;
+
+    if (warp == 16) {
+        // ---------------- issuer ----------------
+        if (lane == 0) {
+            const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
+            const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(e.kc) + (size_t)kv * e.rows_k * 256;
+            const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(e.vc) + (size_t)kv * e.rows_k * 256;
+            constexpr uint32_t kTileBytes = kTile * 256;     // one K or V tile image
+            auto load_tile = [&](int b) {
+                const int st = b % kKvStages;
+                mbar_expect_tx(smem_u32(&sm.full[st]), 2 * kTileBytes);
+                bulk_g2s(smem_u32(sm.k[st]), ksrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
+                bulk_g2s(smem_u32(sm.v[st]), vsrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
+            };
+            constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+            constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            auto issue_qk = [&](int b) {                     // S[t][u] = Q . K_b^T
+                const int st = b % kKvStages, t = b & 1, u = (b >> 1) & 1;
+                mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42, e.wait_cycles);
+                tc_fence_after();
+                const uint32_t qa = smem_u32(sm.q), ka = smem_u32(sm.k[st]);
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off_q = (ks >> 2) * (128u * 128u) + (ks & 3) * 32u;
+                    const uint32_t off_k = (ks >> 2) * (kTile * 128u) + (ks & 3) * 32u;
+                    umma_bf16(tmem + 64u * (2 * t + u), umma_desc_sw128(qa + off_q, 16, 1024),
+                              umma_desc_sw128(ka + off_k, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&sm.s_done[t][u]));
+            };
+            mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
+            bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
+            for (int b = 0; b < kKvStages && b < nblk; ++b) load_tile(b);
+            mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40, e.wait_cycles);
+            issue_qk(0);
+            if (nblk > 1) issue_qk(1);
+            for (int blk = 0; blk < nblk; ++blk) {
+                const int t = blk & 1, i = blk >> 1, u = i & 1;
+                if (blk + 2 < nblk) issue_qk(blk + 2);
+                if (blk > 0 && blk - 1 + kKvStages < nblk) {
+                    // P.V of the previous block is complete: its stage can take the tile four blocks ahead
+                    const int pb = blk - 1;
+                    mbar_wait(smem_u32(&sm.o_done[pb & 1][(pb >> 1) & 1]), (uint32_t)((pb >> 2) & 1), e.err, dead, 46, e.wait_cycles);
+                    load_tile(blk - 1 + kKvStages);
+                }
+                mbar_wait(smem_u32(&sm.p_ready[t][u]), (uint32_t)((i >> 1) & 1), e.err, dead, 47, e.wait_cycles);
+                tc_fence_after();
+                const uint32_t va = smem_u32(sm.v[blk % kKvStages]);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)               // 16 keys per step: 8 packed columns of P
+                    umma_bf16_ts(tmem + kPairO + 128u * t, tmem + 64u * (2 * t + u) + 8u * ks,
+                                 umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024), kIdescPV, (i > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&sm.o_done[t][u]));
+            }
+        }
+    } else {
+        // ---------------- softmax teams ----------------
+        const int team = warp >> 3, cq = (warp >> 2) & 1, rq = warp & 3;   // team, column half, row (lane) quarter
+        const int r_in = rq * 32 + lane;                     // row inside the 128-row tile
+        const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
+        const uint32_t t_o = tmem + lane_base + kPairO + 128u * team + (uint32_t)(OW * cq);
+        const int row = qt * 128 + r_in;
+        const int lim = base_vis + row;
+        const float cap = e.logit_cap;
+        const float mul = cap > 0.f ? 1.f : e.sm_scale * kLog2eX;     // x * mul is the logit in base-2 units
+        float m_ref = 0.f, l_run = 0.f;
+        int i = 0;
+        for (int blk = team; blk < nblk; blk += 2, ++i) {
+            const int u = i & 1;
+            const uint32_t t_s = tmem + lane_base + 64u * (2 * team + u) + (uint32_t)(W * cq);
+            const uint32_t t_p = tmem + lane_base + 64u * (2 * team + u) + (uint32_t)(W / 2 * cq);
+            mbar_wait(smem_u32(&sm.s_done[team][u]), (uint32_t)((i >> 1) & 1), e.err, dead, 43, e.wait_cycles);
+            tc_fence_after();
+            float x[W];
+            {
+                uint32_t r0[W / 16][16];
+#pragma unroll
+                for (int j = 0; j < W / 16; ++j) tmem_ld16(t_s + 16u * j, r0[j]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < W; ++c) x[c] = __uint_as_float(r0[c / 16][c % 16]);
+            }
+            float mx = -INFINITY;
+            const int key0 = blk * kTile + W * cq;
+            if (cap > 0.f) {
+#pragma unroll
+                for (int c = 0; c < W; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
+            }
+            if (blk * kTile + kTile - 1 > base_vis + qt * 128) {      // only blocks that reach the diagonal are masked
+#pragma unroll
+                for (int c = 0; c < W; ++c)
+                    if (key0 + c > lim) x[c] = -INFINITY;
+            }
+#pragma unroll
+            for (int c = 0; c < W; ++c) mx = fmaxf(mx, x[c]);
+            mx *= mul;                                               // base-2 units (mul > 0)
+            float* rm = &sm.rowmax[team][u][0][r_in];
+            rm[cq * 128] = mx;
+            // the two warps that share these rows; both have read their S columns by now, so P may overwrite them
+            named_bar_sync(1 + 4 * team + rq, 64);
+            mx = fmaxf(rm[0], rm[128]);
+            if (i > 0) {
+                const bool grow = mx > m_ref + 8.f;
+                if (__any_sync(0xffffffffu, grow)) {
+                    // O is rescaled in place: the team's P.V issued so far must be complete (they run in order)
+                    mbar_wait(smem_u32(&sm.o_done[team][(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1), e.err, dead, 44, e.wait_cycles);
+                    tc_fence_after();
+                    const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
+#pragma unroll 1
+                    for (int j = 0; j < OW / 16; ++j) {
+                        uint32_t r[16];
+                        tmem_ld16(t_o + 16u * j, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                        tmem_st16(t_o + 16u * j, r);
+                    }
+                    l_run *= corr;
+                    if (grow) m_ref = mx;
+                }
+            } else {
+                m_ref = mx == -INFINITY ? 0.f : mx;
+            }
+            float sum = 0.f;
+            uint32_t w[W / 16][8];
+#pragma unroll
+            for (int c = 0; c < W / 2; ++c) {
+                const float p0 = ex2_fast(fmaf(x[2 * c], mul, -m_ref)), p1 = ex2_fast(fmaf(x[2 * c + 1], mul, -m_ref));
+                sum += p0 + p1;
+                w[c / 8][c % 8] = pack_bf16(p0, p1);
+            }
+#pragma unroll
+            for (int j = 0; j < W / 16; ++j) tmem_st8(t_p + 8u * j, w[j]);
+            tmem_wait_st();
+            l_run += sum;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[team][u]));
+        }
+        // what the join needs: the team's reference maximum and row sums; the team's last P.V must have landed
+        if (cq == 0) sm.fin[team][0][r_in] = m_ref;
+        sm.fin[team][1 + cq][r_in] = l_run;
+        if (i > 0) {
+            mbar_wait(smem_u32(&sm.o_done[team][(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1), e.err, dead, 45, e.wait_cycles);
+            tc_fence_after();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp < 8) {
+        // ---------------- join of the two teams' results, by team 0's threads ----------------
+        tc_fence_after();
+        const int cq = (warp >> 2) & 1, rq = warp & 3, r_in = rq * 32 + lane;
+        const int row = qt * 128 + r_in;
+        const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
+        const bool two = nblk > 1;
+        const float m0 = sm.fin[0][0][r_in], l0 = sm.fin[0][1][r_in] + sm.fin[0][2][r_in];
+        const float m1 = two ? sm.fin[1][0][r_in] : m0, l1 = two ? sm.fin[1][1][r_in] + sm.fin[1][2][r_in] : 0.f;
+        const float mm = fmaxf(l0 > 0.f ? m0 : -INFINITY, l1 > 0.f ? m1 : -INFINITY);   // a team without weight sets no scale
+        const float w0 = l0 > 0.f ? ex2_fast(m0 - mm) : 0.f, w1 = l1 > 0.f ? ex2_fast(m1 - mm) : 0.f;
+        const float l_tot = w0 * l0 + w1 * l1;
+        const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+        const float s0 = w0 * inv, s1 = w1 * inv;
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + OW * cq;
+#pragma unroll 1
+        for (int j = 0; j < OW / 16; ++j) {
+            uint32_t r[16];
+            float o[16];
+            tmem_ld16(tmem + lane_base + kPairO + (uint32_t)(OW * cq) + 16u * j, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 16; ++c) o[c] = s0 > 0.f ? __uint_as_float(r[c]) * s0 : 0.f;
+            if (two) {                                       // (a team that never ran leaves its accumulator unwritten)
+                tmem_ld16(tmem + lane_base + kPairO + 128u + (uint32_t)(OW * cq) + 16u * j, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 16; ++c) o[c] += s1 > 0.f ? __uint_as_float(r[c]) * s1 : 0.f;
+            }
+            if (row < lq) {
+#pragma unroll
+                for (int c8 = 0; c8 < 2; ++c8) {
+                    uint4 w;
+                    w.x = pack_bf16(o[c8 * 8 + 0], o[c8 * 8 + 1]);
+                    w.y = pack_bf16(o[c8 * 8 + 2], o[c8 * 8 + 3]);
+                    w.z = pack_bf16(o[c8 * 8 + 4], o[c8 * 8 + 5]);
+                    w.w = pack_bf16(o[c8 * 8 + 6], o[c8 * 8 + 7]);
+                    *reinterpret_cast<uint4*>(out + 16 * j + c8 * 8) = w;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // 4b. the same on CUDA cores in fp32 (fp32 check mode, head_dim 64): one warp per (query, head)
 // ------------------------------------------------------------------------------------------------
 template <typename T, int E>
@@ -865,7 +1133,13 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     if (tc5) {
         static SmemConfig configured5 = {};
         const size_t smem5 = sizeof(Tc5Smem) + 1024;
-        if (!(l.flags & TS_CFG_EXTEND_FOUR_PER_ROW)) {
+        if (!(l.flags & (TS_CFG_EXTEND_FOUR_PER_ROW | TS_CFG_EXTEND_ONE_TEAM))) {
+            static SmemConfig configured_pair = {};
+            const size_t smem_pair = sizeof(Tc5PairSmem) + 1024;
+            err = ensure_dynamic_smem(extend_attend_tc5_pair_kernel, smem_pair, configured_pair);
+            if (err != cudaSuccess) return err;
+            extend_attend_tc5_pair_kernel<<<dim3(e.rows_q / 128, e.hq), 544, smem_pair, l.stream>>>(e);
+        } else if (!(l.flags & TS_CFG_EXTEND_FOUR_PER_ROW)) {
             static SmemConfig configured2 = {};
             err = ensure_dynamic_smem(extend_attend_tc5_kernel<2>, smem5, configured2);
             if (err != cudaSuccess) return err;

@@ -12,6 +12,13 @@
 namespace ts {
 
 // Decision for one request given the three cosine terms.  Thread 0 of the block calls it.
+// The request's flag, and the caller's copy of it when one was asked for (written by the kernel itself: a copy
+// node between the kernels of a captured token would serialise them).
+__device__ __forceinline__ void put_flag(const LayerParams& p, int b, int f) {
+    p.flags[b] = f;
+    if (p.flags_out != nullptr) p.flags_out[b] = f;
+}
+
 template <typename T>
 __device__ __forceinline__ int decide(const LayerParams& p, int b, int req, float dot, float qq, float cc) {
     int flag = TS_FLAG_RECOMPUTE;
@@ -59,7 +66,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     const int req = p.req_pool_indices[b];
     const int hd = p.hq * p.d;
     if (n < 1 || n > p.max_ctx || req < 0 || req >= p.max_reqs) {
-        if (tid == 0) { set_error(p.err, TS_ERR_BAD_LENGTH, n); p.flags[b] = TS_FLAG_DENSE; }
+        if (tid == 0) { set_error(p.err, TS_ERR_BAD_LENGTH, n); put_flag(p, b, TS_FLAG_DENSE); }
         return;
     }
 
@@ -67,7 +74,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     if (p.k_new != nullptr) {
         int loc = p.out_cache_loc[b];
         if (loc < 0 || loc >= p.pool_rows) {
-            if (tid == 0) { set_error(p.err, TS_ERR_BAD_SLOT, loc); p.flags[b] = TS_FLAG_DENSE; }
+            if (tid == 0) { set_error(p.err, TS_ERR_BAD_SLOT, loc); put_flag(p, b, TS_FLAG_DENSE); }
             return;
         }
         const int row_vec = p.hkv * p.d * (int)sizeof(T) / 16;
@@ -86,7 +93,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
 
     // 3. guard (:376-378): short requests attend to everything
     if (p.n_sel >= n) {
-        if (tid == 0) p.flags[b] = TS_FLAG_DENSE;
+        if (tid == 0) put_flag(p, b, TS_FLAG_DENSE);
         return;
     }
 
@@ -145,7 +152,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         }
     }
     if (!kFusedDecide) {
-        if (tid == 0) p.flags[b] = TS_FLAG_RECOMPUTE;   // provisional: decide_kernel overwrites it
+        if (tid == 0) put_flag(p, b, TS_FLAG_RECOMPUTE);   // provisional: decide_kernel overwrites it
         return;
     }
     tg.sync();
@@ -153,7 +160,7 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     // 6. decision and cache update (:395-421)
     if (tid == 0) {
         int f = decide<T>(p, b, req, s_terms[0], s_terms[1], s_terms[2]);
-        p.flags[b] = f;
+        put_flag(p, b, f);
         s_flag = f;
     }
     tg.sync();
@@ -176,7 +183,7 @@ __device__ __forceinline__ void decide_request(const LayerParams& p, int b, Prep
     const int hd = p.hq * p.d;
     if (tid == 0) {
         int f = decide<T>(p, b, req, p.cos_terms[4 * b], p.cos_terms[4 * b + 1], p.cos_terms[4 * b + 2]);
-        p.flags[b] = f;
+        put_flag(p, b, f);
         s_flag = f;
     }
     __syncthreads();
