@@ -41,9 +41,12 @@ METRIC = "decode tok/s at 128K ctx (1-8 GPU); select+attn us/layer vs HBM roofli
 HQ, HKV, D, LAYERS = 32, 8, 128, 32
 N_INIT, N_LOCAL, TOP_K, ROPE_BASE = 128, 512, 2048, 5e5
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes (read + write) the selection kernel moved per algorithmic byte in its last ncu capture at the
-# headline shape (277.37 MB against 267.70 MB): the key stream once, plus the logits written back from L2.
+# DRAM bytes (read + write) per algorithmic byte in the last ncu capture at the headline shape.  Selection kernel
+# alone: 277.37 MB against 267.70 MB (the key stream once, plus the logits written back from L2).  Layer-step
+# kernel (selection, attention and merge in one launch): 277.89 MB read + 10.92 MB written (mean of two launches)
+# against 278.70 MB.
 SELECT_DRAM_BYTES_PER_ALGORITHMIC_BYTE = 277.37 / 267.70
+STEP_DRAM_BYTES_PER_ALGORITHMIC_BYTE = (277.89 + 10.92) / 278.70
 
 
 def parse_args():
@@ -648,11 +651,13 @@ def run_batch_config(args, which):
                        if tp > 1 else "single GPU",
                        "l2": "inputs larger than L2: every layer streams its own keys", "launch": "kernels launched from the host"},
             "us_per_layer": us_layer,
-            "roofline": {"bound": "hbm", "kernel": "decode_step_kernel", "achieved": layer_bytes / (us_layer * 1e-6) / 1e9,
+            "roofline": {"bound": "hbm",
+                         "kernel": "decode_step_kernel" if launches == steps * layers else
+                                   "fused_select_kernel (+ attend_split_tc_kernel, attend_merge_kernel: three launches per layer)",
+                         "achieved": layer_bytes / (us_layer * 1e-6) / 1e9,
                          "peak": peak, "unit": "GB/s", "frac": layer_bytes / (us_layer * 1e-6) / 1e9 / peak, "peak_source": peak_kind,
                          "bytes_per_launch": layer_bytes, "us_per_launch": us_layer, "traffic": None,
-                         "note": "per rank: algorithmic bytes of one layer step of the whole batch over the time of a layer step "
-                                 "(one launch)"},
+                         "note": "per rank: algorithmic bytes of one layer step of the whole batch over the time of a layer step"},
             "e2e": {"value": bs * steps / (ms_e2e * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": layers * bs * d_in * 2,
                     "d2h_bytes_per_step": layers * bs * hq * D * 2},
             "gpu_launches": int(launches), "clocks": clocks,
@@ -700,7 +705,8 @@ def run_prefill(args):
     out = torch.empty(chunk, HQ * D, dtype=torch.bfloat16, device=dev)
     cfg = TokenSelectConfig(rope_base=ROPE_BASE, max_n_tokens=ctx + 8, top_k=TOP_K, n_init=N_INIT, n_local=N_LOCAL,
                             n_layers=layers, num_q_heads=HQ, num_kv_heads=HKV, head_dim=D, max_reqs=2, max_batch=1,
-                            max_total_tokens=ctx + 8, prefill_chunk=chunk, extra_flags=args.flags)
+                            max_total_tokens=ctx + 8, prefill_chunk=chunk,
+                            extra_flags=(32 if args.phase_times else 0) | args.flags)
     eng = TokenSelectEngine(cfg, device=dev)
     n_chunks = (ctx + chunk - 1) // chunk
 
@@ -731,6 +737,13 @@ def run_prefill(args):
     eng.timing_begin(8 * layers * 4 + 16)
     prefill(max(0, n_chunks - 8), n_chunks)
     stages = {k: v for k, v in eng.timing_end().items() if v[1]}
+    if args.phase_times:
+        # cycle counts the attention kernel's CTA (0, 0) left on its last launch (TS_CFG_PHASE_STAMPS)
+        ts = eng.debug_read(3, 128, torch.int64).tolist()
+        names = ["loop", "wait S", "tcgen05.ld", "mask+max+exchange", "exp+pack", "tcgen05.st+arrive", "blocks"]
+        inames = ["loop", "QK issue + K tile wait", "-", "wait P", "wait V tile", "blocks"]
+        print("prefill attention, cycles of CTA (0,0): issuing thread " + str(dict(zip(inames, ts[64:70])))
+              + "; softmax warp 0 " + str(dict(zip(names, ts[72:79]))), file=sys.stderr, flush=True)
     n_sel = N_INIT + TOP_K + N_LOCAL
     count = min(ctx, n_sel)
     flops = 4.0 * HQ * D * sum(count - chunk + t + 1 for t in range(chunk))
@@ -745,7 +758,7 @@ def run_prefill(args):
         "us_per_chunk_layer": 1e3 * ms / (n_chunks * layers),
         "kernel_us_last_chunks": {k: round(1e3 * v[0] / v[1], 2) for k, v in stages.items()},
         "roofline": {"bound": "tensor", "kernel": "extend_attend_tc5_kernel" if args.flags & (16 | 512) else
-                     "extend_attend_tc5_pair_kernel", "achieved": flops / (att_us * 1e-6) / 1e12,
+                     "extend_attend_tc5_wide_kernel", "achieved": flops / (att_us * 1e-6) / 1e12,
                      "peak": peak, "unit": "TFLOP/s", "frac": flops / (att_us * 1e-6) / 1e12 / peak, "peak_source": src,
                      "flops_per_launch": flops, "us_per_launch": att_us, "traffic": None},
         "gpu_launches": launches, "clocks": clocks,
@@ -1130,7 +1143,8 @@ def main():
                          "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                          "peak_source": peak_kind, "bytes_per_launch": kernel_bytes,
                          "us_per_launch": score_us,
-                         "traffic": (kernel_bytes * SELECT_DRAM_BYTES_PER_ALGORITHMIC_BYTE) if tp == 1 else None,
+                         "traffic": (kernel_bytes * (STEP_DRAM_BYTES_PER_ALGORITHMIC_BYTE if one_launch else
+                                                     SELECT_DRAM_BYTES_PER_ALGORITHMIC_BYTE)) if tp == 1 else None,
                          "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel "
                                             "at this shape under ncu (a separate run), scaled by the algorithmic bytes "
                                             "of this run's sequence length; not measured in this run")

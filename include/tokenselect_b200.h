@@ -60,7 +60,7 @@ extern "C" {
 #define TS_CFG_DIRECT_SCORE 2u    /* bf16: load keys straight into mma fragments whatever the row size */
 #define TS_CFG_EXTEND_MMA_SYNC 8u /* prefill attention with mma.sync instead of tcgen05 (diagnostic) */
 #define TS_CFG_EXTEND_FOUR_PER_ROW 16u /* prefill attention: one softmax team, four threads per query row (diagnostic) */
-#define TS_CFG_EXTEND_ONE_TEAM 512u /* prefill attention: one softmax team of two threads per row instead of two teams on alternating key blocks (diagnostic) */
+#define TS_CFG_EXTEND_NARROW_BLOCKS 512u /* prefill attention in 64-key blocks with one issuing thread, two softmax threads per row (the earlier form; diagnostic) */
 #define TS_CFG_PHASE_STAMPS 32u   /* kernels record %globaltimer at their phase boundaries for ts_debug_read(3) (diagnostic; off: no timer reads) */
 #define TS_CFG_INLINE_ATTEND 1024u /* attention inside the layer-step kernel also for batches of several requests (default: single requests only) */
 #define TS_CFG_SPLIT_ATTEND 256u  /* attention in separate kernels after the selection kernel whatever the shape (diagnostic) */

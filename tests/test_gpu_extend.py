@@ -225,10 +225,10 @@ def test_rope_scale_and_soft_cap_decode_and_chunk(dtype, tol):
     assert (out2.cpu().double() - want2).abs().max().item() <= tol
 
 
-@pytest.mark.parametrize("flags", [8, 16, 512], ids=["mma_sync_kernel", "four_threads_per_row", "one_softmax_team"])
+@pytest.mark.parametrize("flags", [8, 16, 512], ids=["mma_sync_kernel", "four_threads_per_row", "narrow_key_blocks"])
 def test_diagnostic_attention_variants_agree(flags):
     """The diagnostic variants of the prefill attention (TS_CFG_EXTEND_MMA_SYNC, TS_CFG_EXTEND_FOUR_PER_ROW,
-    TS_CFG_EXTEND_ONE_TEAM) against the oracle on a full chunk and a tail chunk."""
+    TS_CFG_EXTEND_NARROW_BLOCKS) against the oracle on a full chunk and a tail chunk."""
     hq, hkv, d, n_init, n_local, top_k, base = 8, 2, 128, 16, 512, 256, 5e5
     for seed, n, lq in ((91, 3000, 512), (92, 2100, 77)):
         case = synth.make_layer_case(seed, n, hq, hkv, d, n_init, n_local, base, dtype=BF16)

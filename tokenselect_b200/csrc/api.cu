@@ -120,7 +120,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_cnt = cv.take((size_t)c->max_reqs * 16);
     // prefill chunks: fingerprint, (length, slot) pair, compact rotated K / V / Q arrays
     const int ext = c->prefill_chunk;
-    const int rows_k = (n_sel + 63) / 64 * 64, rows_q = (ext + 127) / 128 * 128;
+    const int rows_k = (n_sel + 127) / 128 * 128, rows_q = (ext + 127) / 128 * 128;
     size_t o_xfp = cv.take(ext > 0 ? hd * elem : 16);
     size_t o_xmeta = cv.take(16);
     size_t o_xk = cv.take(ext > 0 ? (size_t)c->hkv * rows_k * c->head_dim * elem : 16);
@@ -497,6 +497,7 @@ int ts_extend_chunk(ts_handle* h, const ts_extend_args* a) {
     e.out = a->out;
     e.fp = h->ext_fp; e.meta = h->ext_meta; e.kc = h->ext_k; e.vc = h->ext_v; e.qc = h->ext_q;
     e.rows_k = h->ext_rows_k; e.rows_q = (a->chunk_len + 127) / 128 * 128;
+    e.stamps = h->base.stamps ? h->base.phase_ts : nullptr;
     e.sel_slots = h->base.sel_slots; e.sel_count = h->base.sel_count; e.attn_cs = h->base.attn_cs;
     e.err = h->base.err;
     e.wait_cycles = h->wait_cycles;

@@ -299,6 +299,7 @@ struct ExtendParams {
     const float2* attn_cs;
     int* err;
     long long wait_cycles;
+    unsigned long long* stamps; // TS_CFG_PHASE_STAMPS: where the attention kernel leaves its cycle counts, else null
 };
 
 cudaError_t launch_extend_prep(const ExtendParams& e, const Launch& l);

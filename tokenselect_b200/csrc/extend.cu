@@ -195,7 +195,7 @@ __device__ __forceinline__ void store8(T* head_base, int d, int row, int e0, con
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const ExtendParams e, const int layout) {
+__global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const ExtendParams e, const int layout, const int kv_tile) {
     if (*(volatile int*)e.err != 0) return;
     const int half = e.d / 2;
     const int tpi = half / 8;                                             // threads per (row, head) item
@@ -213,8 +213,8 @@ __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const Extend
         T* kc = reinterpret_cast<T*>(e.kc) + (size_t)kv * e.rows_k * e.d;
         T* vc = reinterpret_cast<T*>(e.vc) + (size_t)kv * e.rows_k * e.d;
         if (j >= count) {
-            store8<T>(kc, e.d, j, i0, z, layout, 64); store8<T>(kc, e.d, j, i0 + half, z, layout, 64);
-            store8<T>(vc, e.d, j, i0, z, layout, 64); store8<T>(vc, e.d, j, i0 + half, z, layout, 64);
+            store8<T>(kc, e.d, j, i0, z, layout, kv_tile); store8<T>(kc, e.d, j, i0 + half, z, layout, kv_tile);
+            store8<T>(vc, e.d, j, i0, z, layout, kv_tile); store8<T>(vc, e.d, j, i0 + half, z, layout, kv_tile);
             return;
         }
         int slot = e.sel_slots[j];
@@ -234,8 +234,8 @@ __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const Extend
             r1[u] = x1[u] * c.x - x2[u] * c.y;
             r2[u] = x2[u] * c.x + x1[u] * c.y;
         }
-        store8<T>(kc, e.d, j, i0, r1, layout, 64); store8<T>(kc, e.d, j, i0 + half, r2, layout, 64);
-        store8<T>(vc, e.d, j, i0, v1, layout, 64); store8<T>(vc, e.d, j, i0 + half, v2, layout, 64);
+        store8<T>(kc, e.d, j, i0, r1, layout, kv_tile); store8<T>(kc, e.d, j, i0 + half, r2, layout, kv_tile);
+        store8<T>(vc, e.d, j, i0, v1, layout, kv_tile); store8<T>(vc, e.d, j, i0 + half, v2, layout, kv_tile);
         return;
     }
     const int qitem = item - k_items;
@@ -790,36 +790,39 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
 }
 
 // ------------------------------------------------------------------------------------------------
-// 4a''. two softmax teams on alternating key blocks (the default)
+// 4a''. key blocks of 128, loads issued by a warp of their own (the default)
 // ------------------------------------------------------------------------------------------------
-// One softmax team cannot keep up with the tensor pipe: its per-block chain (wait for S, tcgen05.ld, row
-// maximum through shared memory, 32 exponentials per thread, pack, tcgen05.st, arrive) runs with two warps per
-// scheduler and is bound by its own latencies.  Here two teams of 256 threads run that chain on alternating key
-// blocks -- team t takes blocks t, t + 2, ... -- each with its OWN online softmax (reference maximum, row sums)
-// and its OWN output accumulator, so the teams share no state; the two (reference, sum, output) triples of a row
-// are joined once at the end.  Tensor memory (all 512 columns):
-//   S[t][u]  128 x 64 fp32, columns 64 (2t + u), u = the team's block count mod 2;  P (packed bf16, 32 columns)
-//            is written over the start of the S buffer it was computed from
-//   O[t]     128 x 128 fp32, columns 256 + 128 t
-// The issuing thread keeps the tensor pipe two key blocks ahead of the softmax: S(b + 2) = Q.K_(b+2)^T is issued
-// before it waits for P(b).  MMAs execute in issue order, so S(b + 2) lands on the buffer of block b - 2 only
-// after P(b - 2).V has read it.
-struct Tc5PairSmem {
-    unsigned char q[128 * 256];                 // 2 halves x [128 rows][128 B]
-    unsigned char k[kKvStages][kTile * 256];    // 2 halves x [64 keys][128 B]
-    unsigned char v[kKvStages][kTile * 256];
-    float rowmax[2][2][2][128];                 // [team][buffer][column half][row]
-    float fin[2][3][128];                       // [team][reference maximum, row sum of column half 0, of half 1][row]
-    uint64_t qbar, full[kKvStages], s_done[2][2], o_done[2][2], p_ready[2][2];
+// What bounds the kernels above is neither the tensor pipe nor the softmax but the ONE thread that issues the
+// asynchronous operations: measured on this part, every tcgen05.mma, tcgen05.commit, bulk copy and mbarrier
+// wait costs that thread about 80 cycles, and a 64-key block needs two dozen of them (~1950 cycles per block
+// against ~1060 cycles of softmax work and ~550 cycles of tensor-pipe time).  Two softmax teams on alternating
+// blocks did not help for that reason.  This form halves the operations per key: blocks of 128 keys (Q.K^T as
+// eight M128 x N128 x K16 MMAs instead of sixteen N64 ones, one commit and one tile request per 128 keys), and
+// the tile requests and the waits that guard them moved to a second single-thread warp.
+//   S[b&1]  128 x 128 fp32, TMEM columns 128 (b&1) ..;  P (packed bf16, 64 columns) overwrites the start of the S
+//           buffer it was computed from (all readers of the buffer have passed the row-maximum exchange by then)
+//   O       128 x 128 fp32, TMEM columns 256 .. 383
+// 512 softmax threads: thread (column quarter c = warp / 4, lane quarter w = warp % 4, lane l) owns query row
+// 32 w + l and columns [32 c, 32 c + 32) of S and of O.  K tiles (32 KB) have two stages, freed as soon as their
+// Q.K^T has run; V tiles three, freed after their P.V.
+constexpr int kWide = 128;                                   // keys per block
+constexpr int kWideKStages = 2, kWideVStages = 3;
+struct Tc5WideSmem {
+    unsigned char q[128 * 256];                  // 2 halves x [128 rows][128 B]
+    unsigned char k[kWideKStages][kWide * 256];  // 2 halves x [128 keys][128 B]
+    unsigned char v[kWideVStages][kWide * 256];
+    float rowmax[2][4][128];                     // [block parity][column quarter][row]: row maxima; row sums at the end
+    uint64_t qbar, full_k[kWideKStages], full_v[kWideVStages], s_done[4], o_done[4], p_ready[2];
     uint32_t tmem_base;
 };
+static_assert(sizeof(Tc5WideSmem) + 1024 <= 232448, "the kernel's shared memory must fit one CTA's maximum");
 
-__global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const ExtendParams e) {
+__global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const ExtendParams e) {
     constexpr int W = 32;                                    // S columns per thread
-    constexpr int OW = 64;                                   // O columns per thread
-    constexpr uint32_t kPairO = 256;
+    constexpr int OW = 32;                                   // O columns per thread
+    constexpr uint32_t kWideO = 256;
     extern __shared__ unsigned char tc5_dyn[];
-    Tc5PairSmem& sm = *reinterpret_cast<Tc5PairSmem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
+    Tc5WideSmem& sm = *reinterpret_cast<Tc5WideSmem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = blockIdx.x, h = blockIdx.y, kv = h / e.group;
     const int lq = e.chunk_len;
@@ -827,18 +830,20 @@ __global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const Ex
     const int count = min(*e.sel_count, e.n_sel);
     const int base_vis = count - lq;                         // query row r sees list entries j <= base_vis + r
     const int kmax = min(count - 1, base_vis + qt * 128 + 127);
-    const int nblk = kmax / kTile + 1;
+    const int nblk = kmax / kWide + 1;
     bool dead = false;
+    const bool timed_cta = e.stamps != nullptr && qt == 0 && h == 0;      // cycle counts under TS_CFG_PHASE_STAMPS
 
     if (tid == 0) {
         mbar_init(smem_u32(&sm.qbar), 1);
-        for (int s = 0; s < kKvStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
-        for (int t = 0; t < 2; ++t)
-            for (int u = 0; u < 2; ++u) {
-                mbar_init(smem_u32(&sm.s_done[t][u]), 1);
-                mbar_init(smem_u32(&sm.o_done[t][u]), 1);
-                mbar_init(smem_u32(&sm.p_ready[t][u]), 8);   // the team's eight warps
-            }
+        for (int s = 0; s < kWideKStages; ++s) mbar_init(smem_u32(&sm.full_k[s]), 1);
+        for (int s = 0; s < kWideVStages; ++s) mbar_init(smem_u32(&sm.full_v[s]), 1);
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(smem_u32(&sm.s_done[s]), 1);
+            mbar_init(smem_u32(&sm.o_done[s]), 1);
+        }
+        mbar_init(smem_u32(&sm.p_ready[0]), 16);             // the sixteen softmax warps
+        mbar_init(smem_u32(&sm.p_ready[1]), 16);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -850,79 +855,102 @@ __global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const Ex
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *(volatile uint32_t*)&sm.tmem_base;
+    constexpr uint32_t kTileBytes = kWide * 256;             // one K or V tile image
 
-    if (warp == 16) {
-        // ---------------- issuer ----------------
+    if (warp == 17) {
+        // ---------------- loader: one thread requests every tile ----------------
         if (lane == 0) {
             const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
             const unsigned char* ksrc = reinterpret_cast<const unsigned char*>(e.kc) + (size_t)kv * e.rows_k * 256;
             const unsigned char* vsrc = reinterpret_cast<const unsigned char*>(e.vc) + (size_t)kv * e.rows_k * 256;
-            constexpr uint32_t kTileBytes = kTile * 256;     // one K or V tile image
-            auto load_tile = [&](int b) {
-                const int st = b % kKvStages;
-                mbar_expect_tx(smem_u32(&sm.full[st]), 2 * kTileBytes);
-                bulk_g2s(smem_u32(sm.k[st]), ksrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
-                bulk_g2s(smem_u32(sm.v[st]), vsrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full[st]));
-            };
-            constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((64u >> 3) << 17) | ((128u >> 4) << 24);
+            mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
+            bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
+            for (int b = 0; b < nblk; ++b) {
+                if (b >= kWideKStages) {                     // the stage's previous tile: its Q.K^T has run
+                    const int pb = b - kWideKStages;
+                    mbar_wait(smem_u32(&sm.s_done[pb & 3]), (uint32_t)((pb >> 2) & 1), e.err, dead, 46, e.wait_cycles);
+                }
+                mbar_expect_tx(smem_u32(&sm.full_k[b % kWideKStages]), kTileBytes);
+                bulk_g2s(smem_u32(sm.k[b % kWideKStages]), ksrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full_k[b % kWideKStages]));
+                if (b >= kWideVStages) {                     // the stage's previous tile: its P.V has run
+                    const int pb = b - kWideVStages;
+                    mbar_wait(smem_u32(&sm.o_done[pb & 3]), (uint32_t)((pb >> 2) & 1), e.err, dead, 49, e.wait_cycles);
+                }
+                mbar_expect_tx(smem_u32(&sm.full_v[b % kWideVStages]), kTileBytes);
+                bulk_g2s(smem_u32(sm.v[b % kWideVStages]), vsrc + (size_t)b * kTileBytes, kTileBytes, smem_u32(&sm.full_v[b % kWideVStages]));
+            }
+        }
+    } else if (warp == 16) {
+        // ---------------- issuer: one thread issues every MMA ----------------
+        if (lane == 0) {
+            // instruction descriptors: fp32 accumulate, bf16 A and B, M = 128, N = 128; B K-major (Q.K^T) / MN-major (P.V)
+            constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
             constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-            auto issue_qk = [&](int b) {                     // S[t][u] = Q . K_b^T
-                const int st = b % kKvStages, t = b & 1, u = (b >> 1) & 1;
-                mbar_wait(smem_u32(&sm.full[st]), (uint32_t)((b / kKvStages) & 1), e.err, dead, 42, e.wait_cycles);
+            long long w_k = 0, w_p = 0, w_v = 0, c0 = 0;
+            const long long t_begin = clock64();
+            auto issue_qk = [&](int b) {                     // S[b&1] = Q . K_b^T
+                const int st = b % kWideKStages;
+                mbar_wait(smem_u32(&sm.full_k[st]), (uint32_t)((b / kWideKStages) & 1), e.err, dead, 42, e.wait_cycles);
                 tc_fence_after();
                 const uint32_t qa = smem_u32(sm.q), ka = smem_u32(sm.k[st]);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off_q = (ks >> 2) * (128u * 128u) + (ks & 3) * 32u;
-                    const uint32_t off_k = (ks >> 2) * (kTile * 128u) + (ks & 3) * 32u;
-                    umma_bf16(tmem + 64u * (2 * t + u), umma_desc_sw128(qa + off_q, 16, 1024),
+                    const uint32_t off_k = (ks >> 2) * (kWide * 128u) + (ks & 3) * 32u;
+                    umma_bf16(tmem + 128u * (b & 1), umma_desc_sw128(qa + off_q, 16, 1024),
                               umma_desc_sw128(ka + off_k, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&sm.s_done[t][u]));
+                umma_commit(smem_u32(&sm.s_done[b & 3]));
             };
-            mbar_expect_tx(smem_u32(&sm.qbar), 128 * 256);
-            bulk_g2s(smem_u32(sm.q), qsrc, 128 * 256, smem_u32(&sm.qbar));
-            for (int b = 0; b < kKvStages && b < nblk; ++b) load_tile(b);
             mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40, e.wait_cycles);
             issue_qk(0);
-            if (nblk > 1) issue_qk(1);
             for (int blk = 0; blk < nblk; ++blk) {
-                const int t = blk & 1, i = blk >> 1, u = i & 1;
-                if (blk + 2 < nblk) issue_qk(blk + 2);
-                if (blk > 0 && blk - 1 + kKvStages < nblk) {
-                    // P.V of the previous block is complete: its stage can take the tile four blocks ahead
-                    const int pb = blk - 1;
-                    mbar_wait(smem_u32(&sm.o_done[pb & 1][(pb >> 1) & 1]), (uint32_t)((pb >> 2) & 1), e.err, dead, 46, e.wait_cycles);
-                    load_tile(blk - 1 + kKvStages);
-                }
-                mbar_wait(smem_u32(&sm.p_ready[t][u]), (uint32_t)((i >> 1) & 1), e.err, dead, 47, e.wait_cycles);
+                if (timed_cta) c0 = clock64();
+                if (blk + 1 < nblk) issue_qk(blk + 1);
+                if (timed_cta) { const long long c = clock64(); w_k += c - c0; c0 = c; }
+                mbar_wait(smem_u32(&sm.p_ready[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 47, e.wait_cycles);
+                if (timed_cta) { const long long c = clock64(); w_p += c - c0; c0 = c; }
+                mbar_wait(smem_u32(&sm.full_v[blk % kWideVStages]), (uint32_t)((blk / kWideVStages) & 1), e.err, dead, 41, e.wait_cycles);
+                if (timed_cta) { const long long c = clock64(); w_v += c - c0; c0 = c; }
                 tc_fence_after();
-                const uint32_t va = smem_u32(sm.v[blk % kKvStages]);
+                const uint32_t va = smem_u32(sm.v[blk % kWideVStages]);
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)               // 16 keys per step: 8 packed columns of P
-                    umma_bf16_ts(tmem + kPairO + 128u * t, tmem + 64u * (2 * t + u) + 8u * ks,
-                                 umma_desc_sw128(va + ks * 2048u, kTile * 128u, 1024), kIdescPV, (i > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&sm.o_done[t][u]));
+                for (int ks = 0; ks < 8; ++ks)               // 16 keys per step: 8 packed columns of P
+                    umma_bf16_ts(tmem + kWideO, tmem + 128u * (blk & 1) + 8u * ks,
+                                 umma_desc_sw128(va + ks * 2048u, kWide * 128u, 1024), kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(smem_u32(&sm.o_done[blk & 3]));
+            }
+            if (timed_cta) {
+                e.stamps[64] = (unsigned long long)(clock64() - t_begin);     // issuer: its whole loop
+                e.stamps[65] = (unsigned long long)w_k;                        // Q.K^T issue incl. the wait for the K tile
+                e.stamps[66] = 0ull;
+                e.stamps[67] = (unsigned long long)w_p;                        // wait for P
+                e.stamps[68] = (unsigned long long)w_v;                        // wait for the V tile
+                e.stamps[69] = (unsigned long long)nblk;
             }
         }
     } else {
-        // ---------------- softmax teams ----------------
-        const int team = warp >> 3, cq = (warp >> 2) & 1, rq = warp & 3;   // team, column half, row (lane) quarter
+        // ---------------- softmax ----------------
+        const int cq = warp >> 2, rq = warp & 3;             // column quarter, row (lane) quarter
         const int r_in = rq * 32 + lane;                     // row inside the 128-row tile
         const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
-        const uint32_t t_o = tmem + lane_base + kPairO + 128u * team + (uint32_t)(OW * cq);
+        const uint32_t t_o = tmem + lane_base + kWideO + (uint32_t)(OW * cq);
         const int row = qt * 128 + r_in;
         const int lim = base_vis + row;
         const float cap = e.logit_cap;
         const float mul = cap > 0.f ? 1.f : e.sm_scale * kLog2eX;     // x * mul is the logit in base-2 units
         float m_ref = 0.f, l_run = 0.f;
-        int i = 0;
-        for (int blk = team; blk < nblk; blk += 2, ++i) {
-            const int u = i & 1;
-            const uint32_t t_s = tmem + lane_base + 64u * (2 * team + u) + (uint32_t)(W * cq);
-            const uint32_t t_p = tmem + lane_base + 64u * (2 * team + u) + (uint32_t)(W / 2 * cq);
-            mbar_wait(smem_u32(&sm.s_done[team][u]), (uint32_t)((i >> 1) & 1), e.err, dead, 43, e.wait_cycles);
+        const bool timed = timed_cta && warp == 0 && lane == 0;
+        long long c_s = 0, c_ld = 0, c_bar = 0, c_exp = 0, c_st = 0, c0 = 0;
+        const long long t_begin = clock64();
+
+        for (int blk = 0; blk < nblk; ++blk) {
+            const uint32_t t_s = tmem + lane_base + 128u * (blk & 1) + (uint32_t)(W * cq);
+            const uint32_t t_p = tmem + lane_base + 128u * (blk & 1) + (uint32_t)(W / 2 * cq);
+            if (timed) c0 = clock64();
+            mbar_wait(smem_u32(&sm.s_done[blk & 3]), (uint32_t)((blk >> 2) & 1), e.err, dead, 43, e.wait_cycles);
             tc_fence_after();
+            if (timed) { const long long c = clock64(); c_s += c - c0; c0 = c; }
             float x[W];
             {
                 uint32_t r0[W / 16][16];
@@ -932,13 +960,15 @@ __global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const Ex
 #pragma unroll
                 for (int c = 0; c < W; ++c) x[c] = __uint_as_float(r0[c / 16][c % 16]);
             }
+            if (timed) { const long long c = clock64(); c_ld += c - c0; c0 = c; }
+            // x keeps S in raw units unless the soft cap is on; the scale goes into the exponent's FMA
             float mx = -INFINITY;
-            const int key0 = blk * kTile + W * cq;
+            const int key0 = blk * kWide + W * cq;
             if (cap > 0.f) {
 #pragma unroll
                 for (int c = 0; c < W; ++c) x[c] = cap * tanhf(x[c] * e.sm_scale / cap) * kLog2eX;
             }
-            if (blk * kTile + kTile - 1 > base_vis + qt * 128) {      // only blocks that reach the diagonal are masked
+            if (blk * kWide + kWide - 1 > base_vis + qt * 128) {      // only blocks that reach the diagonal are masked
 #pragma unroll
                 for (int c = 0; c < W; ++c)
                     if (key0 + c > lim) x[c] = -INFINITY;
@@ -946,16 +976,17 @@ __global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const Ex
 #pragma unroll
             for (int c = 0; c < W; ++c) mx = fmaxf(mx, x[c]);
             mx *= mul;                                               // base-2 units (mul > 0)
-            float* rm = &sm.rowmax[team][u][0][r_in];
+            float* rm = &sm.rowmax[blk & 1][0][r_in];
             rm[cq * 128] = mx;
-            // the two warps that share these rows; both have read their S columns by now, so P may overwrite them
-            named_bar_sync(1 + 4 * team + rq, 64);
-            mx = fmaxf(rm[0], rm[128]);
-            if (i > 0) {
+            // the four warps that share these rows; all have read their S columns by now, so P may overwrite them
+            named_bar_sync(1 + rq, 128);
+            mx = fmaxf(fmaxf(rm[0], rm[128]), fmaxf(rm[256], rm[384]));
+            if (timed) { const long long c = clock64(); c_bar += c - c0; c0 = c; }
+            if (blk > 0) {
                 const bool grow = mx > m_ref + 8.f;
                 if (__any_sync(0xffffffffu, grow)) {
-                    // O is rescaled in place: the team's P.V issued so far must be complete (they run in order)
-                    mbar_wait(smem_u32(&sm.o_done[team][(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1), e.err, dead, 44, e.wait_cycles);
+                    // O is rescaled in place: every P.V issued so far must be complete (they run in order)
+                    mbar_wait(smem_u32(&sm.o_done[(blk - 1) & 3]), (uint32_t)(((blk - 1) >> 2) & 1), e.err, dead, 44, e.wait_cycles);
                     tc_fence_after();
                     const float corr = grow ? ex2_fast(m_ref - mx) : 1.f;
 #pragma unroll 1
@@ -981,61 +1012,48 @@ __global__ void __launch_bounds__(544, 1) extend_attend_tc5_pair_kernel(const Ex
                 sum += p0 + p1;
                 w[c / 8][c % 8] = pack_bf16(p0, p1);
             }
+            if (timed) { const long long c = clock64(); c_exp += c - c0; c0 = c; }
 #pragma unroll
             for (int j = 0; j < W / 16; ++j) tmem_st8(t_p + 8u * j, w[j]);
             tmem_wait_st();
             l_run += sum;
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[team][u]));
+            if (lane == 0) mbar_arrive(smem_u32(&sm.p_ready[blk & 1]));
+            if (timed) { const long long c = clock64(); c_st += c - c0; c0 = c; }
         }
-        // what the join needs: the team's reference maximum and row sums; the team's last P.V must have landed
-        if (cq == 0) sm.fin[team][0][r_in] = m_ref;
-        sm.fin[team][1 + cq][r_in] = l_run;
-        if (i > 0) {
-            mbar_wait(smem_u32(&sm.o_done[team][(i - 1) & 1]), (uint32_t)(((i - 1) >> 1) & 1), e.err, dead, 45, e.wait_cycles);
-            tc_fence_after();
+        if (timed) {
+            unsigned long long* o = e.stamps + 72;
+            o[0] = (unsigned long long)(clock64() - t_begin);   // the softmax loop
+            o[1] = (unsigned long long)c_s;                      // wait for S
+            o[2] = (unsigned long long)c_ld;                     // tcgen05.ld + wait
+            o[3] = (unsigned long long)c_bar;                    // mask, maximum, exchange with the other column quarters
+            o[4] = (unsigned long long)c_exp;                    // (rescale,) exponentials, pack
+            o[5] = (unsigned long long)c_st;                     // tcgen05.st + wait, arrive
+            o[6] = (unsigned long long)nblk;
         }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp < 8) {
-        // ---------------- join of the two teams' results, by team 0's threads ----------------
-        tc_fence_after();
-        const int cq = (warp >> 2) & 1, rq = warp & 3, r_in = rq * 32 + lane;
-        const int row = qt * 128 + r_in;
-        const uint32_t lane_base = (uint32_t)(rq * 32) << 16;
-        const bool two = nblk > 1;
-        const float m0 = sm.fin[0][0][r_in], l0 = sm.fin[0][1][r_in] + sm.fin[0][2][r_in];
-        const float m1 = two ? sm.fin[1][0][r_in] : m0, l1 = two ? sm.fin[1][1][r_in] + sm.fin[1][2][r_in] : 0.f;
-        const float mm = fmaxf(l0 > 0.f ? m0 : -INFINITY, l1 > 0.f ? m1 : -INFINITY);   // a team without weight sets no scale
-        const float w0 = l0 > 0.f ? ex2_fast(m0 - mm) : 0.f, w1 = l1 > 0.f ? ex2_fast(m1 - mm) : 0.f;
-        const float l_tot = w0 * l0 + w1 * l1;
+        // row sums: the four partial sums of a row share the reference maximum
+        float* rs = &sm.rowmax[nblk & 1][0][r_in];
+        rs[cq * 128] = l_run;
+        named_bar_sync(1 + rq, 128);
+        const float l_tot = (rs[0] + rs[128]) + (rs[256] + rs[384]);
         const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
-        const float s0 = w0 * inv, s1 = w1 * inv;
+        mbar_wait(smem_u32(&sm.o_done[(nblk - 1) & 3]), (uint32_t)(((nblk - 1) >> 2) & 1), e.err, dead, 45, e.wait_cycles);
+        tc_fence_after();
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(e.out) + (size_t)row * e.hq * 128 + (size_t)h * 128 + OW * cq;
 #pragma unroll 1
         for (int j = 0; j < OW / 16; ++j) {
             uint32_t r[16];
-            float o[16];
-            tmem_ld16(tmem + lane_base + kPairO + (uint32_t)(OW * cq) + 16u * j, r);
+            tmem_ld16(t_o + 16u * j, r);
             tmem_wait_ld();
-#pragma unroll
-            for (int c = 0; c < 16; ++c) o[c] = s0 > 0.f ? __uint_as_float(r[c]) * s0 : 0.f;
-            if (two) {                                       // (a team that never ran leaves its accumulator unwritten)
-                tmem_ld16(tmem + lane_base + kPairO + 128u + (uint32_t)(OW * cq) + 16u * j, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 16; ++c) o[c] += s1 > 0.f ? __uint_as_float(r[c]) * s1 : 0.f;
-            }
             if (row < lq) {
 #pragma unroll
                 for (int c8 = 0; c8 < 2; ++c8) {
                     uint4 w;
-                    w.x = pack_bf16(o[c8 * 8 + 0], o[c8 * 8 + 1]);
-                    w.y = pack_bf16(o[c8 * 8 + 2], o[c8 * 8 + 3]);
-                    w.z = pack_bf16(o[c8 * 8 + 4], o[c8 * 8 + 5]);
-                    w.w = pack_bf16(o[c8 * 8 + 6], o[c8 * 8 + 7]);
+                    w.x = pack_bf16(__uint_as_float(r[c8 * 8 + 0]) * inv, __uint_as_float(r[c8 * 8 + 1]) * inv);
+                    w.y = pack_bf16(__uint_as_float(r[c8 * 8 + 2]) * inv, __uint_as_float(r[c8 * 8 + 3]) * inv);
+                    w.z = pack_bf16(__uint_as_float(r[c8 * 8 + 4]) * inv, __uint_as_float(r[c8 * 8 + 5]) * inv);
+                    w.w = pack_bf16(__uint_as_float(r[c8 * 8 + 6]) * inv, __uint_as_float(r[c8 * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(out + 16 * j + c8 * 8) = w;
                 }
             }
@@ -1120,12 +1138,14 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     const int items = e.rows_k * e.hkv + e.rows_q * e.hq;
     const int per_block = kExtThreads / (half / 8);
     const bool tc5 = tc && !(l.flags & TS_CFG_EXTEND_MMA_SYNC);
+    const bool wide = tc5 && !(l.flags & (TS_CFG_EXTEND_FOUR_PER_ROW | TS_CFG_EXTEND_NARROW_BLOCKS));
     const int layout = tc5 ? kLayoutImage : tc ? kLayoutXor16 : kLayoutPlain;
+    const int kv_tile = wide ? kWide : kTile;                // keys per K / V tile image
     stage_begin(l, kStageExtendGather);
     if (l.dtype == TS_DTYPE_BF16)
-        extend_gather_kernel<__nv_bfloat16><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, layout);
+        extend_gather_kernel<__nv_bfloat16><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, layout, kv_tile);
     else
-        extend_gather_kernel<float><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, layout);
+        extend_gather_kernel<float><<<(items + per_block - 1) / per_block, kExtThreads, 0, l.stream>>>(e, layout, kv_tile);
     stage_end(l);
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return err;
@@ -1133,12 +1153,12 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
     if (tc5) {
         static SmemConfig configured5 = {};
         const size_t smem5 = sizeof(Tc5Smem) + 1024;
-        if (!(l.flags & (TS_CFG_EXTEND_FOUR_PER_ROW | TS_CFG_EXTEND_ONE_TEAM))) {
-            static SmemConfig configured_pair = {};
-            const size_t smem_pair = sizeof(Tc5PairSmem) + 1024;
-            err = ensure_dynamic_smem(extend_attend_tc5_pair_kernel, smem_pair, configured_pair);
+        if (wide) {
+            static SmemConfig configured_wide = {};
+            const size_t smem_wide = sizeof(Tc5WideSmem) + 1024;
+            err = ensure_dynamic_smem(extend_attend_tc5_wide_kernel, smem_wide, configured_wide);
             if (err != cudaSuccess) return err;
-            extend_attend_tc5_pair_kernel<<<dim3(e.rows_q / 128, e.hq), 544, smem_pair, l.stream>>>(e);
+            extend_attend_tc5_wide_kernel<<<dim3(e.rows_q / 128, e.hq), 576, smem_wide, l.stream>>>(e);
         } else if (!(l.flags & TS_CFG_EXTEND_FOUR_PER_ROW)) {
             static SmemConfig configured2 = {};
             err = ensure_dynamic_smem(extend_attend_tc5_kernel<2>, smem5, configured2);

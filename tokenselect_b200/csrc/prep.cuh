@@ -128,13 +128,28 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
         float dot = 0.f, qq = 0.f, cc = 0.f;
         const bool have = p.valid[(size_t)req * p.n_layers + p.layer] != 0;
         if (have) {
+            // sixteen elements per lane are requested together (the sums stay in ascending order): this warp is
+            // on the critical path of every layer when the cache is on, and one round trip per element would
+            // cost it tens of microseconds
+            constexpr int kBatch = 16;
 #pragma unroll 1
-            for (int e = tid; e < hd; e += 32) {
-                float a = to_f32<T>(qr[e]);
-                float c = to_f32<T>(fp[e]);
-                dot = __fadd_rn(dot, __fmul_rn(a, c));
-                qq = __fadd_rn(qq, __fmul_rn(a, a));
-                cc = __fadd_rn(cc, __fmul_rn(c, c));
+            for (int e0 = tid; e0 < hd; e0 += 32 * kBatch) {
+                float a[kBatch], c[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int e = e0 + 32 * u;
+                    const bool in = e < hd;
+                    a[u] = in ? to_f32<T>(qr[e]) : 0.f;
+                    c[u] = in ? to_f32<T>(fp[e]) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    if (e0 + 32 * u < hd) {
+                        dot = __fadd_rn(dot, __fmul_rn(a[u], c[u]));
+                        qq = __fadd_rn(qq, __fmul_rn(a[u], a[u]));
+                        cc = __fadd_rn(cc, __fmul_rn(c[u], c[u]));
+                    }
+                }
             }
 #pragma unroll
             for (int o = 16; o >= 1; o >>= 1) {
