@@ -557,13 +557,15 @@ def run_batch_config(args, which):
                                            want_pos[N_INIT:N_INIT + top_k].numpy() - N_INIT,
                                            info["votes"].double().numpy(), top_k)
             check["oracle_match"], check["oracle_detail"] = bool(ok), why
-            err = 0.0
+            err, beyond, ref_max = 0.0, 0.0, 0.0
             for r in range(tp):
                 ref = orc.sparse_attention(q_sub[r].view(hq, D), k_sub[r], v_sub[r], got_pos[:n_sel].long(), D ** -0.5, base, 1.0,
                                            0.0, torch.float64).reshape(-1)
-                err = max(err, (o_sub[r].double() - ref).abs().max().item())
-            check["attn_max_abs_err"] = err
-            check["ok"] = bool(check["ranks_agree"] and ok and err <= 2e-2)
+                e1, b1, m1 = attention_error(o_sub[r], ref)
+                err, beyond, ref_max = max(err, e1), max(beyond, b1), max(ref_max, m1)
+            check["attn_max_abs_err"], check["attn_max_err_beyond_output_rounding"] = err, beyond
+            check["attn_ref_max_abs"] = ref_max
+            check["ok"] = bool(check["ranks_agree"] and ok and beyond <= 2e-2)
         flag = torch.tensor([1 if (rank != 0 or check["ok"]) else 0], device=dev)
         if tp > 1:
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -741,8 +743,9 @@ def run_prefill(args):
         # cycle counts the attention kernel's CTA (0, 0) left on its last launch (TS_CFG_PHASE_STAMPS)
         ts = eng.debug_read(3, 128, torch.int64).tolist()
         names = ["loop", "wait S", "tcgen05.ld", "mask+max+exchange", "exp+pack", "tcgen05.st+arrive", "blocks"]
-        inames = ["loop", "QK issue + K tile wait", "-", "wait P", "wait V tile", "blocks"]
-        print("prefill attention, cycles of CTA (0,0): issuing thread " + str(dict(zip(inames, ts[64:70])))
+        inames = ["QK thread: loop", "QK: K tile wait + 8 MMAs + commit", "QK: wait for the S buffer", "PV thread: wait P",
+                  "PV: wait V tile", "blocks", "PV: 8 MMAs + commit"]
+        print("prefill attention, cycles of CTA (0,0): issuing threads " + str(dict(zip(inames, ts[64:71])))
               + "; softmax warp 0 " + str(dict(zip(names, ts[72:79]))), file=sys.stderr, flush=True)
     n_sel = N_INIT + TOP_K + N_LOCAL
     count = min(ctx, n_sel)
@@ -764,6 +767,15 @@ def run_prefill(args):
         "gpu_launches": launches, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
+
+
+def attention_error(out, ref):
+    """(max |out - ref|, max of |out - ref| - 2^-8 |ref|, max |ref|).  The output is rounded to bf16, which alone
+    moves an element by up to half a bf16 step = 2^-8 of its magnitude; the synthetic V rows carry outlier channels
+    (x 8), so outputs of magnitude 10 and more occur and their rounding exceeds any fixed absolute bound.  The check
+    therefore holds the error BEYOND that rounding to the 2e-2 the tests use for outputs of order one."""
+    d = (out.double() - ref).abs()
+    return d.max().item(), (d - ref.abs() * 2.0 ** -8).max().item(), ref.abs().max().item()
 
 
 def print_phase_times(eng, rank, tp):
@@ -793,7 +805,8 @@ def correctness_check(eng, dist, rank, tp, q, k_new, v_new, loc, k_pool, v_pool,
     must hold the same row list; the list must equal the oracle's tensor-parallel emulation (rank-local head
     map, votes summed over ranks, one top-k: token_retrieval.py:357-372) under the index-set rule (equal
     except inside the 1e-4 relative band of the k-th vote); each rank's attention output must agree with
-    the oracle's fp64 attention over its own heads within 2e-2.  Returns the result on rank 0, None elsewhere."""
+    the oracle's fp64 attention over its own heads within 2e-2 plus the output's own bf16 rounding (attention_error).
+    Returns the result on rank 0, None elsewhere."""
     dbg = eng.new_debug_buffers(1)
     out = eng.decode_layer(0, q, k_new, v_new, loc, k_pool, v_pool, rtt, ridx, lens, debug=dbg)
     torch.cuda.synchronize()
@@ -829,14 +842,15 @@ def correctness_check(eng, dist, rank, tp, q, k_new, v_new, loc, k_pool, v_pool,
                       torch.equal(pos.cpu()[N_INIT + TOP_K:], want_pos[N_INIT + TOP_K:].to(torch.int32)))
     res["oracle_match"] = bool(ok and windows_ok)
     res["oracle_detail"] = why
-    err = 0.0
+    err, beyond, ref_max = 0.0, 0.0, 0.0
     sl = all_slots[0].cpu()
     for r in range(tp):
         ref = orc.sparse_attention(all_q[r].cpu().view(hq_r, D), all_k[r], all_v[r], sl, D ** -0.5, ROPE_BASE, 1.0,
                                    0.0, torch.float64).reshape(-1)
-        err = max(err, (all_out[r].cpu().double() - ref).abs().max().item())
-    res["attn_max_abs_err"] = err
-    res["ok"] = bool(res["ranks_agree"] and res["oracle_match"] and err <= 2e-2)
+        e1, b1, m1 = attention_error(all_out[r].cpu(), ref)
+        err, beyond, ref_max = max(err, e1), max(beyond, b1), max(ref_max, m1)
+    res["attn_max_abs_err"], res["attn_max_err_beyond_output_rounding"], res["attn_ref_max_abs"] = err, beyond, ref_max
+    res["ok"] = bool(res["ranks_agree"] and res["oracle_match"] and beyond <= 2e-2)
     return res
 
 

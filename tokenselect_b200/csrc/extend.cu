@@ -799,9 +799,13 @@ __global__ void __launch_bounds__(128 * NS + 32, 1) extend_attend_tc5_kernel(con
 // blocks did not help for that reason.  This form halves the operations per key: blocks of 128 keys (Q.K^T as
 // eight M128 x N128 x K16 MMAs instead of sixteen N64 ones, one commit and one tile request per 128 keys), and
 // the tile requests and the waits that guard them moved to a second single-thread warp.
-//   S[b&1]  128 x 128 fp32, TMEM columns 128 (b&1) ..;  P (packed bf16, 64 columns) overwrites the start of the S
-//           buffer it was computed from (all readers of the buffer have passed the row-maximum exchange by then)
+//   S[b&1]  128 x 128 fp32, TMEM columns 128 (b&1) ..
 //   O       128 x 128 fp32, TMEM columns 256 .. 383
+//   P[b&1]  128 x 128 packed bf16 = 64 columns, TMEM columns 384 + 64 (b&1) ..
+// TWO issuing threads (different warps): one issues every Q.K^T as soon as the S buffer has been read (two blocks
+// ahead of the softmax), the other every P.V as soon as P is written; they touch disjoint tensor memory (S / O, P),
+// and every dependency between them and the softmax goes through an mbarrier (S written -> s_done, S read and P
+// written -> p_ready, P read -> o_done).
 // 512 softmax threads: thread (column quarter c = warp / 4, lane quarter w = warp % 4, lane l) owns query row
 // 32 w + l and columns [32 c, 32 c + 32) of S and of O.  K tiles (32 KB) have two stages, freed as soon as their
 // Q.K^T has run; V tiles three, freed after their P.V.
@@ -817,10 +821,10 @@ struct Tc5WideSmem {
 };
 static_assert(sizeof(Tc5WideSmem) + 1024 <= 232448, "the kernel's shared memory must fit one CTA's maximum");
 
-__global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const ExtendParams e) {
+__global__ void __launch_bounds__(608, 1) extend_attend_tc5_wide_kernel(const ExtendParams e) {
     constexpr int W = 32;                                    // S columns per thread
     constexpr int OW = 32;                                   // O columns per thread
-    constexpr uint32_t kWideO = 256;
+    constexpr uint32_t kWideO = 256, kWideP = 384;            // TMEM columns of O and of the two P buffers (64 each)
     extern __shared__ unsigned char tc5_dyn[];
     Tc5WideSmem& sm = *reinterpret_cast<Tc5WideSmem*>(tc5_dyn + ((1024u - (smem_u32(tc5_dyn) & 1023u)) & 1023u));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -857,7 +861,7 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
     const uint32_t tmem = *(volatile uint32_t*)&sm.tmem_base;
     constexpr uint32_t kTileBytes = kWide * 256;             // one K or V tile image
 
-    if (warp == 17) {
+    if (warp == 18) {
         // ---------------- loader: one thread requests every tile ----------------
         if (lane == 0) {
             const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
@@ -881,14 +885,20 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
             }
         }
     } else if (warp == 16) {
-        // ---------------- issuer: one thread issues every MMA ----------------
+        // ---------------- first issuing thread: every Q.K^T ----------------
         if (lane == 0) {
-            // instruction descriptors: fp32 accumulate, bf16 A and B, M = 128, N = 128; B K-major (Q.K^T) / MN-major (P.V)
+            // instruction descriptor: fp32 accumulate, bf16 A and B, M = 128, N = 128, B K-major
             constexpr uint32_t kIdescQK = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-            constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-            long long w_k = 0, w_p = 0, w_v = 0, c0 = 0;
+            long long w_k = 0, w_s = 0, c0 = 0;
             const long long t_begin = clock64();
-            auto issue_qk = [&](int b) {                     // S[b&1] = Q . K_b^T
+            mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40, e.wait_cycles);
+            for (int b = 0; b < nblk; ++b) {
+                if (timed_cta) c0 = clock64();
+                if (b >= 2) {                                // the S buffer's previous block has been read by the softmax
+                    const int pb = b - 2;
+                    mbar_wait(smem_u32(&sm.p_ready[pb & 1]), (uint32_t)((pb >> 1) & 1), e.err, dead, 47, e.wait_cycles);
+                }
+                if (timed_cta) { const long long c = clock64(); w_s += c - c0; c0 = c; }
                 const int st = b % kWideKStages;
                 mbar_wait(smem_u32(&sm.full_k[st]), (uint32_t)((b / kWideKStages) & 1), e.err, dead, 42, e.wait_cycles);
                 tc_fence_after();
@@ -901,13 +911,23 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
                               umma_desc_sw128(ka + off_k, 16, 1024), kIdescQK, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&sm.s_done[b & 3]));
-            };
-            mbar_wait(smem_u32(&sm.qbar), 0, e.err, dead, 40, e.wait_cycles);
-            issue_qk(0);
+                if (timed_cta) { const long long c = clock64(); w_k += c - c0; c0 = c; }
+            }
+            if (timed_cta) {
+                e.stamps[64] = (unsigned long long)(clock64() - t_begin);     // its whole loop
+                e.stamps[65] = (unsigned long long)w_k;                        // wait for the K tile, 8 MMAs, commit
+                e.stamps[66] = (unsigned long long)w_s;                        // wait for the S buffer
+                e.stamps[69] = (unsigned long long)nblk;
+            }
+        }
+    } else if (warp == 17) {
+        // ---------------- second issuing thread: every P.V ----------------
+        if (lane == 0) {
+            // fp32 accumulate, bf16 A (tensor memory) and B (MN-major), M = 128, N = 128
+            constexpr uint32_t kIdescPV = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            long long w_p = 0, w_v = 0, w_i = 0, c0 = 0;
             for (int blk = 0; blk < nblk; ++blk) {
                 if (timed_cta) c0 = clock64();
-                if (blk + 1 < nblk) issue_qk(blk + 1);
-                if (timed_cta) { const long long c = clock64(); w_k += c - c0; c0 = c; }
                 mbar_wait(smem_u32(&sm.p_ready[blk & 1]), (uint32_t)((blk >> 1) & 1), e.err, dead, 47, e.wait_cycles);
                 if (timed_cta) { const long long c = clock64(); w_p += c - c0; c0 = c; }
                 mbar_wait(smem_u32(&sm.full_v[blk % kWideVStages]), (uint32_t)((blk / kWideVStages) & 1), e.err, dead, 41, e.wait_cycles);
@@ -916,17 +936,15 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
                 const uint32_t va = smem_u32(sm.v[blk % kWideVStages]);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)               // 16 keys per step: 8 packed columns of P
-                    umma_bf16_ts(tmem + kWideO, tmem + 128u * (blk & 1) + 8u * ks,
+                    umma_bf16_ts(tmem + kWideO, tmem + kWideP + 64u * (blk & 1) + 8u * ks,
                                  umma_desc_sw128(va + ks * 2048u, kWide * 128u, 1024), kIdescPV, (blk > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(smem_u32(&sm.o_done[blk & 3]));
+                if (timed_cta) { const long long c = clock64(); w_i += c - c0; c0 = c; }
             }
             if (timed_cta) {
-                e.stamps[64] = (unsigned long long)(clock64() - t_begin);     // issuer: its whole loop
-                e.stamps[65] = (unsigned long long)w_k;                        // Q.K^T issue incl. the wait for the K tile
-                e.stamps[66] = 0ull;
                 e.stamps[67] = (unsigned long long)w_p;                        // wait for P
                 e.stamps[68] = (unsigned long long)w_v;                        // wait for the V tile
-                e.stamps[69] = (unsigned long long)nblk;
+                e.stamps[70] = (unsigned long long)w_i;                        // 8 MMAs, commit
             }
         }
     } else {
@@ -946,7 +964,7 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
 
         for (int blk = 0; blk < nblk; ++blk) {
             const uint32_t t_s = tmem + lane_base + 128u * (blk & 1) + (uint32_t)(W * cq);
-            const uint32_t t_p = tmem + lane_base + 128u * (blk & 1) + (uint32_t)(W / 2 * cq);
+            const uint32_t t_p = tmem + lane_base + kWideP + 64u * (blk & 1) + (uint32_t)(W / 2 * cq);
             if (timed) c0 = clock64();
             mbar_wait(smem_u32(&sm.s_done[blk & 3]), (uint32_t)((blk >> 2) & 1), e.err, dead, 43, e.wait_cycles);
             tc_fence_after();
@@ -978,8 +996,7 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
             mx *= mul;                                               // base-2 units (mul > 0)
             float* rm = &sm.rowmax[blk & 1][0][r_in];
             rm[cq * 128] = mx;
-            // the four warps that share these rows; all have read their S columns by now, so P may overwrite them
-            named_bar_sync(1 + rq, 128);
+            named_bar_sync(1 + rq, 128);                     // the four warps that share these rows
             mx = fmaxf(fmaxf(rm[0], rm[128]), fmaxf(rm[256], rm[384]));
             if (timed) { const long long c = clock64(); c_bar += c - c0; c0 = c; }
             if (blk > 0) {
@@ -1013,6 +1030,10 @@ __global__ void __launch_bounds__(576, 1) extend_attend_tc5_wide_kernel(const Ex
                 w[c / 8][c % 8] = pack_bf16(p0, p1);
             }
             if (timed) { const long long c = clock64(); c_exp += c - c0; c0 = c; }
+            if (blk >= 2) {                                  // P.V of block blk-2 has finished reading this P buffer
+                mbar_wait(smem_u32(&sm.o_done[(blk - 2) & 3]), (uint32_t)(((blk - 2) >> 2) & 1), e.err, dead, 48, e.wait_cycles);
+                tc_fence_after();
+            }
 #pragma unroll
             for (int j = 0; j < W / 16; ++j) tmem_st8(t_p + 8u * j, w[j]);
             tmem_wait_st();
@@ -1158,7 +1179,7 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
             const size_t smem_wide = sizeof(Tc5WideSmem) + 1024;
             err = ensure_dynamic_smem(extend_attend_tc5_wide_kernel, smem_wide, configured_wide);
             if (err != cudaSuccess) return err;
-            extend_attend_tc5_wide_kernel<<<dim3(e.rows_q / 128, e.hq), 576, smem_wide, l.stream>>>(e);
+            extend_attend_tc5_wide_kernel<<<dim3(e.rows_q / 128, e.hq), 608, smem_wide, l.stream>>>(e);
         } else if (!(l.flags & TS_CFG_EXTEND_FOUR_PER_ROW)) {
             static SmemConfig configured2 = {};
             err = ensure_dynamic_smem(extend_attend_tc5_kernel<2>, smem5, configured2);
