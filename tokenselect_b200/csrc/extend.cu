@@ -196,6 +196,8 @@ __device__ __forceinline__ void store8(T* head_base, int d, int row, int e0, con
 
 template <typename T>
 __global__ void __launch_bounds__(kExtThreads) extend_gather_kernel(const ExtendParams e, const int layout, const int kv_tile) {
+    // the attention kernel that follows may be scheduled now: it waits (griddepcontrol.wait) for this grid to finish
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (*(volatile int*)e.err != 0) return;
     const int half = e.d / 2;
     const int tpi = half / 8;                                             // threads per (row, head) item
@@ -830,13 +832,8 @@ __global__ void __launch_bounds__(608, 1) extend_attend_tc5_wide_kernel(const Ex
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int qt = blockIdx.x, h = blockIdx.y, kv = h / e.group;
     const int lq = e.chunk_len;
-    if (*(volatile int*)e.err != 0 || qt * 128 >= lq) return;
-    const int count = min(*e.sel_count, e.n_sel);
-    const int base_vis = count - lq;                         // query row r sees list entries j <= base_vis + r
-    const int kmax = min(count - 1, base_vis + qt * 128 + 127);
-    const int nblk = kmax / kWide + 1;
+    if (qt * 128 >= lq) return;
     bool dead = false;
-    const bool timed_cta = e.stamps != nullptr && qt == 0 && h == 0;      // cycle counts under TS_CFG_PHASE_STAMPS
 
     if (tid == 0) {
         mbar_init(smem_u32(&sm.qbar), 1);
@@ -860,8 +857,18 @@ __global__ void __launch_bounds__(608, 1) extend_attend_tc5_wide_kernel(const Ex
     tc_fence_after();
     const uint32_t tmem = *(volatile uint32_t*)&sm.tmem_base;
     constexpr uint32_t kTileBytes = kWide * 256;             // one K or V tile image
+    // Launched with programmatic stream serialization: everything above touched only this CTA's shared and tensor
+    // memory and ran while the gather kernel was finishing; nothing global is read before this wait.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const bool skip = *(volatile int*)e.err != 0;            // a handle in error: no work, but the tensor memory is freed
+    const int count = min(*e.sel_count, e.n_sel);
+    const int base_vis = count - lq;                         // query row r sees list entries j <= base_vis + r
+    const int kmax = min(count - 1, base_vis + qt * 128 + 127);
+    const int nblk = kmax / kWide + 1;
+    const bool timed_cta = e.stamps != nullptr && qt == 0 && h == 0;      // cycle counts under TS_CFG_PHASE_STAMPS
 
-    if (warp == 18) {
+    if (skip) {
+    } else if (warp == 18) {
         // ---------------- loader: one thread requests every tile ----------------
         if (lane == 0) {
             const unsigned char* qsrc = reinterpret_cast<const unsigned char*>(e.qc) + ((size_t)h * e.rows_q + (size_t)qt * 128) * 256;
@@ -1179,7 +1186,18 @@ cudaError_t launch_extend_attend(const ExtendParams& e, const Launch& l) {
             const size_t smem_wide = sizeof(Tc5WideSmem) + 1024;
             err = ensure_dynamic_smem(extend_attend_tc5_wide_kernel, smem_wide, configured_wide);
             if (err != cudaSuccess) return err;
-            extend_attend_tc5_wide_kernel<<<dim3(e.rows_q / 128, e.hq), 608, smem_wide, l.stream>>>(e);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(e.rows_q / 128, e.hq);
+            cfg.blockDim = dim3(608);
+            cfg.dynamicSmemBytes = smem_wide;
+            cfg.stream = l.stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            err = cudaLaunchKernelEx(&cfg, extend_attend_tc5_wide_kernel, e);
+            if (err != cudaSuccess) return err;
         } else if (!(l.flags & TS_CFG_EXTEND_FOUR_PER_ROW)) {
             static SmemConfig configured2 = {};
             err = ensure_dynamic_smem(extend_attend_tc5_kernel<2>, smem5, configured2);
