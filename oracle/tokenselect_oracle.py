@@ -10,7 +10,10 @@ It restates, in plain torch/numpy on the CPU, the algorithm of the reference fil
 Parity pin: the reference ships no tests or golden vectors.  The pin used here is the
 reference module itself, executed verbatim on the CPU (``oracle/reference_verbatim.py``), whose
 outputs are committed under ``tests/golden/`` and compared with this restatement by
-``tests/test_oracle_golden.py``.
+``tests/test_oracle_golden.py``.  The attention half (the third-party FlashInfer wrappers the reference
+calls, ``:746-772`` and ``:802-823``) is pinned to outputs of that library taken on a B200 with the
+reference's call-site arguments (``tests/golden/flashinfer_attention.npz``, made by
+``tests/golden/make_flashinfer_golden.py``, compared in ``tests/test_oracle_flashinfer.py``).
 
 Two arithmetic modes exist for the vote vector:
 

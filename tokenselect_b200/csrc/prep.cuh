@@ -124,6 +124,16 @@ __device__ __forceinline__ void prepare_request(const LayerParams& p, int b, Pre
     // 5. cosine terms against the cached query in a fixed order: lane j sums elements j + 32*i in
     //    ascending i, then an XOR butterfly (16, 8, 4, 2, 1) joins the 32 partial sums.
     const T* fp = reinterpret_cast<const T*>(p.fp_cache) + ((size_t)req * p.n_layers + p.layer) * hd;
+    if (p.query_cache) {
+        // every thread pulls a line of the two operand rows into L1 first: the one warp that sums them in the fixed
+        // order then waits for L1 instead of L2 on each of its batches
+        constexpr int kLine = 128 / (int)sizeof(T);
+#pragma unroll 1
+        for (int e = tid * kLine; e < hd; e += tg.nthr * kLine) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(fp + e));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(qr + e));
+        }
+    }
     if (p.query_cache && tid < 32) {
         float dot = 0.f, qq = 0.f, cc = 0.f;
         const bool have = p.valid[(size_t)req * p.n_layers + p.layer] != 0;
