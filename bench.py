@@ -1132,8 +1132,15 @@ def main():
         score_ms += stages["select_tp_b"][0]
         score_us = 1e3 * score_ms / max(score_n, 1)
         kernel_bytes = ab["layer"] if one_launch else ab["select"]
-        achieved = kernel_bytes / (score_us * 1e-6) / 1e9 if score_n else None
         us_layer = 1e3 * ms / (args.steps * layers)
+        launch_us_source = "event pair around every launch of the kernel (separate pass after the timed region)"
+        if one_launch:
+            # the timed region holds nothing but this kernel's launches, back to back: its CUDA events over the
+            # region divided by the launches are the kernel's average duration (the event-pair pass, kept in
+            # kernel_us, adds the events' own cost and the launch gaps they open)
+            score_us = us_layer
+            launch_us_source = "CUDA events over the timed region / launches in it (the region holds only this kernel)"
+        achieved = kernel_bytes / (score_us * 1e-6) / 1e9 if score_n else None
         per_stage_us = {k: round(1e3 * v[0] / max(v[1], 1), 3) for k, v in stages.items() if v[1]}
         line = {
             "metric": METRIC, "value": args.steps / (ms * 1e-3), "unit": "tok/s", "n_gpus": tp,
@@ -1156,7 +1163,7 @@ def main():
                          "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                          "peak_source": peak_kind, "bytes_per_launch": kernel_bytes,
-                         "us_per_launch": score_us,
+                         "us_per_launch": score_us, "us_per_launch_source": launch_us_source,
                          "traffic": (kernel_bytes * (STEP_DRAM_BYTES_PER_ALGORITHMIC_BYTE if one_launch else
                                                      SELECT_DRAM_BYTES_PER_ALGORITHMIC_BYTE)) if tp == 1 else None,
                          "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel "
