@@ -36,3 +36,19 @@ def test_algorithmic_bytes_of_the_headline_shape():
     assert ab["select"] == 130432 * 2048 + 130432 * 4 + 32 * 128 * 2 + 2688 * 4
     assert ab["attend"] == 2 * 2688 * 2048 + 2688 * 4 + 2 * 32 * 128 * 2
     assert abs(ab["layer"] / 1e6 - 278.7) < 0.1
+
+
+def test_attention_error_discounts_only_the_output_rounding():
+    """The bench's attention check holds the error beyond the output's own bf16 rounding (half a bf16 step =
+    2^-8 of the magnitude) to 2e-2: a large output rounded to bf16 passes, a small output that is off does not."""
+    import torch
+    sys.path.insert(0, ROOT)
+    import bench
+    ref = torch.tensor([13.037, -9.51, 0.3, 1e-3], dtype=torch.float64)
+    rounded = ref.to(torch.bfloat16)
+    err, beyond, ref_max = bench.attention_error(rounded, ref)
+    assert err > 2e-2 and beyond <= 1e-6 and abs(ref_max - 13.037) < 1e-9        # pure rounding: nothing beyond it
+    off = ref.clone()
+    off[2] += 0.05
+    err, beyond, _ = bench.attention_error(off, ref)
+    assert abs(err - 0.05) < 1e-9 and beyond > 2e-2                               # an error of order-one outputs shows
