@@ -62,6 +62,7 @@ extern "C" {
 #define TS_CFG_EXTEND_FOUR_PER_ROW 16u /* prefill attention: one softmax team, four threads per query row (diagnostic) */
 #define TS_CFG_EXTEND_NARROW_BLOCKS 512u /* prefill attention in 64-key blocks with one issuing thread, two softmax threads per row (the earlier form; diagnostic) */
 #define TS_CFG_PHASE_STAMPS 32u   /* kernels record %globaltimer at their phase boundaries for ts_debug_read(3) (diagnostic; off: no timer reads) */
+#define TS_CFG_TP_PULL 2048u       /* tensor-parallel exchange: pull the peers' votes after a flag also for tp_size <= 4 (default there: votes pushed with their exchange number attached) */
 #define TS_CFG_INLINE_ATTEND 1024u /* attention inside the layer-step kernel also for batches of several requests (default: single requests only) */
 #define TS_CFG_SPLIT_ATTEND 256u  /* attention in separate kernels after the selection kernel whatever the shape (diagnostic) */
 #define TS_CFG_STAGED_SCORE 4u    /* bf16: stage keys through shared memory by bulk copies whatever the row size */
@@ -232,9 +233,11 @@ int ts_tp_select_attend(ts_handle* h, const ts_decode_args* args);
  * :363-364 with loads from the peers' memory over NVLink).  Every rank allocates a buffer of
  * ts_tp_symmetric_bytes() that its peers can address (CUDA IPC / symmetric memory; zero-filled), then
  * passes the device addresses of ALL ranks' buffers, in rank order, to ts_tp_attach_peers().  After that
- * ts_decode_layer() works with tp_size > 1: each rank writes its raw votes to its own buffer, flags its
- * peers, waits (bounded) for theirs and sums the ranks' votes in rank order, so all ranks select from
- * bit-identical sums.  All ranks must issue the same sequence of calls (the exchanges are counted on the
+ * ts_decode_layer() works with tp_size > 1: up to four ranks, each rank stores its raw votes, paired with the
+ * exchange's number, straight into its peers' buffers and polls its own buffer for theirs (no flags, no
+ * system-scope fence; TS_CFG_TP_PULL selects the other form); above four, each rank writes its raw votes to its
+ * own buffer, flags its peers, waits for their flags and loads their votes.  Either way every wait is bounded and
+ * the ranks' votes are summed in rank order, so all ranks select from bit-identical sums.  All ranks must issue the same sequence of calls (the exchanges are counted on the
  * device, per CTA, by every launch whether it ran to its end or gave up on a wait, so the ranks' counts stay
  * aligned across a device-side time-out and nothing has to be attached again after one; a rank that creates
  * a NEW handle must pair it with new, zero-filled buffers on every rank).  Not available with the selection

@@ -39,6 +39,15 @@ def test_peer_flag_wait_runs_out_and_the_gpu_stays_usable():
     eng.attach_peer_buffers([mine.data_ptr(), silent_peer.data_ptr()])
     case, q, kp, vp, rtt, ridx, lens = _inputs(dev, HQ // 2, HKV // 2)
     out = torch.zeros_like(q)
+    # the same kernel once on a single-rank engine of the rank's shape: the first launch of a kernel in a process
+    # loads it, which takes longer than the limit under test
+    warm = TokenSelectEngine(TokenSelectConfig(rope_base=BASE, max_n_tokens=N + 8, top_k=K, n_init=N_INIT, n_local=N_LOCAL,
+                                               n_layers=1, num_q_heads=HQ // 2, num_kv_heads=HKV // 2, head_dim=D, max_reqs=2,
+                                               max_batch=1, max_total_tokens=N + 8), device=dev)
+    warm.decode_layer(0, q, None, None, None, kp, vp, rtt, ridx, lens, out=out)
+    torch.cuda.synchronize()
+    warm.raise_on_device_error()
+    warm.close()
     t0, t1, t2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
     t0.record()
     eng.decode_layer(0, q, None, None, None, kp, vp, rtt, ridx, lens, out=out)       # returns: the wait is bounded

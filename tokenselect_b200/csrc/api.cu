@@ -27,6 +27,7 @@ struct ts_handle {
     unsigned* dev_cta_epoch;                // [grid] exchanges done, per CTA
     unsigned char* peer_base[kMaxTp];      // every rank's symmetric buffer (host copy)
     float** dev_peer_votes;                 // [2][kMaxTp] device array of pointers
+    uint2** dev_peer_push;                  // [2][kMaxTp]
     unsigned** dev_peer_flags;              // [kMaxTp]
     int last_batch;
     long long wait_cycles;                  // ts_config.wait_limit_us in SM clock cycles
@@ -103,6 +104,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
     size_t o_ts = cv.take(128 * 8);
     size_t o_pv = cv.take(2 * kMaxTp * sizeof(void*));
     size_t o_pf = cv.take(kMaxTp * sizeof(void*));
+    size_t o_pp = cv.take(2 * kMaxTp * sizeof(void*));
     size_t o_ep = cv.take((size_t)grid * 4);
     size_t o_cand = cv.take((size_t)cap * 8);
     size_t o_slots = cv.take((size_t)c->max_batch * n_sel * 4);
@@ -165,6 +167,7 @@ size_t layout(const ts_config* c, int num_sms, ts_handle* h) {
         p.stamps = (c->flags & TS_CFG_PHASE_STAMPS) ? 1 : 0;
         h->dev_peer_votes = reinterpret_cast<float**>(a + o_pv);
         h->dev_peer_flags = reinterpret_cast<unsigned**>(a + o_pf);
+        h->dev_peer_push = reinterpret_cast<uint2**>(a + o_pp);
         h->dev_cta_epoch = reinterpret_cast<unsigned*>(a + o_ep);
         p.cand = reinterpret_cast<uint2*>(a + o_cand);
         p.sel_slots = reinterpret_cast<int*>(a + o_slots);
@@ -213,7 +216,15 @@ int num_sms_of(int device, int* out) {
 
 size_t sym_flag_bytes() { return (size_t)2 * kMaxTp * kFlagPad * sizeof(unsigned); }
 size_t sym_votes_offset(long long cap, int parity) { return sym_flag_bytes() + (size_t)parity * (size_t)cap * sizeof(float); }
-size_t sym_total_bytes(long long cap) { return sym_votes_offset(cap, 2); }
+// Push area (tensor-parallel degrees up to kPushMaxTp): per parity, one slice of cand_capacity (vote, number) pairs
+// per source rank.
+bool tp_pushes(const ts_config* c) { return c->tp_size > 1 && c->tp_size <= kPushMaxTp && !(c->flags & TS_CFG_TP_PULL); }
+size_t sym_push_offset(long long cap, int tp, int parity) {
+    return ((sym_votes_offset(cap, 2) + 255) & ~(size_t)255) + (size_t)parity * (size_t)tp * (size_t)cap * sizeof(uint2);
+}
+size_t sym_total_bytes(const ts_config* c, long long cap) {
+    return tp_pushes(c) ? sym_push_offset(cap, c->tp_size, 2) : sym_votes_offset(cap, 2);
+}
 
 int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l, bool fused_tp = false) {
     if (!h || !a || a->struct_size != sizeof(ts_decode_args)) return TS_ERR_INVALID_ARG;
@@ -244,6 +255,8 @@ int fill(ts_handle* h, const ts_decode_args* a, LayerParams& p, Launch& l, bool 
         // that a fast rank never overwrites votes a slow peer is still reading); the sum lands in the workspace
         p.peer_votes = h->dev_peer_votes;
         p.peer_flags = h->dev_peer_flags;
+        p.peer_push = h->dev_peer_push;
+        p.tp_push = tp_pushes(&h->cfg) ? 1 : 0;
         p.cta_epoch = h->dev_cta_epoch;
         p.votes_final = h->base.votes;
     }
@@ -421,7 +434,7 @@ int ts_tp_symmetric_bytes(const ts_config* cfg, size_t* bytes) {
     int s = validate(cfg);
     if (s != TS_OK) return s;
     if (!bytes) return TS_ERR_INVALID_ARG;
-    *bytes = sym_total_bytes(cand_capacity_of(cfg));
+    *bytes = sym_total_bytes(cfg, cand_capacity_of(cfg));
     return TS_OK;
 }
 
@@ -429,15 +442,20 @@ int ts_tp_attach_peers(ts_handle* h, const uint64_t* peer_buffers, int32_t count
     if (!h || !peer_buffers || count != h->cfg.tp_size || count > kMaxTp) return TS_ERR_INVALID_ARG;
     float* votes[2 * kMaxTp] = {nullptr};
     unsigned* flags[kMaxTp] = {nullptr};
+    uint2* push[2 * kMaxTp] = {nullptr};
     for (int r = 0; r < count; ++r) {
         if (!peer_buffers[r]) return TS_ERR_INVALID_ARG;
         h->peer_base[r] = reinterpret_cast<unsigned char*>(peer_buffers[r]);
         flags[r] = reinterpret_cast<unsigned*>(h->peer_base[r]);
-        for (int par = 0; par < 2; ++par)
+        for (int par = 0; par < 2; ++par) {
             votes[par * kMaxTp + r] = reinterpret_cast<float*>(h->peer_base[r] + sym_votes_offset(h->cand_capacity, par));
+            if (tp_pushes(&h->cfg))
+                push[par * kMaxTp + r] = reinterpret_cast<uint2*>(h->peer_base[r] + sym_push_offset(h->cand_capacity, count, par));
+        }
     }
     TS_TRY(cudaMemcpy(h->dev_peer_votes, votes, sizeof(votes), cudaMemcpyHostToDevice), "peer table");
     TS_TRY(cudaMemcpy(h->dev_peer_flags, flags, sizeof(flags), cudaMemcpyHostToDevice), "peer table");
+    TS_TRY(cudaMemcpy(h->dev_peer_push, push, sizeof(push), cudaMemcpyHostToDevice), "peer table");
     // The per-CTA exchange counts are NOT restarted: every launch of every rank counts, also one that gave
     // up on a wait, so the ranks stay aligned and a flag left in a pad by an earlier exchange can never equal
     // a later exchange's number.

@@ -21,6 +21,7 @@ constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stag
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
 constexpr int kFlagPad = 256;          // per-CTA flags per (parity, source rank) in the tensor-parallel flag pad
 constexpr int kMaxTp = 8;
+constexpr int kPushMaxTp = 4;             // largest tensor-parallel degree whose votes are pushed (8 bytes per vote and peer) rather than pulled
 constexpr int kFusedDynSmem = 196608;    // dynamic shared memory of the selection kernels (5 stages of 34 KB; the tail needs more)
 constexpr int kAttnThreads = 256;
 constexpr long long kWaitCycles = 2000000000LL;  // bound of every device-side wait (~1 s)
@@ -71,6 +72,8 @@ struct LayerParams {
     // tensor-parallel exchange over peer memory (mode kModeTpFused)
     float* const* peer_votes;  // [2][kMaxTp] every rank's raw-vote buffer (own included), one set per parity
     unsigned* const* peer_flags;  // [tp_size] every rank's flag pad [2][tp_size][kFlagPad]
+    uint2* const* peer_push;   // [2][kMaxTp] every rank's push area [source rank][cand_capacity] of (vote bits, exchange number), one per parity
+    int tp_push;               // votes are pushed to the peers with their exchange number attached (tp_size <= kPushMaxTp), else pulled after a flag
     unsigned* cta_epoch;       // [grid] exchanges done so far, kept per CTA: the next one carries count + 1 in
                                // its flags and uses the buffers of parity (count + 1) & 1; all ranks' same-numbered
                                // CTAs count alike, and nothing on the host changes from call to call

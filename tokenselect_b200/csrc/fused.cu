@@ -1104,11 +1104,97 @@ __device__ __forceinline__ void vote_phase(const LayerParams& p, FusedShared& sh
 // its raw votes are written, waits for theirs, and sums the ranks' votes of its own candidates in rank
 // order (so every rank gets bit-identical sums).  Replaces dist.all_reduce (token_retrieval.py:363-364).
 // All ranks run the same plan, hence the same ownership.  The wait is bounded.
+// The exchange for small tensor-parallel degrees: no flags, no system-scope release.  Every vote travels as an
+// 8-byte (vote bits, exchange number) pair stored straight into the peers' push areas (one 8-byte store is one
+// transaction, so a pair is seen whole or not at all); the receiver polls its OWN memory until a pair carries
+// the current exchange number.  The areas alternate with the number's parity and the numbers only grow, so a
+// pair left by an earlier exchange never matches.  Costs 8 bytes per vote and peer over NVLink instead of 4,
+// which is why degrees above kPushMaxTp pull instead.
+__device__ __forceinline__ void tp_exchange_push(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist,
+                                                 bool& dead) {
+    const int tid = threadIdx.x;
+    const int tp = p.tp_size, me = p.tp_rank;
+    const unsigned epoch = sh.epoch;
+    const int parity = (int)(epoch & 1u);
+    const size_t cap = (size_t)p.cand_capacity;
+    const float* mine = p.peer_votes[parity * kMaxTp + me];
+    uint2* const* push = p.peer_push + parity * kMaxTp;
+    // 1. own raw votes to every peer
+#pragma unroll 1
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const size_t off = (size_t)sh.plan.off[sg.b];
+#pragma unroll 1
+        for (int t = sg.t0 + tid; t < sg.t1; t += kFusedThreads) {
+            const unsigned v = __float_as_uint(__ldcg(mine + off + t));
+#pragma unroll 1
+            for (int r = 0; r < tp; ++r) {
+                if (r == me) continue;
+                uint2* dst = push[r] + (size_t)me * cap + off + t;
+                asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(v), "r"(epoch) : "memory");
+            }
+        }
+    }
+    stamp(p, 26);
+#pragma unroll 1
+    for (int i = tid; i < kHistBins; i += kFusedThreads) sh.hist[i] = 0u;
+    __syncthreads();
+    // 2. the peers' votes of the own candidates, as they arrive; summed in rank order
+    const uint2* own_area = push[me];
+    const long long t_begin = clock64();
+#pragma unroll 1
+    for (int s = 0; s < sh.nseg; ++s) {
+        const Seg sg = sh.seg[s];
+        const size_t off = (size_t)sh.plan.off[sg.b];
+        float* out = p.votes_final + off;
+#pragma unroll 1
+        for (int tb = sg.t0; tb < sg.t1; tb += kFusedThreads) {          // warp-uniform trip count
+            const int t = tb + tid;
+            const bool live = t < sg.t1;
+            float acc = 0.f;
+            if (live) {
+                const float own = __ldcg(mine + off + t);
+#pragma unroll 1
+                for (int r = 0; r < tp; ++r) {
+                    if (r == me) { acc += own; continue; }
+                    const uint2* src = own_area + (size_t)r * cap + off + t;
+                    uint2 v = make_uint2(0u, 0u);
+                    unsigned spins = 0;
+                    while (!dead) {
+                        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src) : "memory");
+                        if (v.y == epoch) break;
+                        if ((++spins & 63u) == 0u) {
+                            if (clock64() - t_begin > p.wait_cycles) {
+                                set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + r);
+                                dead = true;
+                            } else if (*(volatile int*)p.err != 0) {
+                                dead = true;
+                            }
+                        }
+                    }
+                    acc += __uint_as_float(v.x);
+                }
+                out[t] = acc;
+                if (sh.own_in_smem) own_votes(dyn)[sh.seg_off[s] + (t - sg.t0)] = acc;
+            }
+            if (with_hist) hist_add(sh.hist, vote_bin(acc), live);
+        }
+        stamp(p, 25);
+        if (with_hist) flush_hist(p, sh, sg.b);
+    }
+    // a wait that ran out in one thread ends the others' waits through the error word; all leave together
+    dead = __syncthreads_or(dead ? 1 : 0) != 0;
+}
+
 __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedShared& sh, unsigned char* dyn, bool with_hist,
                                                   bool& dead) {
     const int tid = threadIdx.x;
     const int tp = p.tp_size, me = p.tp_rank;
     __syncthreads();                                   // this CTA's raw votes are written
+    if (p.tp_push) {
+        tp_exchange_push(p, sh, dyn, with_hist, dead);
+        return;
+    }
     if (tid < tp && tid != me) {
         // release at system scope: the CTA's votes (ordered before this store by the barrier above) are
         // visible to the peer that observes the flag
