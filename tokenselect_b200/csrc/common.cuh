@@ -21,6 +21,7 @@ constexpr int kScoreStageUnits = 128; // (token, kv-head) rows of 256 B per stag
 constexpr int kIdxBlock = 1024;       // pool-row indices staged in shared memory at a time
 constexpr int kFlagPad = 256;          // per-CTA flags per (parity, source rank) in the tensor-parallel flag pad
 constexpr int kMaxTp = 8;
+constexpr long long kPushMaxVotes = 600000;  // candidates x peers up to which the votes are pushed (beyond: pulled, half the bytes)
 constexpr int kPushMaxTp = 4;             // largest tensor-parallel degree whose votes are pushed (8 bytes per vote and peer) rather than pulled
 constexpr int kFusedDynSmem = 196608;    // dynamic shared memory of the selection kernels (5 stages of 34 KB; the tail needs more)
 constexpr int kAttnThreads = 256;

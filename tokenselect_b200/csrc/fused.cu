@@ -1191,7 +1191,10 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
     const int tid = threadIdx.x;
     const int tp = p.tp_size, me = p.tp_rank;
     __syncthreads();                                   // this CTA's raw votes are written
-    if (p.tp_push) {
+    // Pushing costs 8 bytes per vote and peer against 4 for pulling but saves the flag round trip and the
+    // system-scope release (~4.5 us): it wins while the exchange is latency-bound.  Every CTA of every rank sees the
+    // same candidate total, so all take the same branch.
+    if (p.tp_push && (long long)sh.plan.off[p.batch] * (tp - 1) <= kPushMaxVotes) {
         tp_exchange_push(p, sh, dyn, with_hist, dead);
         return;
     }
