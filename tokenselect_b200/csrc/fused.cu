@@ -1142,6 +1142,7 @@ __device__ __forceinline__ void tp_exchange_push(const LayerParams& p, FusedShar
     // 2. the peers' votes of the own candidates, as they arrive; summed in rank order
     const uint2* own_area = push[me];
     const long long t_begin = clock64();
+    const long long peer_limit = p.wait_cycles - (p.wait_cycles >> 3);   // see tp_exchange_phase
 #pragma unroll 1
     for (int s = 0; s < sh.nseg; ++s) {
         const Seg sg = sh.seg[s];
@@ -1164,7 +1165,7 @@ __device__ __forceinline__ void tp_exchange_push(const LayerParams& p, FusedShar
                         asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src) : "memory");
                         if (v.y == epoch) break;
                         if ((++spins & 63u) == 0u) {
-                            if (clock64() - t_begin > p.wait_cycles) {
+                            if (clock64() - t_begin > peer_limit) {
                                 set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + r);
                                 dead = true;
                             } else if (*(volatile int*)p.err != 0) {
@@ -1207,13 +1208,15 @@ __device__ __forceinline__ void tp_exchange_phase(const LayerParams& p, FusedSha
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(epoch) : "memory");
         stamp(p, 26);
         const unsigned* src = p.peer_flags[me] + ((size_t)(parity * tp + tid) * kFlagPad + blockIdx.x);
+        // a peer that stays silent is reported as such (30 + its rank): the waits for peers give up at 7/8 of the
+        // limit, before a grid barrier that some CTA entered at about the same time can
         const long long t0 = clock64();
         unsigned v = 0, spins = 0;
         while (!dead) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
             if (v == epoch) break;
             if ((++spins & 63u) == 0u) {
-                if (clock64() - t0 > p.wait_cycles) {
+                if (clock64() - t0 > p.wait_cycles - (p.wait_cycles >> 3)) {
                     set_error(p.err, TS_ERR_DEVICE_TIMEOUT, 30 + tid);
                     dead = true;
                 } else if (*(volatile int*)p.err != 0) {
