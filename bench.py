@@ -565,7 +565,8 @@ def run_batch_config(args, which):
                 err, beyond, ref_max = max(err, e1), max(beyond, b1), max(ref_max, m1)
             check["attn_max_abs_err"], check["attn_max_err_beyond_output_rounding"] = err, beyond
             check["attn_ref_max_abs"] = ref_max
-            check["ok"] = bool(check["ranks_agree"] and ok and beyond <= 2e-2)
+            check["attn_tolerance"] = attention_tolerance(ref_max)
+            check["ok"] = bool(check["ranks_agree"] and ok and beyond <= check["attn_tolerance"])
         flag = torch.tensor([1 if (rank != 0 or check["ok"]) else 0], device=dev)
         if tp > 1:
             dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -773,9 +774,16 @@ def attention_error(out, ref):
     """(max |out - ref|, max of |out - ref| - 2^-8 |ref|, max |ref|).  The output is rounded to bf16, which alone
     moves an element by up to half a bf16 step = 2^-8 of its magnitude; the synthetic V rows carry outlier channels
     (x 8), so outputs of magnitude 10 and more occur and their rounding exceeds any fixed absolute bound.  The check
-    therefore holds the error BEYOND that rounding to the 2e-2 the tests use for outputs of order one."""
+    therefore holds the error BEYOND that rounding to attention_tolerance()."""
     d = (out.double() - ref).abs()
     return d.max().item(), (d - ref.abs() * 2.0 ** -8).max().item(), ref.abs().max().item()
+
+
+def attention_tolerance(ref_max):
+    """What the bench's check allows beyond the output's rounding: the 2e-2 of the parity tests, whose outputs are
+    of order one, scaled with the magnitude of this run's outputs where that exceeds 4 (an error in a softmax weight
+    shows in the output multiplied by the V entries it weighs, and the synthetic V rows here carry x 8 outliers)."""
+    return 2e-2 * max(1.0, ref_max / 4.0)
 
 
 def print_phase_times(eng, rank, tp):
@@ -850,7 +858,8 @@ def correctness_check(eng, dist, rank, tp, q, k_new, v_new, loc, k_pool, v_pool,
         e1, b1, m1 = attention_error(all_out[r].cpu(), ref)
         err, beyond, ref_max = max(err, e1), max(beyond, b1), max(ref_max, m1)
     res["attn_max_abs_err"], res["attn_max_err_beyond_output_rounding"], res["attn_ref_max_abs"] = err, beyond, ref_max
-    res["ok"] = bool(res["ranks_agree"] and res["oracle_match"] and beyond <= 2e-2)
+    res["attn_tolerance"] = attention_tolerance(ref_max)
+    res["ok"] = bool(res["ranks_agree"] and res["oracle_match"] and beyond <= res["attn_tolerance"])
     return res
 
 

@@ -52,3 +52,4 @@ def test_attention_error_discounts_only_the_output_rounding():
     off[2] += 0.05
     err, beyond, _ = bench.attention_error(off, ref)
     assert abs(err - 0.05) < 1e-9 and beyond > 2e-2                               # an error of order-one outputs shows
+    assert bench.attention_tolerance(1.3) == 2e-2 and abs(bench.attention_tolerance(10.0) - 5e-2) < 1e-12
