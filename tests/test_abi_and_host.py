@@ -69,6 +69,24 @@ def test_workspace_query_and_validation(built_library):
     assert built_library.ts_decode_layer(None, None) == 1
 
 
+def test_symmetric_buffer_size_follows_the_exchange_form(built_library):
+    """Peer-visible memory per rank: flag pad + two vote buffers; up to four ranks add two push areas of
+    tp_size x capacity 8-byte pairs (votes pushed with their exchange number), unless TS_CFG_TP_PULL."""
+    def nbytes(**kw):
+        n = C.c_size_t()
+        assert built_library.ts_tp_symmetric_bytes(C.byref(_cfg(**kw)), C.byref(n)) == 0
+        return n.value
+    ve = C.c_int64()
+    assert built_library.ts_vote_buffer_elems(C.byref(_cfg(hq=4, hkv=1, tp_size=8)), C.byref(ve)) == 0
+    cap = ve.value
+    pull8 = nbytes(hq=4, hkv=1, tp_size=8)
+    assert pull8 == 2 * 8 * 256 * 4 + 2 * cap * 4                      # flags [2][8][256] + votes [2][cap]
+    assert nbytes(hq=8, hkv=2, tp_size=4, flags=2048) == pull8         # pull forced: same layout at any degree
+    push4, push2 = nbytes(hq=8, hkv=2, tp_size=4), nbytes(hq=16, hkv=4, tp_size=2)
+    assert 0 <= push4 - pull8 - 2 * 4 * cap * 8 < 256                  # + [2][4][cap] pairs, 256-byte aligned
+    assert 0 <= push2 - pull8 - 2 * 2 * cap * 8 < 256
+
+
 def test_struct_layout_matches_header():
     """Compile a one-line C program against the header and compare sizeof with the ctypes mirror."""
     import subprocess
